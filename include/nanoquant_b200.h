@@ -1,0 +1,177 @@
+/*
+ * nanoquant_b200 — C ABI of the sm_100a kernels for the NanoQuant binary
+ * low-rank quantised linear
+ *
+ *     y = s_out * (U_b . (s_mid * (V_b . (s_in * x))))
+ *
+ * with V_b [R, N] and U_b [M, R] packed ±1 matrices (bit 1 = -1, bit 0 = +1),
+ * N = in_features, R = rank, M = out_features, T = tokens.
+ *
+ * Every pointer is a DEVICE pointer unless its name ends in `_host`.  No torch
+ * types cross this boundary.  All functions are asynchronous on `stream`
+ * (a `cudaStream_t`), never synchronise the device, never allocate unless the
+ * comment says so, and return 0 (NQ_OK) or a negative nq_status.  They do not
+ * throw.  The library is built for sm_100a only and has no CPU fallback.
+ *
+ * The citations name the reference interface (SamsungLabs/NanoQuant, paths
+ * relative to that project) that each entry point replaces.
+ */
+#ifndef NANOQUANT_B200_H
+#define NANOQUANT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* nq_stream_t; /* == cudaStream_t */
+
+typedef enum {
+    NQ_OK = 0,
+    NQ_ERR_NULL = -1,        /* a required pointer is NULL */
+    NQ_ERR_SHAPE = -2,       /* a dimension is <= 0 or violates a divisibility rule */
+    NQ_ERR_DTYPE = -3,       /* dtype is not NQ_F16 / NQ_BF16, or method id unknown */
+    NQ_ERR_ALIGN = -4,       /* a pointer is not aligned as required (16 bytes) */
+    NQ_ERR_SCRATCH = -5,     /* scratch / workspace buffer too small */
+    NQ_ERR_CUDA = -6,        /* a CUDA runtime call failed; see nq_last_cuda_error() */
+    NQ_ERR_TIMEOUT = -7,     /* a bounded device-side wait gave up (read from a status word) */
+    NQ_ERR_UNSUPPORTED = -8, /* shape outside what the kernels implement */
+    NQ_ERR_TOO_LARGE = -9    /* size beyond a stated fixed maximum */
+} nq_status;
+
+typedef enum { NQ_F16 = 0, NQ_BF16 = 1 } nq_dtype;
+
+/* Bit order inside a 32-column word.
+ * reference: src/nanoquant/kernel/utils.py:99-104 */
+typedef enum {
+    NQ_LSB_FIRST = 0, /* element k -> bit k (checkpoint layout) */
+    NQ_HALF2 = 1      /* element 2j -> bit 15-j, element 2j+1 -> bit 31-j (GEMV runtime layout) */
+} nq_bit_order;
+
+/* Library / ABI identification. */
+int nq_abi_version(void);
+const char* nq_strerror(int status);
+/* Text of the last CUDA runtime error seen by this thread inside the library. */
+const char* nq_last_cuda_error(void);
+
+/* ------------------------------------------------------------------------ *
+ * Pack / layout kernels (bit-exact with the reference's PyTorch packers)
+ * ------------------------------------------------------------------------ */
+
+/* ±1 int8 [rows, cols] -> int32 [rows, ceil(cols/32)], padding columns +1.
+ * replaces: pack_binary_gemv, src/nanoquant/kernel/utils.py:51-113 */
+int nq_pack_rows(const int8_t* w, int32_t* packed, int64_t rows, int64_t cols,
+                 int bit_order, nq_stream_t stream);
+
+/* inverse of nq_pack_rows.
+ * replaces: unpack_binary_gemv, src/nanoquant/kernel/utils.py:116-183 */
+int nq_unpack_rows(const int32_t* packed, int8_t* w, int64_t rows, int64_t cols,
+                   int bit_order, nq_stream_t stream);
+
+/* Re-order the bits of every word from one nq_bit_order to another without
+ * materialising the dense ±1 matrix (checkpoint layout -> GEMV runtime layout).
+ * replaces: the unpack-to-bf16 + re-pack detour of
+ * src/nanoquant/utils/load_utils.py:279-287 and src/nanoquant/modules/linear.py:171-172 */
+int nq_reorder_words(const int32_t* in, int32_t* out, int64_t n_words,
+                     int order_in, int order_out, nq_stream_t stream);
+
+/* ±1 int8 weight [out_f, in_f] (out_f % 64 == 0, in_f % 16 == 0) ->
+ * int32 B [in_f/16, out_f/2] in the Marlin mma-fragment order.
+ * replaces: the bit part of pack_binary_marlin, src/nanoquant/kernel/utils.py:191-205 */
+int nq_pack_marlin(const int8_t* w, int32_t* B, int64_t out_f, int64_t in_f,
+                   nq_stream_t stream);
+
+/* inverse of nq_pack_marlin: B [in_f/16, out_f/2] -> row-packed words
+ * [out_f, in_f/32] in `bit_order` (in_f % 32 == 0).  Lets operands prepared
+ * with the reference's Marlin packer be consumed by the kernels here. */
+int nq_marlin_to_rows(const int32_t* B, int32_t* packed, int64_t out_f, int64_t in_f,
+                      int bit_order, nq_stream_t stream);
+
+/* Scale permutations of the Marlin packer on 16-bit elements.
+ * kind 0: per group of 16, new[4b+2a+c] = old[8a+2b+c]  (utils.py:206-207)
+ * kind 1: per group of 32, new[8b+2a+c] = old[8a+2b+c]  (utils.py:208-209)
+ * inverse != 0 applies the inverse permutation. */
+int nq_permute_scale16(const void* s, void* out, int64_t n, int kind, int inverse,
+                       nq_stream_t stream);
+
+/* ------------------------------------------------------------------------ *
+ * Runtime tile layout of the GEMV kernel
+ * ------------------------------------------------------------------------ */
+
+/* Bytes of the tile layout of a packed [rows, cols] matrix:
+ * ceil(rows/16) * ceil(cols/256) tiles of 512 bytes. */
+size_t nq_tiles_bytes(int64_t rows, int64_t cols);
+
+/* rows layout (int32 [rows, ceil(cols/32)] in `bit_order`) -> tile layout.
+ * A tile covers 16 rows x 256 columns, stored as 32 lanes x 16 bytes, tiles
+ * ordered [row_group][chunk]; lane 4g+q holds the words {row g cols h=0, row g+8
+ * h=0, row g h=1, row g+8 h=1} and the weight of chunk column 32j + 16h + 4q + b
+ * sits at bit 8b + j of its word.  Rows / columns beyond the matrix are +1.
+ * replaces: the `binary_packer(..., method="half2")` re-pack of
+ * src/nanoquant/modules/linear.py:171-172 (runtime layout of the reference GEMV) */
+int nq_rows_to_tiles(const int32_t* packed, void* tiles, int64_t rows, int64_t cols,
+                     int bit_order, nq_stream_t stream);
+
+/* inverse of nq_rows_to_tiles. */
+int nq_tiles_to_rows(const void* tiles, int32_t* packed, int64_t rows, int64_t cols,
+                     int bit_order, nq_stream_t stream);
+
+/* ------------------------------------------------------------------------ *
+ * Decode GEMV (small T)
+ * ------------------------------------------------------------------------ */
+
+/* One quantised linear y[T, M] = s_out * (U . (s_mid * (V . (s_in * x[T, N])))).
+ * v_tiles / u_tiles are V [R, N] and U [M, R] in the tile layout, s_mid may be
+ * NULL; x, y and the scales share one dtype; ldx / ldy are row strides in elements. */
+typedef struct {
+    const void* x;
+    const void* s_in;
+    const void* v_tiles;
+    const void* s_mid;
+    const void* u_tiles;
+    const void* s_out;
+    void* y;
+    int N, R, M;
+    int64_t ldx, ldy;
+} nq_linear_desc;
+
+/* Bytes of scratch nq_gemv_fwd / nq_gemv_group_fwd need (0 on invalid sizes). */
+size_t nq_gemv_scratch_bytes(int T, int N, int R, int M);
+size_t nq_gemv_group_scratch_bytes(const nq_linear_desc* linears_host, int n_linears, int T);
+
+/* The decode GEMV.  Accumulation is exact integer arithmetic on a 16-bit
+ * fixed-point image of (s_in * x) and of the rank-R intermediate (per-token
+ * scale), results are converted once per output in fp32.  `scratch` holds a
+ * 256-byte header (device-wide barrier state + status word) followed by the
+ * fp32 intermediate; it must be 16-byte aligned, at least
+ * nq_gemv_scratch_bytes() long and ZEROED ONCE by the caller after allocation
+ * (the kernel leaves the header reusable).  Calls that share a scratch buffer
+ * must be ordered on one stream.  T > 4 is processed as several launches.
+ * fp16 outputs saturate at +-64504, bf16 at +-3.3895e38 like the reference.
+ * replaces: nanoquant_dyn_forward, src/nanoquant/kernel/cuda/gemv_kernel.cu:308-429
+ * (schema src/nanoquant/kernel/pybind.cpp:85-90) */
+int nq_gemv_fwd(const void* x, const void* s_in, const void* v_tiles, const void* s_mid,
+                const void* u_tiles, const void* s_out, void* y,
+                void* scratch, size_t scratch_bytes,
+                int T, int N, int R, int M, int dtype, nq_stream_t stream);
+
+/* Up to 4 linears whose two phases run together in ONE launch (q/k/v or
+ * gate/up of a decoder layer).  `linears_host` is a HOST array; its pointers are
+ * device pointers.  Same scratch contract as nq_gemv_fwd with
+ * nq_gemv_group_scratch_bytes().
+ * replaces: consecutive nanoquant_dyn_forward calls issued by
+ * src/nanoquant/modules/linear.py:121-130 for projections that share a layer input */
+int nq_gemv_group_fwd(const nq_linear_desc* linears_host, int n_linears, int T, int dtype,
+                      void* scratch, size_t scratch_bytes, nq_stream_t stream);
+
+/* Synchronises `stream` and returns the status word of a scratch buffer:
+ * NQ_OK, or NQ_ERR_TIMEOUT when a device-wide wait of an earlier launch gave up
+ * (the scratch must then be zeroed again before reuse). */
+int nq_scratch_status(const void* scratch, nq_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NANOQUANT_B200_H */

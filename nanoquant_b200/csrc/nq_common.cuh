@@ -1,0 +1,90 @@
+// Shared helpers of the nanoquant_b200 kernels: status handling, argument
+// checks and the bit-order conversions of a 32-column word.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/nanoquant_b200.h"
+
+namespace nq {
+
+// Records the text of a failed CUDA runtime call for nq_last_cuda_error().
+void set_cuda_error(cudaError_t e, const char* where);
+
+inline int check_cuda(cudaError_t e, const char* where) {
+    if (e == cudaSuccess) return NQ_OK;
+    set_cuda_error(e, where);
+    return NQ_ERR_CUDA;
+}
+
+#define NQ_CUDA_TRY(expr)                                             \
+    do {                                                              \
+        int _s = ::nq::check_cuda((expr), #expr);                     \
+        if (_s != NQ_OK) return _s;                                   \
+    } while (0)
+
+// Launch errors surface through cudaGetLastError right after the <<<>>>.
+#define NQ_LAUNCH_CHECK() NQ_CUDA_TRY(cudaGetLastError())
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+inline cudaStream_t as_stream(nq_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
+
+// Number of SMs of the current device (cached per device).
+int sm_count();
+
+// ---------------------------------------------------------------------------
+// bit orders of a 32-column word
+//   lsb_first: element k              -> bit k
+//   half2:     element 2j / element 2j+1 -> bit 15-j / bit 31-j
+// ---------------------------------------------------------------------------
+
+// keep the even bits of w, squeezed into the low 16 bits
+__host__ __device__ inline uint32_t squeeze_even_bits(uint32_t w) {
+    uint32_t x = w & 0x55555555u;
+    x = (x | (x >> 1)) & 0x33333333u;
+    x = (x | (x >> 2)) & 0x0F0F0F0Fu;
+    x = (x | (x >> 4)) & 0x00FF00FFu;
+    x = (x | (x >> 8)) & 0x0000FFFFu;
+    return x;
+}
+
+// spread the low 16 bits of v onto the even bit positions
+__host__ __device__ inline uint32_t spread_to_even_bits(uint32_t v) {
+    uint32_t x = v & 0x0000FFFFu;
+    x = (x | (x << 8)) & 0x00FF00FFu;
+    x = (x | (x << 4)) & 0x0F0F0F0Fu;
+    x = (x | (x << 2)) & 0x33333333u;
+    x = (x | (x << 1)) & 0x55555555u;
+    return x;
+}
+
+__host__ __device__ inline uint32_t reverse16(uint32_t v) {
+    v = ((v & 0x5555u) << 1) | ((v >> 1) & 0x5555u);
+    v = ((v & 0x3333u) << 2) | ((v >> 2) & 0x3333u);
+    v = ((v & 0x0F0Fu) << 4) | ((v >> 4) & 0x0F0Fu);
+    v = ((v & 0x00FFu) << 8) | ((v >> 8) & 0x00FFu);
+    return v & 0xFFFFu;
+}
+
+__host__ __device__ inline uint32_t lsb_to_half2(uint32_t w) {
+    uint32_t even = squeeze_even_bits(w);       // elements 0,2,4,.. in bits 0..15
+    uint32_t odd = squeeze_even_bits(w >> 1);   // elements 1,3,5,..
+    return reverse16(even) | (reverse16(odd) << 16);
+}
+
+__host__ __device__ inline uint32_t half2_to_lsb(uint32_t h) {
+    uint32_t even = reverse16(h & 0xFFFFu);
+    uint32_t odd = reverse16(h >> 16);
+    return spread_to_even_bits(even) | (spread_to_even_bits(odd) << 1);
+}
+
+__host__ __device__ inline uint32_t convert_order(uint32_t w, int from, int to) {
+    if (from == to) return w;
+    return from == NQ_LSB_FIRST ? lsb_to_half2(w) : half2_to_lsb(w);
+}
+
+}  // namespace nq

@@ -1,0 +1,346 @@
+// Pack / layout kernels.  All integer work, bit-exact with the reference's
+// PyTorch packers (src/nanoquant/kernel/utils.py in the reference project):
+//
+//   rows layout    int32 [rows, ceil(cols/32)], bit order lsb_first or half2
+//   marlin layout  int32 [in/16, out/2], one word = the B fragments of one lane
+//   tile layout    the runtime layout of the GEMV kernel here, see nq_rows_to_tiles
+//
+// Each thread produces whole output words so that stores are coalesced; the
+// kernels are bound by the bytes they read and write.
+#include "nq_common.cuh"
+
+namespace nq {
+
+constexpr int kPackThreads = 256;
+
+static inline unsigned grid_for(int64_t n, int threads) {
+    int64_t g = (n + threads - 1) / threads;
+    const int64_t cap = 148LL * 64;  // grid-stride beyond this
+    return static_cast<unsigned>(g < 1 ? 1 : (g > cap ? cap : g));
+}
+
+// sign bits of four int8 values held in one register -> 4-bit field (byte b -> bit b)
+__device__ __forceinline__ uint32_t sign_nibble(uint32_t v) {
+    uint32_t x = (v >> 7) & 0x01010101u;
+    return (x * 0x01020408u) >> 24;  // gathers bits 0,8,16,24 into bits 0..3
+}
+
+// 4-bit field -> bit b placed at position 8*b
+__device__ __forceinline__ uint32_t spread_nibble(uint32_t n) {
+    return ((n & 0xFu) * 0x00204081u) & 0x01010101u;
+}
+
+// ---------------------------------------------------------------------------
+// rows layout
+// ---------------------------------------------------------------------------
+__global__ void pack_rows_kernel(const int8_t* __restrict__ w, uint32_t* __restrict__ out,
+                                 int64_t rows, int64_t cols, int64_t words, int order, bool vec) {
+    const int64_t total = rows * words;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / words, wi = i - r * words;
+        const int64_t c0 = wi * 32;
+        const int8_t* src = w + r * cols + c0;
+        uint32_t bits = 0;
+        if (vec && c0 + 32 <= cols) {
+            const uint4 a = __ldg(reinterpret_cast<const uint4*>(src));
+            const uint4 b = __ldg(reinterpret_cast<const uint4*>(src) + 1);
+            bits = sign_nibble(a.x) | (sign_nibble(a.y) << 4) | (sign_nibble(a.z) << 8) |
+                   (sign_nibble(a.w) << 12) | (sign_nibble(b.x) << 16) | (sign_nibble(b.y) << 20) |
+                   (sign_nibble(b.z) << 24) | (sign_nibble(b.w) << 28);
+        } else {
+            const int n = (int)((cols - c0) < 32 ? (cols - c0) : 32);
+            for (int k = 0; k < n; ++k) bits |= (uint32_t)(src[k] < 0) << k;  // padding stays +1 (bit 0)
+        }
+        out[i] = convert_order(bits, NQ_LSB_FIRST, order);
+    }
+}
+
+__global__ void unpack_rows_kernel(const uint32_t* __restrict__ packed, int8_t* __restrict__ w,
+                                   int64_t rows, int64_t cols, int64_t words, int order, bool vec) {
+    const int64_t total = rows * words;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / words, wi = i - r * words;
+        const int64_t c0 = wi * 32;
+        const uint32_t bits = convert_order(packed[i], order, NQ_LSB_FIRST);
+        int8_t* dst = w + r * cols + c0;
+        if (vec && c0 + 32 <= cols) {
+            uint32_t v[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                // bit b of the nibble -> byte b; +1 = 0x01, -1 = 0xFF  (1 - 2*bit)
+                const uint32_t s = spread_nibble(bits >> (4 * k));
+                v[k] = 0x01010101u + s * 0xFEu;
+            }
+            reinterpret_cast<uint4*>(dst)[0] = make_uint4(v[0], v[1], v[2], v[3]);
+            reinterpret_cast<uint4*>(dst)[1] = make_uint4(v[4], v[5], v[6], v[7]);
+        } else {
+            const int n = (int)((cols - c0) < 32 ? (cols - c0) : 32);
+            for (int k = 0; k < n; ++k) dst[k] = ((bits >> k) & 1u) ? (int8_t)-1 : (int8_t)1;
+        }
+    }
+}
+
+__global__ void reorder_words_kernel(const uint32_t* __restrict__ in, uint32_t* __restrict__ out,
+                                     int64_t n, int from, int to) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n;
+         i += (int64_t)gridDim.x * blockDim.x)
+        out[i] = convert_order(in[i], from, to);
+}
+
+// ---------------------------------------------------------------------------
+// marlin layout.  out = 64*to + 16*o16 + 8*o8 + o1, in = 16*tr + 8*r8 + 2*r2 + r1
+//   word (tr, 32*to + 4*o1 + r2), bit 15 - 4*o16 - 2*o8 - r8 + 16*r1
+// ---------------------------------------------------------------------------
+__global__ void pack_marlin_kernel(const int8_t* __restrict__ w, uint32_t* __restrict__ B,
+                                   int64_t out_f, int64_t in_f) {
+    const int64_t ncol = out_f / 2, total = (in_f / 16) * ncol;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t tr = i / ncol, col = i - tr * ncol;
+        const int64_t to = col >> 5;
+        const int o1 = (int)(col & 31) >> 2, r2 = (int)(col & 3);
+        uint32_t bits = 0;
+#pragma unroll
+        for (int o16 = 0; o16 < 4; ++o16)
+#pragma unroll
+            for (int o8 = 0; o8 < 2; ++o8)
+#pragma unroll
+                for (int r8 = 0; r8 < 2; ++r8) {
+                    const int64_t o = 64 * to + 16 * o16 + 8 * o8 + o1;
+                    const int64_t k = 16 * tr + 8 * r8 + 2 * r2;
+                    const int8_t* p = w + o * in_f + k;
+                    const int pos = 15 - 4 * o16 - 2 * o8 - r8;
+                    bits |= (uint32_t)(p[0] < 0) << pos;
+                    bits |= (uint32_t)(p[1] < 0) << (pos + 16);
+                }
+        B[i] = bits;
+    }
+}
+
+__global__ void marlin_to_rows_kernel(const uint32_t* __restrict__ B, uint32_t* __restrict__ packed,
+                                      int64_t out_f, int64_t in_f, int order) {
+    const int64_t words = in_f / 32, total = out_f * words, ncol = out_f / 2;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t o = i / words, wi = i - o * words;
+        const int64_t to = o >> 6;
+        const int o16 = (int)(o >> 4) & 3, o8 = (int)(o >> 3) & 1, o1 = (int)o & 7;
+        uint32_t bits = 0;
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {  // two k-tiles of 16 per 32-column word
+            const int64_t tr = wi * 2 + t;
+#pragma unroll
+            for (int r2 = 0; r2 < 4; ++r2) {
+                const uint32_t src = B[tr * ncol + 32 * to + 4 * o1 + r2];
+#pragma unroll
+                for (int r8 = 0; r8 < 2; ++r8)
+#pragma unroll
+                    for (int r1 = 0; r1 < 2; ++r1) {
+                        const int pos = 15 - 4 * o16 - 2 * o8 - r8 + 16 * r1;
+                        const int k = 16 * t + 8 * r8 + 2 * r2 + r1;
+                        bits |= ((src >> pos) & 1u) << k;
+                    }
+            }
+        }
+        packed[i] = convert_order(bits, NQ_LSB_FIRST, order);
+    }
+}
+
+// kind 0: groups of 16, new[4b+2a+c] = old[8a+2b+c]; kind 1: groups of 32, new[8b+2a+c] = old[8a+2b+c]
+__global__ void permute_scale16_kernel(const uint16_t* __restrict__ s, uint16_t* __restrict__ out,
+                                       int64_t n, int kind, int inverse) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        int64_t base;
+        int p, a, b, c, src;
+        if (kind == 0) {
+            base = i & ~15LL; p = (int)(i & 15);
+            b = p >> 2; a = (p >> 1) & 1; c = p & 1;   // p = 4b + 2a + c
+            src = 8 * a + 2 * b + c;
+        } else {
+            base = i & ~31LL; p = (int)(i & 31);
+            b = p >> 3; a = (p >> 1) & 3; c = p & 1;   // p = 8b + 2a + c
+            src = 8 * a + 2 * b + c;
+        }
+        if (!inverse) out[i] = s[base + src];
+        else out[base + src] = s[i];
+    }
+}
+
+// ---------------------------------------------------------------------------
+// tile layout of the GEMV kernel
+//
+// A tile covers 16 rows x 256 columns and is stored as 32 lanes x uint4 (512 B),
+// tiles ordered [row_group][chunk].  Lane l = 4*g + q holds
+//   .x: row g,   columns half h=0      .y: row g+8, h=0
+//   .z: row g,   h=1                   .w: row g+8, h=1
+// and inside a word the weight of column 32*j + 16*h + 4*q + b (of the chunk)
+// sits at bit 8*b + j.  `word & (0x01010101 << j)` is then directly the int8
+// A-fragment register of an m16n8k32 MMA over columns [32j, 32j+32) with values
+// {0, 2^j} (j = 7: {0, -128}).  Rows and columns beyond the matrix are +1 (bit 0).
+// ---------------------------------------------------------------------------
+__global__ void rows_to_tiles_kernel(const uint32_t* __restrict__ packed, uint4* __restrict__ tiles,
+                                     int64_t rows, int64_t words, int64_t row_groups, int64_t chunks,
+                                     int order) {
+    const int64_t total = row_groups * chunks * 32;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int lane = (int)(i & 31);
+        const int64_t tile = i >> 5;
+        const int64_t rg = tile / chunks, c = tile - rg * chunks;
+        const int g = lane >> 2, q = lane & 3;
+        uint32_t o[4] = {0, 0, 0, 0};
+#pragma unroll
+        for (int half_row = 0; half_row < 2; ++half_row) {
+            const int64_t r = rg * 16 + g + 8 * half_row;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int64_t wi = c * 8 + j;
+                uint32_t src = 0;
+                if (r < rows && wi < words) src = convert_order(packed[r * words + wi], order, NQ_LSB_FIRST);
+                o[half_row] |= spread_nibble(src >> (4 * q)) << j;           // h = 0
+                o[2 + half_row] |= spread_nibble(src >> (16 + 4 * q)) << j;  // h = 1
+            }
+        }
+        tiles[i] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+
+__global__ void tiles_to_rows_kernel(const uint4* __restrict__ tiles, uint32_t* __restrict__ packed,
+                                     int64_t rows, int64_t words, int64_t chunks, int order) {
+    const int64_t total = rows * words;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / words, wi = i - r * words;
+        const int64_t rg = r >> 4, c = wi >> 3;
+        const int g = (int)(r & 7), half_row = (int)(r >> 3) & 1, j = (int)(wi & 7);
+        uint32_t bits = 0;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const uint4 t = tiles[(rg * chunks + c) * 32 + 4 * g + q];
+            const uint32_t lo = half_row ? t.y : t.x, hi = half_row ? t.w : t.z;
+            const uint32_t nlo = (((lo >> j) & 0x01010101u) * 0x01020408u) >> 24;
+            const uint32_t nhi = (((hi >> j) & 0x01010101u) * 0x01020408u) >> 24;
+            bits |= (nlo & 0xFu) << (4 * q);
+            bits |= (nhi & 0xFu) << (16 + 4 * q);
+        }
+        packed[i] = convert_order(bits, NQ_LSB_FIRST, order);
+    }
+}
+
+static int check_order(int o) { return (o == NQ_LSB_FIRST || o == NQ_HALF2) ? NQ_OK : NQ_ERR_DTYPE; }
+
+}  // namespace nq
+
+using namespace nq;
+
+extern "C" {
+
+int nq_pack_rows(const int8_t* w, int32_t* packed, int64_t rows, int64_t cols, int bit_order,
+                 nq_stream_t stream) {
+    if (rows < 0 || cols < 0) return NQ_ERR_SHAPE;
+    if (check_order(bit_order) != NQ_OK) return NQ_ERR_DTYPE;
+    if (rows == 0 || cols == 0) return NQ_OK;
+    if (!w || !packed) return NQ_ERR_NULL;
+    const int64_t words = (cols + 31) / 32;
+    const bool vec = (cols % 16 == 0) && aligned16(w);
+    pack_rows_kernel<<<grid_for(rows * words, kPackThreads), kPackThreads, 0, as_stream(stream)>>>(
+        w, reinterpret_cast<uint32_t*>(packed), rows, cols, words, bit_order, vec);
+    NQ_LAUNCH_CHECK();
+    return NQ_OK;
+}
+
+int nq_unpack_rows(const int32_t* packed, int8_t* w, int64_t rows, int64_t cols, int bit_order,
+                   nq_stream_t stream) {
+    if (rows < 0 || cols < 0) return NQ_ERR_SHAPE;
+    if (check_order(bit_order) != NQ_OK) return NQ_ERR_DTYPE;
+    if (rows == 0 || cols == 0) return NQ_OK;
+    if (!w || !packed) return NQ_ERR_NULL;
+    const int64_t words = (cols + 31) / 32;
+    const bool vec = (cols % 16 == 0) && aligned16(w);
+    unpack_rows_kernel<<<grid_for(rows * words, kPackThreads), kPackThreads, 0, as_stream(stream)>>>(
+        reinterpret_cast<const uint32_t*>(packed), w, rows, cols, words, bit_order, vec);
+    NQ_LAUNCH_CHECK();
+    return NQ_OK;
+}
+
+int nq_reorder_words(const int32_t* in, int32_t* out, int64_t n_words, int order_in, int order_out,
+                     nq_stream_t stream) {
+    if (n_words < 0) return NQ_ERR_SHAPE;
+    if (check_order(order_in) != NQ_OK || check_order(order_out) != NQ_OK) return NQ_ERR_DTYPE;
+    if (n_words == 0) return NQ_OK;
+    if (!in || !out) return NQ_ERR_NULL;
+    reorder_words_kernel<<<grid_for(n_words, kPackThreads), kPackThreads, 0, as_stream(stream)>>>(
+        reinterpret_cast<const uint32_t*>(in), reinterpret_cast<uint32_t*>(out), n_words, order_in, order_out);
+    NQ_LAUNCH_CHECK();
+    return NQ_OK;
+}
+
+int nq_pack_marlin(const int8_t* w, int32_t* B, int64_t out_f, int64_t in_f, nq_stream_t stream) {
+    if (out_f < 0 || in_f < 0 || out_f % 64 || in_f % 16) return NQ_ERR_SHAPE;
+    if (out_f == 0 || in_f == 0) return NQ_OK;
+    if (!w || !B) return NQ_ERR_NULL;
+    pack_marlin_kernel<<<grid_for((in_f / 16) * (out_f / 2), kPackThreads), kPackThreads, 0, as_stream(stream)>>>(
+        w, reinterpret_cast<uint32_t*>(B), out_f, in_f);
+    NQ_LAUNCH_CHECK();
+    return NQ_OK;
+}
+
+int nq_marlin_to_rows(const int32_t* B, int32_t* packed, int64_t out_f, int64_t in_f, int bit_order,
+                      nq_stream_t stream) {
+    if (out_f < 0 || in_f < 0 || out_f % 64 || in_f % 32) return NQ_ERR_SHAPE;
+    if (check_order(bit_order) != NQ_OK) return NQ_ERR_DTYPE;
+    if (out_f == 0 || in_f == 0) return NQ_OK;
+    if (!B || !packed) return NQ_ERR_NULL;
+    marlin_to_rows_kernel<<<grid_for(out_f * (in_f / 32), kPackThreads), kPackThreads, 0, as_stream(stream)>>>(
+        reinterpret_cast<const uint32_t*>(B), reinterpret_cast<uint32_t*>(packed), out_f, in_f, bit_order);
+    NQ_LAUNCH_CHECK();
+    return NQ_OK;
+}
+
+int nq_permute_scale16(const void* s, void* out, int64_t n, int kind, int inverse, nq_stream_t stream) {
+    if (kind != 0 && kind != 1) return NQ_ERR_DTYPE;
+    if (n < 0 || n % (kind == 0 ? 16 : 32)) return NQ_ERR_SHAPE;
+    if (n == 0) return NQ_OK;
+    if (!s || !out) return NQ_ERR_NULL;
+    if (s == out) return NQ_ERR_UNSUPPORTED;  // not an in-place permutation
+    permute_scale16_kernel<<<grid_for(n, kPackThreads), kPackThreads, 0, as_stream(stream)>>>(
+        static_cast<const uint16_t*>(s), static_cast<uint16_t*>(out), n, kind, inverse);
+    NQ_LAUNCH_CHECK();
+    return NQ_OK;
+}
+
+size_t nq_tiles_bytes(int64_t rows, int64_t cols) {
+    if (rows <= 0 || cols <= 0) return 0;
+    return (size_t)((rows + 15) / 16) * (size_t)((cols + 255) / 256) * 512;
+}
+
+int nq_rows_to_tiles(const int32_t* packed, void* tiles, int64_t rows, int64_t cols, int bit_order,
+                     nq_stream_t stream) {
+    if (rows <= 0 || cols <= 0) return NQ_ERR_SHAPE;
+    if (check_order(bit_order) != NQ_OK) return NQ_ERR_DTYPE;
+    if (!packed || !tiles) return NQ_ERR_NULL;
+    if (!aligned16(tiles)) return NQ_ERR_ALIGN;
+    const int64_t words = (cols + 31) / 32, rgs = (rows + 15) / 16, chunks = (cols + 255) / 256;
+    rows_to_tiles_kernel<<<grid_for(rgs * chunks * 32, kPackThreads), kPackThreads, 0, as_stream(stream)>>>(
+        reinterpret_cast<const uint32_t*>(packed), static_cast<uint4*>(tiles), rows, words, rgs, chunks, bit_order);
+    NQ_LAUNCH_CHECK();
+    return NQ_OK;
+}
+
+int nq_tiles_to_rows(const void* tiles, int32_t* packed, int64_t rows, int64_t cols, int bit_order,
+                     nq_stream_t stream) {
+    if (rows <= 0 || cols <= 0) return NQ_ERR_SHAPE;
+    if (check_order(bit_order) != NQ_OK) return NQ_ERR_DTYPE;
+    if (!packed || !tiles) return NQ_ERR_NULL;
+    if (!aligned16(tiles)) return NQ_ERR_ALIGN;
+    const int64_t words = (cols + 31) / 32, chunks = (cols + 255) / 256;
+    tiles_to_rows_kernel<<<grid_for(rows * words, kPackThreads), kPackThreads, 0, as_stream(stream)>>>(
+        static_cast<const uint4*>(tiles), reinterpret_cast<uint32_t*>(packed), rows, words, chunks, bit_order);
+    NQ_LAUNCH_CHECK();
+    return NQ_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,178 @@
+"""``torch.ops.binary_kernels.*`` — the reference's dispatcher operators, backed
+by ``libnanoquant_b200.so``.
+
+The three schemas are the reference's, verbatim
+(``src/nanoquant/kernel/pybind.cpp:83-105``); CUDA implementations call the C
+ABI with ``data_ptr()`` and the current stream, fake (Meta) implementations
+give shapes for tracing (``pybind.cpp:11-31``, ``cuda/gemm.cpp:100-134``).
+Nothing here computes on the CPU.
+
+Operand layouts accepted by ``nanoquant_dyn_forward``:
+
+* 2-D int32 ``[rows, cols/32]`` in ``half2`` bit order — what the reference's
+  ``binary_packer(..., method="half2")`` produces.  Converted once to the tile
+  layout of the kernel and cached on the tensor object.
+* 3-D int32 ``[rows/16, ceil(cols/256), 128]`` — the tile layout itself
+  (``nanoquant_b200.kernel.utils.pack_tiles``), used as is.
+
+Note the reference's argument naming: ``Ubits`` is the FIRST factor (module
+``V``, ``[R, N]``) and ``Vbits`` the second (module ``U``, ``[M, R]``).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import _lib
+from .kernel import utils as ku
+
+_DEFINED = False
+
+_SWEEP = {  # reference: cuda/gemv_kernel.cu:351-354
+    "n_th": (64, 128, 256),
+    "n_rpw": (1, 2, 4, 8),
+    "n_acc": (1, 2),
+    "n_pipe": (1, 2, 4, 8, 16),
+}
+
+_scratch = {}  # (device index, stream) -> zero-initialised uint8 tensor
+_SCRATCH_MIN = 4 << 20
+
+
+def _check_sweep(name: str, kind: str, value: int) -> None:
+    """The reference dispatches the tuning arguments through compile-time
+    lists and raises ``ValueError`` on a miss (``cuda/meta_utils.h:14-38``).  The
+    kernel here has no such knobs; the values are validated the same way and
+    otherwise ignored."""
+    choices = _SWEEP[kind]
+    if value not in choices:
+        raise ValueError(f"{name} should be one of [{', '.join(map(str, choices))}], but {value} was given")
+
+
+def scratch_for(device: torch.device, nbytes: int) -> torch.Tensor:
+    """Per (device, stream) scratch of the GEMV: zeroed once at allocation, as
+    the C ABI asks."""
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    buf = _scratch.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.zeros(max(nbytes, _SCRATCH_MIN), dtype=torch.uint8, device=device)
+        _scratch[key] = buf
+    return buf
+
+
+def _dtype_id(t: torch.Tensor) -> int:
+    if t.dtype == torch.float16:
+        return _lib.NQ_F16
+    if t.dtype == torch.bfloat16:
+        return _lib.NQ_BF16
+    raise RuntimeError("Support only Half or BFloat16")
+
+
+def _check_cuda_cont(t: torch.Tensor, name: str, dtype: torch.dtype, dtype_name: str) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor")
+    if not t.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous")
+    if t.dtype != dtype:
+        raise RuntimeError(f"{name} must be {dtype_name} tensor")
+
+
+def as_tiles(bits: torch.Tensor, cols: int) -> torch.Tensor:
+    """Tile-layout view of a factor given in either accepted layout."""
+    if bits.dim() == 3:
+        return bits
+    cached = getattr(bits, "_nq_tiles", None)
+    if cached is not None and cached[0] == bits._version:
+        return cached[1]
+    rows = bits.size(0)
+    if bits.size(1) != (cols + 31) // 32:
+        raise RuntimeError(f"packed factor of shape {tuple(bits.shape)} does not match {cols} columns")
+    tiles = ku.pack_tiles(bits, (rows, cols), method="half2")
+    bits._nq_tiles = (bits._version, tiles)
+    return tiles
+
+
+def gemv_forward(x: torch.Tensor, s_in: torch.Tensor, v_tiles: torch.Tensor, s_mid: Optional[torch.Tensor],
+                 u_tiles: torch.Tensor, s_out: torch.Tensor, R: int) -> torch.Tensor:
+    """Launch ``nq_gemv_fwd`` on the current stream; ``x`` is ``[T, N]``."""
+    T, N = x.shape
+    M = s_out.size(0)
+    y = torch.empty((T, M), dtype=x.dtype, device=x.device)
+    if T == 0:
+        return y
+    L = _lib.lib()
+    nbytes = L.nq_gemv_scratch_bytes(T, N, R, M)
+    scratch = scratch_for(x.device, nbytes)
+    with torch.cuda.device(x.device):
+        st = L.nq_gemv_fwd(x.data_ptr(), s_in.data_ptr(), v_tiles.data_ptr(),
+                           s_mid.data_ptr() if s_mid is not None else None,
+                           u_tiles.data_ptr(), s_out.data_ptr(), y.data_ptr(),
+                           scratch.data_ptr(), scratch.numel(), T, N, R, M, _dtype_id(x),
+                           torch.cuda.current_stream(x.device).cuda_stream)
+    _lib.check(st, "nq_gemv_fwd")
+    return y
+
+
+def _nanoquant_dyn_forward_cuda(x, scale_g, Ubits, scale_l, Vbits, scale_h,
+                                num_thread_stage1=128, num_thread_stage2=128,
+                                num_row_per_warp_stage1=2, num_row_per_warp_stage2=2,
+                                num_acc_stage1=4, num_acc_stage2=4,
+                                num_pipeline_stage1=2, num_pipeline_stage2=2):
+    # checks in the order of the reference host function (cuda/gemv_kernel.cu:317-338)
+    if x.dtype not in (torch.float16, torch.bfloat16):
+        raise RuntimeError("Support only Half or BFloat16")
+    name = "float16" if x.dtype == torch.float16 else "bfloat16"
+    _check_cuda_cont(x, "x", x.dtype, name)
+    _check_cuda_cont(scale_g, "scale_g", x.dtype, name)
+    _check_cuda_cont(scale_h, "scale_h", x.dtype, name)
+    _check_cuda_cont(Ubits, "Ubits", torch.int32, "int32")
+    _check_cuda_cont(Vbits, "Vbits", torch.int32, "int32")
+    N = x.size(-1)
+    M = scale_h.size(0)
+    if Ubits.dim() == 3:
+        R = scale_l.size(0) if scale_l is not None else Ubits.size(0) * 16
+    else:
+        R = Ubits.size(0)
+    if scale_l is not None:
+        _check_cuda_cont(scale_l, "(*scale_l)", x.dtype, name)
+        if scale_l.size(0) != R:
+            raise RuntimeError("scale_l size mismatch")
+    if scale_g.size(0) != N:
+        raise RuntimeError("scale_g size mismatch")
+    _check_sweep("n_th1", "n_th", num_thread_stage1)
+    _check_sweep("n_rpw1", "n_rpw", num_row_per_warp_stage1)
+    _check_sweep("n_acc1", "n_acc", num_acc_stage1)
+    _check_sweep("n_pipe1", "n_pipe", num_pipeline_stage1)
+    _check_sweep("n_th2", "n_th", num_thread_stage2)
+    _check_sweep("n_rpw2", "n_rpw", num_row_per_warp_stage2)
+    _check_sweep("n_acc2", "n_acc", num_acc_stage2)
+    _check_sweep("n_pipe2", "n_pipe", num_pipeline_stage2)
+    v_tiles = as_tiles(Ubits, N)
+    u_tiles = as_tiles(Vbits, R)
+    x2 = x.view(1, N) if x.dim() == 1 else x
+    y = gemv_forward(x2, scale_g, v_tiles, scale_l, u_tiles, scale_h, R)
+    return y.squeeze(0) if x.dim() == 1 else y
+
+
+def _nanoquant_dyn_forward_fake(x, scale_g, Ubits, scale_l, Vbits, scale_h, *args, **kwargs):
+    shape = list(x.shape)
+    shape[-1] = scale_h.size(0)
+    return x.new_empty(shape)
+
+
+def define_ops() -> None:
+    """Define and register the operators once per process."""
+    global _DEFINED
+    if _DEFINED:
+        return
+    torch.library.define(
+        "binary_kernels::nanoquant_dyn_forward",
+        "(Tensor x, Tensor scale_g, Tensor Ubits, Tensor? scale_l, Tensor Vbits, Tensor scale_h, "
+        "int num_thread_stage1=128, int num_thread_stage2=128, int num_row_per_warp_stage1=2, "
+        "int num_row_per_warp_stage2=2, int num_acc_stage1=4, int num_acc_stage2=4, "
+        "int num_pipeline_stage1=2, int num_pipeline_stage2=2) -> Tensor")
+    torch.library.impl("binary_kernels::nanoquant_dyn_forward", "CUDA")(_nanoquant_dyn_forward_cuda)
+    torch.library.register_fake("binary_kernels::nanoquant_dyn_forward")(_nanoquant_dyn_forward_fake)
+    _DEFINED = True
