@@ -1,0 +1,381 @@
+#!/usr/bin/env python
+"""Benchmark of the NanoQuant quantised-linear hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--batch T] [--impl reference]
+
+Workload (``config.workload``): the quantised linears of a Qwen3-8B-shaped decoder at 0.8 bpw —
+36 layers x {q, k, v, o, gate, up, down}, ranks from the reference's rank formula, random ±1
+factors and scales ``(U[0,1)+0.5)*0.01``, synthetic N(0,1) activations — executed for one decode
+step of ``--batch`` tokens (default 1).  A *step* is one pass over all 252 linears, i.e. the
+hot-path work of one generated token per sequence.  Per layer the launches are q/k/v (one group),
+o, gate/up (one group), down: 4 launches of the group GEMV kernel, 144 per step, captured in a
+CUDA graph.  The packed factors (690 MB) exceed L2, so every step streams them from HBM.
+
+* ``value``      tokens/s of the device-resident step (CUDA events around K graph replays).
+* ``e2e``        the same through host buffers: per step the activations are copied from pinned
+                 host memory, the step runs, and the last projection's output is copied back.
+* ``roofline``   algorithmic bytes of a step / step time against the measured HBM copy peak.
+* ``cpu_baseline`` the reference's PyTorch dequantise-then-matmul path (torch CPU, bf16 as the
+                 reference module keeps its parameters) timed on this host on a bounded sample
+                 (one decoder layer), extrapolated to the 36 layers.
+
+``--impl reference`` times only that CPU path and prints the same JSON line with
+``"impl": "reference"``.  With N > 1 (launched by torchrun) every rank runs an independent replica
+of the step (data-parallel decode streams, no data-path collective): weak scaling.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+HIDDEN, INTER, LAYERS, KV = 4096, 12288, 36, 1024
+BPW = 0.8
+
+
+def rank_for_bits(in_f, out_f, bits):
+    """Rank of a layer at a bit budget: floor((bits*in*out/(in+out) - 16) / 32) * 32, the
+    reference's two-scale formula (src/nanoquant/utils/utils.py:132-159)."""
+    r = int(in_f * out_f * bits / (in_f + out_f) - 16) // 32 * 32
+    return max(32, min(r, in_f, out_f))
+
+
+def layer_linears():
+    """(name, N, R, M, input buffer, launch group) of the 7 quantised linears of a layer."""
+    spec = [("q", HIDDEN, HIDDEN, "h", 0), ("k", HIDDEN, KV, "h", 0), ("v", HIDDEN, KV, "h", 0),
+            ("o", HIDDEN, HIDDEN, "h", 1), ("gate", HIDDEN, INTER, "h", 2), ("up", HIDDEN, INTER, "h", 2),
+            ("down", INTER, HIDDEN, "i", 3)]
+    return [(n, N, rank_for_bits(N, M, BPW), M, src, grp) for (n, N, M, src, grp) in spec]
+
+
+def algorithmic_bytes(N, R, M, T, e=2):
+    """Packed factors + scales + activations in and out; the rank-R intermediate stays on chip / in L2."""
+    return R * (N + M) // 8 + e * (N + R + M) + e * T * (N + M)
+
+
+# --------------------------------------------------------------------------------------------
+# clocks sampling
+# --------------------------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            p = [x.strip() for x in ln.split(",")]
+            if len(p) < 7:
+                continue
+            try:
+                sm.append(float(p[0]))
+                mx = float(p[1])
+            except ValueError:
+                continue
+            for n, v in zip(names, p[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------------------------
+# CPU reference arm
+# --------------------------------------------------------------------------------------------
+class CpuLayer:
+    """One decoder layer (7 quantised linears) of the reference's PyTorch dequantise-then-matmul
+    path on the host cores: dense +-1 matrices in bf16, as the reference module keeps them
+    (src/nanoquant/modules/linear.py:69-76,90), through the oracle's restatement of its forward."""
+
+    def __init__(self, T):
+        import torch
+        from oracle import nanoquant_oracle as oc
+        self.torch, self.oc = torch, oc
+        self.cores = os.cpu_count() or 1
+        torch.set_num_threads(self.cores)
+        g = torch.Generator().manual_seed(0)
+        dt = torch.bfloat16
+        self.layers = []
+        for (_, N, R, M, _, _) in layer_linears():
+            V = (torch.randint(0, 2, (R, N), generator=g) * 2 - 1).to(dt)
+            U = (torch.randint(0, 2, (M, R), generator=g) * 2 - 1).to(dt)
+            sc = lambda n: ((torch.rand(n, generator=g) + 0.5) * 0.01).to(dt)
+            self.layers.append((torch.randn(T, N, generator=g).to(dt), V, U, sc(N), sc(R), sc(M)))
+
+    def run_once(self):
+        with self.torch.no_grad():
+            t0 = time.perf_counter()
+            for (x, V, U, a, b, c) in self.layers:
+                self.oc.torch_cpu_forward(x, V, U, a, b, c)
+            return time.perf_counter() - t0
+
+    def timed(self, budget_s, min_reps=5, max_reps=2000):
+        for _ in range(3):
+            self.run_once()
+        times, t_end = [], time.perf_counter() + budget_s
+        while len(times) < min_reps or (time.perf_counter() < t_end and len(times) < max_reps):
+            times.append(self.run_once())
+        return statistics.median(times), len(times)
+
+
+def cpu_sample_text(T, reps):
+    return (f"1 of {LAYERS} decoder layers (7 linears, dense +-1 bf16 matmuls, T={T}), "
+            f"median of {reps} runs, x{LAYERS} layers")
+
+
+def reference_arm(args):
+    """Each step is one pass over the bounded sample (one decoder layer); the step time reported is
+    that pass scaled to the 36 layers of the workload."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    T = args.batch
+    cpu = CpuLayer(T)
+    for _ in range(max(args.warmup, 3)):
+        cpu.run_once()
+    times, t_stop = [], time.perf_counter() + 150.0
+    for _ in range(args.steps):
+        times.append(cpu.run_once())
+        if time.perf_counter() > t_stop:
+            break
+    step_s = statistics.median(times) * LAYERS
+    value = T / step_s
+    out = {
+        "impl": "reference", "metric": "decode tok/s (quantised linears of one decode step)", "value": value,
+        "unit": "tokens/s", "n_gpus": args.gpus, "steps": len(times), "warmup": max(args.warmup, 3),
+        "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": workload_config(T),
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cpu.cores, "kind": "port",
+                         "sample": cpu_sample_text(T, len(times))},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(out), flush=True)
+
+
+def workload_config(T):
+    return {"workload": f"qwen3-8b-shaped decoder, all 252 quantised linears at {BPW} bpw, decode batch {T}",
+            "hidden": HIDDEN, "intermediate": INTER, "layers": LAYERS, "batch": T,
+            "ranks": {n: r for (n, _, r, _, _, _) in layer_linears()},
+            "l2": "packed factors (690 MB per step) exceed L2; no flush needed"}
+
+
+# --------------------------------------------------------------------------------------------
+# GPU arm
+# --------------------------------------------------------------------------------------------
+class Step:
+    """Device-resident weights of the 36 layers and the launch list of one decode step."""
+
+    def __init__(self, T, dtype, device):
+        import torch
+        from nanoquant_b200 import _lib
+        self.torch, self.lib, self.L = torch, _lib, _lib.lib()
+        self.T, self.dtype, self.device = T, dtype, device
+        self.dt_id = _lib.NQ_BF16 if dtype == torch.bfloat16 else _lib.NQ_F16
+        g = torch.Generator(device=device).manual_seed(0)
+        rnd_bits = lambda rows, cols: torch.randint(-2**31, 2**31 - 1, ((rows + 15) // 16, (cols + 255) // 256, 128),
+                                                    generator=g, device=device, dtype=torch.int32)
+        scale = lambda n: ((torch.rand(n, generator=g, device=device) + 0.5) * 0.01).to(dtype)
+        self.x = {"h": torch.randn(T, HIDDEN, generator=g, device=device).to(dtype),
+                  "i": torch.randn(T, INTER, generator=g, device=device).to(dtype)}
+        self.keep, self.launches, self.bytes = [], [], 0
+        scratch_bytes = 0
+        for _ in range(LAYERS):
+            groups = {}
+            for (name, N, R, M, src, grp) in layer_linears():
+                t = dict(v=rnd_bits(R, N), u=rnd_bits(M, R), s_in=scale(N), s_mid=scale(R), s_out=scale(M),
+                         y=torch.empty(T, M, device=device, dtype=dtype))
+                self.keep.append(t)
+                d = _lib.LinearDesc(self.x[src].data_ptr(), t["s_in"].data_ptr(), t["v"].data_ptr(),
+                                    t["s_mid"].data_ptr(), t["u"].data_ptr(), t["s_out"].data_ptr(),
+                                    t["y"].data_ptr(), N, R, M, N, M)
+                groups.setdefault(grp, []).append(d)
+                self.bytes += algorithmic_bytes(N, R, M, T)
+            for grp in sorted(groups):
+                arr = (_lib.LinearDesc * len(groups[grp]))(*groups[grp])
+                scratch_bytes = max(scratch_bytes, self.L.nq_gemv_group_scratch_bytes(arr, len(arr), T))
+                self.launches.append(arr)
+        self.last_y = self.keep[-1]["y"]
+        self.scratch = torch.zeros(scratch_bytes, dtype=torch.uint8, device=device)
+        self.kernels_per_step = len(self.launches) * ((T + 3) // 4)
+        self.graph = None
+
+    def run(self):
+        st = self.torch.cuda.current_stream(self.device).cuda_stream
+        for arr in self.launches:
+            rc = self.L.nq_gemv_group_fwd(arr, len(arr), self.T, self.dt_id, self.scratch.data_ptr(),
+                                          self.scratch.numel(), st)
+            self.lib.check(rc, "nq_gemv_group_fwd")
+
+    def capture(self):
+        torch = self.torch
+        s = torch.cuda.Stream(self.device)
+        s.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(s):
+            self.run()
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph, stream=s):
+                self.run()
+        torch.cuda.current_stream(self.device).wait_stream(s)
+        torch.cuda.synchronize(self.device)
+
+    def status(self):
+        return self.L.nq_scratch_status(self.scratch.data_ptr(), self.torch.cuda.current_stream(self.device).cuda_stream)
+
+
+def gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the hot path has no CPU fallback (use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    T = args.batch
+    dtype = torch.bfloat16
+    step = Step(T, dtype, device)
+    step.capture()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    sampler = ClockSampler(local)
+    for _ in range(max(args.warmup, 3)):
+        step.graph.replay()
+    barrier()
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step.graph.replay()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    # keep the clocks sample meaningful for short runs: load for at least ~1 s in total
+    t_extra = time.perf_counter() + max(0.0, 1.0 - ms * 1e-3)
+    while time.perf_counter() < t_extra:
+        step.graph.replay()
+        torch.cuda.synchronize(device)
+    clocks = sampler.stop() if rank == 0 else None
+    if step.status() != 0:
+        raise SystemExit("bench.py: a device-wide wait timed out inside the GEMV kernel")
+
+    # end to end through host buffers
+    hx = {k: v.cpu().pin_memory() for k, v in step.x.items()}
+    hy = torch.empty_like(step.last_y, device="cpu").pin_memory()
+    def e2e_step():
+        for k in hx:
+            step.x[k].copy_(hx[k], non_blocking=True)
+        step.graph.replay()
+        hy.copy_(step.last_y, non_blocking=True)
+        torch.cuda.current_stream(device).synchronize()
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    f1.record()
+    barrier()
+    e2e_ms = f0.elapsed_time(f1)
+
+    times = torch.tensor([ms, e2e_ms], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = times.tolist()
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except (OSError, ValueError):
+        pass
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    peak_src = "measured (MEASURED_PEAKS.json hbm_gbs)" if "hbm_gbs" in peaks else "fallback 6650 GB/s"
+    step_s = ms * 1e-3 / args.steps
+    achieved = step.bytes / step_s / 1e9
+    launch_us = step_s / step.kernels_per_step * 1e6
+    out = {
+        "metric": "decode tok/s (quantised linears of one decode step)", "value": world * T / step_s,
+        "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "s8 mma / s32 accumulate on 16-bit fixed point; bf16 in/out", "data": "synthetic",
+        "config": dict(workload_config(T), parallelism=("single gpu" if world == 1 else f"{world} independent replicas")),
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "kernel": "gemv_group_kernel",
+                     "bytes_per_launch": step.bytes / step.kernels_per_step, "us_per_launch": launch_us,
+                     "peak_source": peak_src},
+        "e2e": {"value": world * T / (e2e_ms * 1e-3 / args.steps), "unit": "tokens/s",
+                "h2d_bytes_per_step": sum(v.numel() * v.element_size() for v in hx.values()),
+                "d2h_bytes_per_step": hy.numel() * hy.element_size()},
+        "gpu_launches": step.kernels_per_step * args.steps,
+        "clocks": clocks,
+    }
+    if not args.no_cpu_baseline:
+        cpu = CpuLayer(T)
+        t_layer, reps = cpu.timed(budget_s=12.0)
+        out["cpu_baseline"] = {"value": T / (t_layer * LAYERS), "unit": "tokens/s", "cores": cpu.cores,
+                               "kind": "port", "sample": cpu_sample_text(T, reps)}
+    print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--batch", type=int, default=1, help="tokens per decode step (1, 4 or 16 in the workload)")
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+    else:
+        gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

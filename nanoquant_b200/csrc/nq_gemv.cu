@@ -34,16 +34,41 @@
 
 namespace nq {
 
-constexpr int kGemvThreads = 256;
+#ifndef NQ_GEMV_THREADS
+#define NQ_GEMV_THREADS 512
+#endif
+#ifndef NQ_GEMV_STAGES
+#define NQ_GEMV_STAGES 4
+#endif
+constexpr int kGemvThreads = NQ_GEMV_THREADS;
 constexpr int kGemvWarps = kGemvThreads / 32;
 constexpr int kMaxJobs = 4;         // linears per launch
 constexpr int kMaxTok = 4;          // tokens per launch (2 int8 terms each -> 8 MMA columns)
 constexpr int kQMax = 32639;        // 127*256 + 127: hi and lo both fit a signed byte
-constexpr int kPrefetch = 6;        // tile pairs in flight per lane
+constexpr int kStages = NQ_GEMV_STAGES;          // 1 KB weight slots in flight per warp
+constexpr size_t kRedBytes = 384;   // per-warp maxima (kGemvWarps * 4 floats) + 4 inverse scales
+constexpr size_t kFixedBytes = 512;
+constexpr size_t kRingBytes = (size_t)kGemvWarps * kStages * 1024;
 constexpr unsigned kSpinLimit = 4000000u;
 constexpr size_t kHeaderBytes = 256;
 
 enum : int { KIND_F16 = 0, KIND_BF16 = 1, KIND_F32 = 2 };
+
+#ifdef NQ_GEMV_TRACE  // development aid: per-CTA (id, timestamp) records of the phase steps
+__device__ unsigned long long g_trace[148 * 64];
+__device__ int g_trace_n[148];
+__device__ __forceinline__ void trace_mark(int id) {
+    if (threadIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        const int n = g_trace_n[blockIdx.x];
+        if (n < 64) { g_trace[blockIdx.x * 64 + n] = (t << 8) | (unsigned)id; g_trace_n[blockIdx.x] = n + 1; }
+    }
+}
+#define NQ_TRACE(id) trace_mark(id)
+#else
+#define NQ_TRACE(id) ((void)0)
+#endif
 
 struct Job {
     const uint4* tiles;   // [row_groups][chunks][32]
@@ -56,6 +81,7 @@ struct Job {
     int chunks;           // ceil(K / 256)
     int items;            // ceil(rows / 32)
     int in_kind, out_kind;
+    int vec;              // rows of `in` / `pre` are 16-byte aligned and K % 8 == 0
 };
 
 struct Phase {
@@ -80,8 +106,7 @@ __device__ __forceinline__ float load_as_float(const void* p, long long i, int k
 
 __device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                        uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
@@ -94,23 +119,26 @@ __device__ __forceinline__ uint4 load_tile(const uint4* p) {
     return v;
 }
 
-// Bounded device-wide barrier.  Returns false when the wait expired.
+// Bounded device-wide barrier on {count, generation} words.  Returns false when the
+// wait expired (a status word is set and the caller returns).  One thread per CTA
+// arrives with a release and polls with acquires; the CTA barrier before and after
+// extends the ordering to every thread of the CTA.
 __device__ bool grid_barrier(unsigned* header, unsigned nblocks) {
     __shared__ int ok;
     __syncthreads();
     if (threadIdx.x == 0) {
         ok = 1;
-        volatile unsigned* gen = header + 1;
-        const unsigned my_gen = *gen;
-        __threadfence();
-        const unsigned old = atomicAdd(header, 1u);
+        unsigned my_gen, old;
+        asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(my_gen) : "l"(header + 1) : "memory");
+        asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(old) : "l"(header) : "memory");
         if (old == nblocks - 1) {
-            atomicExch(header, 0u);
-            __threadfence();
-            atomicAdd(header + 1, 1u);
+            asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(header), "r"(0u) : "memory");
+            asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(header + 1) : "memory");
         } else {
-            unsigned spins = 0;
-            while (*gen == my_gen) {
+            unsigned spins = 0, cur;
+            while (true) {
+                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(cur) : "l"(header + 1) : "memory");
+                if (cur != my_gen) break;
                 if (++spins > kSpinLimit) {
                     atomicExch(header + 2, (unsigned)(-NQ_ERR_TIMEOUT));
                     ok = 0;
@@ -118,107 +146,206 @@ __device__ bool grid_barrier(unsigned* header, unsigned nblocks) {
                 }
             }
         }
-        __threadfence();
     }
     __syncthreads();
     return ok != 0;
+}
+
+// Eight consecutive elements of a vector as floats (one or two 128-bit loads).
+template <int KIND>
+__device__ __forceinline__ void load8(const void* base, long long i, float (&v)[8]) {
+    if (KIND == KIND_F32) {
+        const float4 a = __ldcg(reinterpret_cast<const float4*>(static_cast<const float*>(base) + i));
+        const float4 b = __ldcg(reinterpret_cast<const float4*>(static_cast<const float*>(base) + i) + 1);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    } else {
+        const uint4 u = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(base) + i);
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            if (KIND == KIND_F16) {
+                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[e]));
+                v[2 * e] = f.x; v[2 * e + 1] = f.y;
+            } else {  // bf16 -> fp32 is a 16-bit shift
+                v[2 * e] = __uint_as_float(w[e] << 16);
+                v[2 * e + 1] = __uint_as_float(w[e] & 0xFFFF0000u);
+            }
+        }
+    }
 }
 
 // Quantise the input vectors of a job into shared memory.
 //   xq: 2*T int8 vectors (row 2*tok = hi term, 2*tok+1 = lo term), `stride` bytes apart,
 //       in the k order the MMA B fragments expect (see below); columns K..Kpad are zero.
 //   sumx[tok]: sum of the 16-bit values, delta[tok]: value of one unit.
-__device__ void quantise_input(const Job& jb, int T, int scale_kind, int8_t* xq, int stride,
-                               float* red, int* sumx, float* delta) {
+// Byte position inside a chunk of 256 columns: 32*j + 8*q + 4*h + b for column
+// 32*j + 16*h + 4*q + b, so that lane (g, q) fetches its two B registers
+// {k = 4q.., k = 16+4q..} of mask j with one 64-bit load.
+// The code is kept as small loops on purpose: it runs once per phase, where
+// instruction fetch, not arithmetic, sets the pace.
+//
+// Vector path: rows of `in` / `pre` 16-byte aligned, K % 8 == 0; eight columns per thread and step.
+template <int IN_KIND>
+__device__ __noinline__ void quantise_vec(const Job& jb, int T, int8_t* xq, int stride, float* red,
+                                          int* sumx, float* delta) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int K = jb.K, Kpad = jb.chunks * 256;
+    constexpr bool kHasPre = (IN_KIND != KIND_F32);
     // pass 1: per-token max |in * pre|
-    float mx[kMaxTok] = {0.f, 0.f, 0.f, 0.f};
-    for (int k = tid; k < K; k += kGemvThreads) {
-        const float s = jb.pre ? load_as_float(jb.pre, k, scale_kind) : 1.f;
-#pragma unroll
-        for (int t = 0; t < kMaxTok; ++t)
-            if (t < T) mx[t] = fmaxf(mx[t], fabsf(load_as_float(jb.in, t * jb.ld_in + k, jb.in_kind) * s));
-    }
-#pragma unroll
-    for (int t = 0; t < kMaxTok; ++t) {
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) mx[t] = fmaxf(mx[t], __shfl_xor_sync(0xffffffffu, mx[t], o));
-        if (lane == 0) red[warp * kMaxTok + t] = mx[t];
-    }
-    if (tid < kMaxTok) sumx[tid] = 0;
-    __syncthreads();
-    float inv[kMaxTok];
-#pragma unroll
-    for (int t = 0; t < kMaxTok; ++t) {
+#pragma unroll 1
+    for (int t = 0; t < T; ++t) {
         float m = 0.f;
-        for (int w = 0; w < kGemvWarps; ++w) m = fmaxf(m, red[w * kMaxTok + t]);
+#pragma unroll 1
+        for (int k8 = tid * 8; k8 < K; k8 += kGemvThreads * 8) {
+            float v[8], s[8];
+            load8<IN_KIND>(jb.in, t * jb.ld_in + k8, v);
+            if (kHasPre) load8<IN_KIND>(jb.pre, k8, s);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) m = fmaxf(m, fabsf(kHasPre ? v[e] * s[e] : v[e]));
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if (lane == 0) red[warp * kMaxTok + t] = m;
+    }
+    __syncthreads();
+    if (tid < T) {
+        float m = 0.f;
+        for (int w = 0; w < kGemvWarps; ++w) m = fmaxf(m, red[w * kMaxTok + tid]);
         // a non-finite or zero maximum quantises everything to zero
         const bool good = (m > 0.f) && (m < 3.0e38f);
-        inv[t] = good ? (float)kQMax / m : 0.f;
-        if (tid == 0) delta[t] = good ? m / (float)kQMax : 0.f;
+        red[kGemvWarps * kMaxTok + tid] = good ? (float)kQMax / m : 0.f;
+        delta[tid] = good ? m / (float)kQMax : 0.f;
+        sumx[tid] = 0;
     }
-    // pass 2: four consecutive k per thread -> one 32-bit word of the hi and of the lo vector.
-    // Byte position inside a chunk of 256: 32*j + 8*q + 4*h + b for k = 32*j + 16*h + 4*q + b,
-    // so that lane (g, q) fetches its two B registers {k=4q.., k=16+4q..} with one 64-bit load.
-    int acc[kMaxTok] = {0, 0, 0, 0};
-    for (int k4 = tid * 4; k4 < Kpad; k4 += kGemvThreads * 4) {
-        const int kin = k4 & 255, j = kin >> 5, h = (kin >> 4) & 1, q = (kin >> 2) & 3;
-        const int pos = (k4 & ~255) + 32 * j + 8 * q + 4 * h;
-        float s[4];
+    __syncthreads();
+    // pass 2: |p * inv| <= kQMax + 2^-8 by construction (same products as in pass 1), no clamp needed
+#pragma unroll 1
+    for (int t = 0; t < T; ++t) {
+        const float inv = red[kGemvWarps * kMaxTok + t];
+        int8_t* rh = xq + (2 * t) * stride;
+        int8_t* rl = rh + stride;
+        int acc = 0;
+#pragma unroll 1
+        for (int k8 = tid * 8; k8 < Kpad; k8 += kGemvThreads * 8) {
+            int X[8];
+            if (k8 < K) {
+                float v[8], s[8];
+                load8<IN_KIND>(jb.in, t * jb.ld_in + k8, v);
+                if (kHasPre) load8<IN_KIND>(jb.pre, k8, s);
 #pragma unroll
-        for (int b = 0; b < 4; ++b)
-            s[b] = (k4 + b < K) ? (jb.pre ? load_as_float(jb.pre, k4 + b, scale_kind) : 1.f) : 0.f;
-#pragma unroll
-        for (int t = 0; t < kMaxTok; ++t) {
-            if (t < T) {
-                uint32_t hi = 0, lo = 0;
-#pragma unroll
-                for (int b = 0; b < 4; ++b) {
-                    int X = 0;
-                    if (k4 + b < K) {
-                        const float v = load_as_float(jb.in, t * jb.ld_in + k4 + b, jb.in_kind) * s[b];
-                        X = __float2int_rn(fminf(fmaxf(v * inv[t], -(float)kQMax), (float)kQMax));
-                    }
-                    acc[t] += X;
-                    const int l = (int)(int8_t)(X & 0xFF);   // signed low byte
-                    const int hh = (X - l) >> 8;             // exact, in [-127, 127]
-                    lo |= (uint32_t)(l & 0xFF) << (8 * b);
-                    hi |= (uint32_t)(hh & 0xFF) << (8 * b);
+                for (int e = 0; e < 8; ++e) {
+                    X[e] = __float2int_rn((kHasPre ? v[e] * s[e] : v[e]) * inv);
+                    acc += X[e];
                 }
-                *reinterpret_cast<uint32_t*>(xq + (2 * t) * stride + pos) = hi;
-                *reinterpret_cast<uint32_t*>(xq + (2 * t + 1) * stride + pos) = lo;
+            } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) X[e] = 0;
             }
-        }
-    }
+            // X = 256 * hi + lo with lo the signed low byte: lo = byte 0 of X, hi = byte 1 of X + 128
+            uint32_t lo[2], hi[2];
 #pragma unroll
-    for (int t = 0; t < kMaxTok; ++t) {
-        if (t < T) {
-            int a = acc[t];
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
-            if (lane == 0 && a != 0) atomicAdd(&sumx[t], a);
+            for (int w = 0; w < 2; ++w) {
+                const uint32_t x0 = X[4 * w], x1 = X[4 * w + 1], x2 = X[4 * w + 2], x3 = X[4 * w + 3];
+                lo[w] = __byte_perm(__byte_perm(x0, x1, 0x0040), __byte_perm(x2, x3, 0x0040), 0x5410);
+                hi[w] = __byte_perm(__byte_perm(x0 + 128u, x1 + 128u, 0x0051),
+                                    __byte_perm(x2 + 128u, x3 + 128u, 0x0051), 0x5410);
+            }
+            const int kin = k8 & 255;  // j = kin >> 5, h = (kin >> 4) & 1, q = (kin >> 2) & 3 (0 or 2)
+            const int pos = (k8 & ~255) + (kin & 0xE0) + 2 * (kin & 8) + ((kin & 16) >> 2);
+            *reinterpret_cast<uint32_t*>(rh + pos) = hi[0];
+            *reinterpret_cast<uint32_t*>(rh + pos + 8) = hi[1];
+            *reinterpret_cast<uint32_t*>(rl + pos) = lo[0];
+            *reinterpret_cast<uint32_t*>(rl + pos + 8) = lo[1];
         }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (lane == 0 && acc != 0) atomicAdd(&sumx[t], acc);
     }
     __syncthreads();
 }
 
-struct TilePair {
-    uint4 a, b;  // row group 2*item and 2*item + 1
-};
+// Scalar path for unaligned or ragged inputs (any K, any alignment).
+__device__ __noinline__ void quantise_scalar(const Job& jb, int T, int scale_kind, int8_t* xq, int stride,
+                                             float* red, int* sumx, float* delta) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int K = jb.K, Kpad = jb.chunks * 256;
+#pragma unroll 1
+    for (int t = 0; t < T; ++t) {
+        float m = 0.f;
+        for (int k = tid; k < K; k += kGemvThreads) {
+            const float s = jb.pre ? load_as_float(jb.pre, k, scale_kind) : 1.f;
+            m = fmaxf(m, fabsf(load_as_float(jb.in, t * jb.ld_in + k, jb.in_kind) * s));
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if (lane == 0) red[warp * kMaxTok + t] = m;
+    }
+    __syncthreads();
+    if (tid < T) {
+        float m = 0.f;
+        for (int w = 0; w < kGemvWarps; ++w) m = fmaxf(m, red[w * kMaxTok + tid]);
+        const bool good = (m > 0.f) && (m < 3.0e38f);
+        red[kGemvWarps * kMaxTok + tid] = good ? (float)kQMax / m : 0.f;
+        delta[tid] = good ? m / (float)kQMax : 0.f;
+        sumx[tid] = 0;
+    }
+    __syncthreads();
+#pragma unroll 1
+    for (int t = 0; t < T; ++t) {
+        const float inv = red[kGemvWarps * kMaxTok + t];
+        int acc = 0;
+        for (int k = tid; k < Kpad; k += kGemvThreads) {
+            int X = 0;
+            if (k < K) {
+                const float s = jb.pre ? load_as_float(jb.pre, k, scale_kind) : 1.f;
+                X = __float2int_rn(load_as_float(jb.in, t * jb.ld_in + k, jb.in_kind) * s * inv);
+            }
+            acc += X;
+            const int kin = k & 255;
+            const int pos = (k & ~255) + (kin & 0xE0) + 2 * (kin & 12) + ((kin & 16) >> 2) + (kin & 3);
+            xq[(2 * t) * stride + pos] = (int8_t)((X + 128) >> 8);
+            xq[(2 * t + 1) * stride + pos] = (int8_t)(X & 0xFF);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (lane == 0 && acc != 0) atomicAdd(&sumx[t], acc);
+    }
+    __syncthreads();
+}
 
-// One phase: every CTA walks the jobs; inside a job it owns the row tiles
-// blockIdx.x, blockIdx.x + gridDim.x, ... and its warps split the K chunks.
-__device__ void run_phase(const Phase& ph, const GemvParams& P, unsigned char* smem) {
+__device__ __forceinline__ void quantise_input(const Job& jb, int T, int scale_kind, int8_t* xq, int stride,
+                                               float* red, int* sumx, float* delta) {
+    if (!jb.vec) quantise_scalar(jb, T, scale_kind, xq, stride, red, sumx, delta);
+    else if (jb.in_kind == KIND_F32) quantise_vec<KIND_F32>(jb, T, xq, stride, red, sumx, delta);
+    else if (jb.in_kind == KIND_F16) quantise_vec<KIND_F16>(jb, T, xq, stride, red, sumx, delta);
+    else quantise_vec<KIND_BF16>(jb, T, xq, stride, red, sumx, delta);
+}
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// One phase: every CTA walks the jobs; inside a job it owns the row tiles (32 rows)
+// blockIdx.x, blockIdx.x + gridDim.x, ... and its warps split the K chunks of those
+// tiles.  Each warp streams its (tile, chunk) pairs - 1 KB of packed weights each -
+// through a private ring of kStages shared-memory slots filled with cp.async, so the
+// loop body exists once and stays small enough for the instruction cache.
+__device__ __noinline__ void run_phase(const Phase& ph, const GemvParams& P, unsigned char* smem) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, q = lane & 3;
     // shared memory carve-up
-    float* red = reinterpret_cast<float*>(smem);                    // [warps][4]
-    int* sumx = reinterpret_cast<int*>(smem + 256);                 // [4]
-    float* delta = reinterpret_cast<float*>(smem + 256 + 16);       // [4]
-    int* s1 = reinterpret_cast<int*>(smem + 512);                   // [max_items][4][32]
-    int8_t* xq = reinterpret_cast<int8_t*>(smem + 512 + (size_t)P.max_items * 512);
+    float* red = reinterpret_cast<float*>(smem);                          // [warps][4]
+    int* sumx = reinterpret_cast<int*>(smem + kRedBytes);                 // [4]
+    float* delta = reinterpret_cast<float*>(smem + kRedBytes + 16);       // [4]
+    uint4* ring = reinterpret_cast<uint4*>(smem + kFixedBytes) + warp * (kStages * 64);  // [stage][2][32]
+    int* s1 = reinterpret_cast<int*>(smem + kFixedBytes + kRingBytes);    // [max_items][4][32]
+    int8_t* xq = reinterpret_cast<int8_t*>(smem + kFixedBytes + kRingBytes + (size_t)P.max_items * 512);
 
+#pragma unroll 1
     for (int ji = 0; ji < ph.njobs; ++ji) {
         const Job& jb = ph.job[ji];
         const int my_items = ((int)blockIdx.x < jb.items)
@@ -226,85 +353,85 @@ __device__ void run_phase(const Phase& ph, const GemvParams& P, unsigned char* s
         if (my_items == 0) continue;  // uniform per CTA
         const int chunks = jb.chunks;
         const int row_groups = (jb.rows + 15) >> 4;
+        // The CTA's (tile, chunk) pairs, tile-major, are split into one contiguous range per
+        // warp: a warp then streams consecutive memory and folds its partial sums into shared
+        // memory only when it leaves a row tile (at most twice more often than it has tiles).
         const int npairs = my_items * chunks;
-        const int my_pairs = (warp < npairs) ? (npairs - 1 - warp) / kGemvWarps + 1 : 0;
+        const int p_begin = (int)((long long)npairs * warp / kGemvWarps);
+        const int p_end = (int)((long long)npairs * (warp + 1) / kGemvWarps);
+        const int my_pairs = p_end - p_begin;
 
-        auto tile_ptr = [&](int p, int second) -> const uint4* {
-            const int il = p / chunks, c = p - il * chunks;
-            int rg = 2 * ((int)blockIdx.x + il * (int)gridDim.x) + second;
-            if (rg >= row_groups) rg = row_groups - 1;  // odd tail: re-read, result discarded
-            return jb.tiles + ((size_t)rg * chunks + c) * 32 + lane;
-        };
-        // issue the first weight loads before the input is prepared: they do not depend on it
-        TilePair buf[kPrefetch];
-#pragma unroll
-        for (int d = 0; d < kPrefetch; ++d) {
-            if (d < my_pairs) {
-                const int p = warp + d * kGemvWarps;
-                buf[d].a = load_tile(tile_ptr(p, 0));
-                buf[d].b = load_tile(tile_ptr(p, 1));
+        // load stream state: (item, chunk) of the next pair to fetch
+        int l_il = p_begin / chunks, l_c = p_begin - l_il * chunks, l_n = 0;
+        auto issue_load = [&]() {
+            if (l_n < my_pairs) {
+                const int rg = 2 * ((int)blockIdx.x + l_il * (int)gridDim.x);
+                const int rgb = (rg + 1 < row_groups) ? rg + 1 : rg;  // odd tail: re-read, result discarded
+                uint4* dst = ring + (l_n % kStages) * 64 + lane;
+                cp_async16(dst, jb.tiles + ((size_t)rg * chunks + l_c) * 32 + lane);
+                cp_async16(dst + 32, jb.tiles + ((size_t)rgb * chunks + l_c) * 32 + lane);
+                if (++l_c == chunks) { l_c = 0; ++l_il; }
+                ++l_n;
             }
-        }
+            cp_async_commit();  // always commit so that group counting stays uniform
+        };
+        // the first weight loads do not depend on the input vector: issue them before it is prepared
+#pragma unroll
+        for (int d = 0; d < kStages - 1; ++d) issue_load();
+
+        NQ_TRACE(1);
         for (int i = tid; i < my_items * 128; i += kGemvThreads) s1[i] = 0;
         quantise_input(jb, P.T, P.scale_kind, xq, P.xq_stride, red, sumx, delta);
+        NQ_TRACE(5);
 
         const int brow = (g < 2 * P.T) ? g : (2 * P.T - 1);  // unused MMA columns re-read a valid vector
         const int8_t* bbase = xq + brow * P.xq_stride + 8 * q;
 
         int accA[8][4], accB[8][4];
-        int cur_item = -1;
-        auto flush = [&]() {
-            if (cur_item < 0) return;
-            // d_j = 2^j * sum (j < 7), -128 * sum (j = 7): exact shifts
-            int v[4] = {0, 0, 0, 0};  // {rows g, g+8 of group A, rows g, g+8 of group B}
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const int sg = (j == 7) ? -1 : 1;
-                v[0] += sg * (((accA[j][0] >> j) << 8) + (accA[j][1] >> j));
-                v[1] += sg * (((accA[j][2] >> j) << 8) + (accA[j][3] >> j));
-                v[2] += sg * (((accB[j][0] >> j) << 8) + (accB[j][1] >> j));
-                v[3] += sg * (((accB[j][2] >> j) << 8) + (accB[j][3] >> j));
-            }
+        for (int j = 0; j < 8; ++j)
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
-                if (v[i] != 0) atomicAdd(&s1[(cur_item * 4 + i) * 32 + lane], v[i]);
-        };
-        auto consume = [&](const TilePair& tp, int p) {
-            const int il = p / chunks, c = p - il * chunks;
-            if (il != cur_item) {
-                flush();
-                cur_item = il;
-#pragma unroll
-                for (int j = 0; j < 8; ++j)
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) { accA[j][i] = 0; accB[j][i] = 0; }
-            }
-            const uint2* bp = reinterpret_cast<const uint2*>(bbase + c * 256);
+            for (int i = 0; i < 4; ++i) { accA[j][i] = 0; accB[j][i] = 0; }
+        int c_il = p_begin / chunks, c_c = p_begin - c_il * chunks;
+#pragma unroll 1
+        for (int n = 0; n < my_pairs; ++n) {
+            issue_load();
+            cp_async_wait<kStages - 1>();
+            __syncwarp();
+            const uint4* slot = ring + (n % kStages) * 64 + lane;
+            const uint4 ta = slot[0], tb = slot[32];
+            const uint2* bp = reinterpret_cast<const uint2*>(bbase + c_c * 256);
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 const uint2 b = bp[j * 4];
                 const uint32_t m = 0x01010101u << j;
-                mma_s8(accA[j], tp.a.x & m, tp.a.y & m, tp.a.z & m, tp.a.w & m, b.x, b.y);
-                mma_s8(accB[j], tp.b.x & m, tp.b.y & m, tp.b.z & m, tp.b.w & m, b.x, b.y);
+                mma_s8(accA[j], ta.x & m, ta.y & m, ta.z & m, ta.w & m, b.x, b.y);
+                mma_s8(accB[j], tb.x & m, tb.y & m, tb.z & m, tb.w & m, b.x, b.y);
             }
-        };
-        for (int base = 0; base < my_pairs; base += kPrefetch) {
+            __syncwarp();  // every lane has read the slot before it is refilled
+            // when this warp leaves the row tile, fold its partial sums into shared memory
+            if (++c_c == chunks || n + 1 == my_pairs) {
+                // d_j = 2^j * sum (j < 7), -128 * sum (j = 7): exact shifts
+                int v[4] = {0, 0, 0, 0};  // {rows g, g+8 of group A, rows g, g+8 of group B}
 #pragma unroll
-            for (int d = 0; d < kPrefetch; ++d) {
-                const int idx = base + d;
-                if (idx < my_pairs) {
-                    const TilePair tp = buf[d];
-                    if (idx + kPrefetch < my_pairs) {
-                        const int pn = warp + (idx + kPrefetch) * kGemvWarps;
-                        buf[d].a = load_tile(tile_ptr(pn, 0));
-                        buf[d].b = load_tile(tile_ptr(pn, 1));
-                    }
-                    consume(tp, warp + idx * kGemvWarps);
+                for (int j = 0; j < 8; ++j) {
+                    const int sg = (j == 7) ? -1 : 1;
+                    v[0] += sg * ((accA[j][0] >> j) * 256 + (accA[j][1] >> j));
+                    v[1] += sg * ((accA[j][2] >> j) * 256 + (accA[j][3] >> j));
+                    v[2] += sg * ((accB[j][0] >> j) * 256 + (accB[j][1] >> j));
+                    v[3] += sg * ((accB[j][2] >> j) * 256 + (accB[j][3] >> j));
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) { accA[j][i] = 0; accB[j][i] = 0; }
                 }
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    if (v[i] != 0) atomicAdd(&s1[(c_il * 4 + i) * 32 + lane], v[i]);
+                if (c_c == chunks) { c_c = 0; ++c_il; }
             }
         }
-        flush();
+        cp_async_wait<0>();
         __syncthreads();
+        NQ_TRACE(6);
         // finalise: thread -> (item, v, lane); lane (g, q) holds token q of rows g / g+8
         for (int i = tid; i < my_items * 128; i += kGemvThreads) {
             const int il = i >> 7, v = (i >> 5) & 3, ln = i & 31;
@@ -327,14 +454,32 @@ __device__ void run_phase(const Phase& ph, const GemvParams& P, unsigned char* s
             }
         }
         __syncthreads();  // xq / s1 are reused by the next job
+        NQ_TRACE(7);
     }
 }
 
 __global__ void __launch_bounds__(kGemvThreads, 1) gemv_group_kernel(const __grid_constant__ GemvParams P) {
     extern __shared__ __align__(16) unsigned char smem[];
-    run_phase(P.phase[0], P, smem);
-    if (!grid_barrier(P.header, gridDim.x)) return;
-    run_phase(P.phase[1], P, smem);
+    // The descriptors are read with runtime indices; one cooperative copy out of the
+    // parameter bank into shared memory replaces many serial constant-cache misses.
+    __shared__ __align__(16) Phase sphase[2];
+#ifdef NQ_GEMV_TRACE
+    if (threadIdx.x == 0) g_trace_n[blockIdx.x] = 0;
+#endif
+    NQ_TRACE(0);
+    {
+        const uint32_t* src = reinterpret_cast<const uint32_t*>(&P.phase[0]);
+        uint32_t* dst = reinterpret_cast<uint32_t*>(&sphase[0]);
+        for (int i = threadIdx.x; i < (int)(sizeof(Phase) * 2 / 4); i += kGemvThreads) dst[i] = src[i];
+        __syncthreads();
+    }
+#pragma unroll 1
+    for (int ph = 0; ph < 2; ++ph) {
+        run_phase(sphase[ph], P, smem);
+        NQ_TRACE(8);
+        if (ph == 0 && !grid_barrier(P.header, gridDim.x)) return;
+        NQ_TRACE(9);
+    }
 }
 
 static size_t round_up(size_t v, size_t m) { return (v + m - 1) / m * m; }
@@ -404,7 +549,7 @@ int nq_gemv_group_fwd(const nq_linear_desc* d, int n_linears, int T, int dtype, 
 
     // tokens are processed in groups that fit the 8 MMA columns and shared memory
     int tg = T < kMaxTok ? T : kMaxTok;
-    auto smem_for = [&](int t) { return (size_t)512 + (size_t)max_items * 512 + (size_t)2 * t * stride; };
+    auto smem_for = [&](int t) { return kFixedBytes + kRingBytes + (size_t)max_items * 512 + (size_t)2 * t * stride; };
     while (tg > 1 && smem_for(tg) > (size_t)smem_optin[dev & 63]) --tg;
     if (smem_for(tg) > (size_t)smem_optin[dev & 63]) return NQ_ERR_UNSUPPORTED;
 
@@ -438,6 +583,7 @@ int nq_gemv_group_fwd(const nq_linear_desc* d, int n_linears, int T, int dtype, 
             a.items = (L.R + 31) / 32;
             a.in_kind = dtype;
             a.out_kind = KIND_F32;
+            a.vec = (L.N % 8 == 0) && (L.ldx % 8 == 0) && aligned16(a.in) && aligned16(L.s_in);
             Job& b = P.phase[1].job[i];
             b.tiles = static_cast<const uint4*>(L.u_tiles);
             b.in = tbuf;
@@ -452,6 +598,7 @@ int nq_gemv_group_fwd(const nq_linear_desc* d, int n_linears, int T, int dtype, 
             b.items = (L.M + 31) / 32;
             b.in_kind = KIND_F32;
             b.out_kind = dtype;
+            b.vec = (L.R % 8 == 0);  // the intermediate lives in the 256-byte aligned scratch
         }
         void* args[] = {&P};
         NQ_CUDA_TRY(cudaLaunchCooperativeKernel((const void*)gemv_group_kernel, dim3(grid), dim3(kGemvThreads),
@@ -468,6 +615,14 @@ int nq_gemv_fwd(const void* x, const void* s_in, const void* v_tiles, const void
     d.y = y; d.N = N; d.R = R; d.M = M; d.ldx = N; d.ldy = M;
     return nq_gemv_group_fwd(&d, 1, T, dtype, scratch, scratch_bytes, stream);
 }
+
+#ifdef NQ_GEMV_TRACE
+int nq_debug_read_trace(unsigned long long* host_out) {
+    NQ_CUDA_TRY(cudaDeviceSynchronize());
+    NQ_CUDA_TRY(cudaMemcpyFromSymbol(host_out, g_trace, sizeof(unsigned long long) * 148 * 64));
+    return NQ_OK;
+}
+#endif
 
 int nq_scratch_status(const void* scratch, nq_stream_t stream) {
     if (!scratch) return NQ_ERR_NULL;
