@@ -2,34 +2,40 @@
 //
 //   y = s_out * (U . (s_mid * (V . (s_in * x))))          T <= 4 tokens per launch
 //
-// The kernel is bound by the HBM stream of the packed factors; everything else is
-// arranged so that the per-weight instruction cost stays far below that stream:
+// The kernel is bound by the HBM stream of the packed factors and, for the layer
+// sizes of 8B-class decoders, by latency; both call for as few instructions per
+// weight and per phase as possible.
 //
+//  * The packed sign bits are the A operand of an integer tensor-core MMA
+//    (mma.sync m16n8k32 s8*s8->s32) WITHOUT unpacking: in the tile layout (see
+//    nq_rows_to_tiles) `word & (0x01010101 << j)` is an int8x4 register with values
+//    {0, 2^j} ({0, -128} for j = 7), so one LOP3 prepares four weights and the eight
+//    masks j = 0..7 consume a whole 32-bit word.  Columns [32j, 32j+32) of a
+//    256-column chunk form the "class" j.
 //  * The input vector of a phase (s_in*x, or the rank-R intermediate t) is turned,
-//    once per CTA, into 16-bit fixed point with a per-token scale and split into
-//    two int8 terms (hi, lo).  These 2*T int8 vectors are the B operand (the N=8
-//    columns) of an integer tensor-core MMA (mma.sync m16n8k32 s8*s8->s32).
-//  * The packed sign bits are the A operand WITHOUT unpacking: in the tile layout
-//    (see nq_rows_to_tiles) `word & (0x01010101 << j)` is an int8x4 register with
-//    values {0, 2^j}, so one LOP3 prepares four weights and eight masks j = 0..7
-//    consume a whole 32-bit word.  Each mask has its own accumulator; the sums are
-//    recombined exactly with shifts at the end of a row tile.
-//  * sum(+-X) = sum(X) - 2 * sum_{bit=1}(X); all accumulation is exact int32, so the
-//    result does not depend on the order in which warps add their parts.
+//    once per CTA, into 17-bit fixed point X with a per-token scale.  A column of
+//    class j is stored as X * 2^(7-j) (negated for j = 7), split into three signed
+//    bytes.  The product of the A value 2^j and that operand is 2^7 * X for every
+//    class, so all eight masks accumulate into ONE accumulator per output row and
+//    byte term.  The three byte terms of a token are three of the N = 8 MMA columns.
+//  * sum(+-X) = sum(X) - 2 * sum_{bit=1}(X).  All accumulation is exact int32 /
+//    int64, so the result does not depend on the order in which warps add up.
 //
-// A legacy SIMT sign-flip-add inner loop issues ~1.5 instructions per weight and
-// tops out near one third of the HBM rate on this part, which is why the integer
-// MMA is used as a wide dot-product unit here.  No floating-point tensor math and
-// no shared-memory staging of the weights is involved: each lane streams its tile
-// words with 128-bit loads straight into the registers that feed the MMA.
+// A SIMT sign-flip-add inner loop issues ~1.5 instructions per weight and tops out
+// near one third of the HBM rate on this part, which is why the integer MMA is
+// used as a wide dot-product unit here.
 //
 // Phases: phase 1 computes t[T,R] (fp32, in scratch), a device-wide barrier
 // follows, phase 2 computes y.  Several linears that share the two phases (q/k/v,
-// gate/up) are processed in one launch.  The barrier spin is bounded: on expiry a
-// status word is set and every CTA returns.
+// gate/up) are processed in one launch.  The weight stream of the next job is
+// started before the current job's epilogue and before the barrier, so the barrier
+// wait overlaps with HBM traffic.  The barrier spin is bounded: on expiry a status
+// word is set and every CTA returns.
 //
 // replaces: src/nanoquant/kernel/cuda/gemv_kernel.cu:43-301 of the reference
 // (two kernels per linear, fp16/bf16 accumulation, sign-flip adds).
+#include <cstring>
+
 #include "nq_common.cuh"
 
 namespace nq {
@@ -43,8 +49,9 @@ namespace nq {
 constexpr int kGemvThreads = NQ_GEMV_THREADS;
 constexpr int kGemvWarps = kGemvThreads / 32;
 constexpr int kMaxJobs = 4;         // linears per launch
-constexpr int kMaxTok = 4;          // tokens per launch (2 int8 terms each -> 8 MMA columns)
-constexpr int kQMax = 32639;        // 127*256 + 127: hi and lo both fit a signed byte
+constexpr int kMaxTok = 4;          // tokens per launch (3 byte terms each, 8 MMA columns per column group)
+constexpr int kQMax = 64000;        // |X| bound: X * 2^7 splits into three signed bytes
+constexpr int kMaxK = 32768;        // keeps sum(X) and every accumulator inside int32
 constexpr int kStages = NQ_GEMV_STAGES;          // 1 KB weight slots in flight per warp
 constexpr size_t kRedBytes = 384;   // per-warp maxima (kGemvWarps * 4 floats) + 4 inverse scales
 constexpr size_t kFixedBytes = 512;
@@ -111,14 +118,6 @@ __device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, ui
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ uint4 load_tile(const uint4* p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(p));
-    return v;
-}
-
 // Bounded device-wide barrier on {count, generation} words.  Returns false when the
 // wait expired (a status word is set and the caller returns).  One thread per CTA
 // arrives with a release and polls with acquires; the CTA barrier before and after
@@ -174,15 +173,57 @@ __device__ __forceinline__ void load8(const void* base, long long i, float (&v)[
     }
 }
 
-// Quantise the input vectors of a job into shared memory.
-//   xq: 2*T int8 vectors (row 2*tok = hi term, 2*tok+1 = lo term), `stride` bytes apart,
-//       in the k order the MMA B fragments expect (see below); columns K..Kpad are zero.
-//   sumx[tok]: sum of the 16-bit values, delta[tok]: value of one unit.
-// Byte position inside a chunk of 256 columns: 32*j + 8*q + 4*h + b for column
-// 32*j + 16*h + 4*q + b, so that lane (g, q) fetches its two B registers
+// Class-shifted operand of column k: X * 2^(7-j), negated for j = 7, j = (k % 256) / 32.
+__device__ __forceinline__ int class_shift(int X, int j) { return (j == 7) ? -X : (X << (7 - j)); }
+
+// Byte offset of column k inside an int8 vector: chunk base + 32*j + 8*q + 4*h + b for
+// k % 256 = 32*j + 16*h + 4*q + b, so that lane (g, q) fetches the two B registers
 // {k = 4q.., k = 16+4q..} of mask j with one 64-bit load.
+__device__ __forceinline__ int xq_pos(int k) {
+    const int kin = k & 255;
+    return (k & ~255) + (kin & 0xE0) + 2 * (kin & 12) + ((kin & 16) >> 2) + (kin & 3);
+}
+
+// red[warp * 4 + t] holds per-warp maxima of token t; thread t < T turns them into the
+// fixed-point scale of the token.
+__device__ __forceinline__ void token_scales(int T, float* red, int* sumx, float* delta) {
+    const int tid = threadIdx.x;
+    if (tid < T) {
+        float m = 0.f;
+        for (int w = 0; w < kGemvWarps; ++w) m = fmaxf(m, red[w * kMaxTok + tid]);
+        // a non-finite or zero maximum quantises everything to zero
+        const bool good = (m > 0.f) && (m < 3.0e38f);
+        red[kGemvWarps * kMaxTok + tid] = good ? (float)kQMax / m : 0.f;
+        delta[tid] = good ? m / (float)kQMax : 0.f;
+        sumx[tid] = 0;
+    }
+}
+
+// Write eight class-shifted operands (columns k8..k8+7 of one token) as three byte vectors.
+__device__ __forceinline__ void store_terms(const uint32_t (&Y)[8], int8_t* r0, int stride, int k8) {
+    // Y = 65536*b2 + 256*b1 + b0 with signed bytes: b0 = byte 0 of Y, b1 = byte 1 of
+    // Y + 0x80, b2 = byte 2 of Y + 0x8080
+    const int pos = xq_pos(k8);
+#pragma unroll
+    for (int w = 0; w < 2; ++w) {
+        const uint32_t y0 = Y[4 * w], y1 = Y[4 * w + 1], y2 = Y[4 * w + 2], y3 = Y[4 * w + 3];
+        const uint32_t z0 = y0 + 0x80u, z1 = y1 + 0x80u, z2 = y2 + 0x80u, z3 = y3 + 0x80u;
+        const uint32_t u0 = y0 + 0x8080u, u1 = y1 + 0x8080u, u2 = y2 + 0x8080u, u3 = y3 + 0x8080u;
+        const uint32_t b0 = __byte_perm(__byte_perm(y0, y1, 0x0040), __byte_perm(y2, y3, 0x0040), 0x5410);
+        const uint32_t b1 = __byte_perm(__byte_perm(z0, z1, 0x0051), __byte_perm(z2, z3, 0x0051), 0x5410);
+        const uint32_t b2 = __byte_perm(__byte_perm(u0, u1, 0x0062), __byte_perm(u2, u3, 0x0062), 0x5410);
+        *reinterpret_cast<uint32_t*>(r0 + pos + 8 * w) = b0;
+        *reinterpret_cast<uint32_t*>(r0 + stride + pos + 8 * w) = b1;
+        *reinterpret_cast<uint32_t*>(r0 + 2 * stride + pos + 8 * w) = b2;
+    }
+}
+
+// Quantise the input vectors of a job into shared memory.
+//   xq: 3*T int8 vectors (row 3*tok + term, term 0 = least significant byte), `stride`
+//       bytes apart, columns in xq_pos() order; columns K..Kpad are zero.
+//   sumx[tok]: sum of the (unshifted) fixed-point values, delta[tok]: value of one unit.
 // The code is kept as small loops on purpose: it runs once per phase, where
-// instruction fetch, not arithmetic, sets the pace.
+// instruction fetch and latency, not arithmetic, set the pace.
 //
 // Vector path: rows of `in` / `pre` 16-byte aligned, K % 8 == 0; eight columns per thread and step.
 template <int IN_KIND>
@@ -208,54 +249,33 @@ __device__ __noinline__ void quantise_vec(const Job& jb, int T, int8_t* xq, int 
         if (lane == 0) red[warp * kMaxTok + t] = m;
     }
     __syncthreads();
-    if (tid < T) {
-        float m = 0.f;
-        for (int w = 0; w < kGemvWarps; ++w) m = fmaxf(m, red[w * kMaxTok + tid]);
-        // a non-finite or zero maximum quantises everything to zero
-        const bool good = (m > 0.f) && (m < 3.0e38f);
-        red[kGemvWarps * kMaxTok + tid] = good ? (float)kQMax / m : 0.f;
-        delta[tid] = good ? m / (float)kQMax : 0.f;
-        sumx[tid] = 0;
-    }
+    token_scales(T, red, sumx, delta);
     __syncthreads();
-    // pass 2: |p * inv| <= kQMax + 2^-8 by construction (same products as in pass 1), no clamp needed
+    // pass 2: |p * inv| <= kQMax + 2^-7 by construction (same products as in pass 1), no clamp needed
 #pragma unroll 1
     for (int t = 0; t < T; ++t) {
         const float inv = red[kGemvWarps * kMaxTok + t];
-        int8_t* rh = xq + (2 * t) * stride;
-        int8_t* rl = rh + stride;
+        int8_t* r0 = xq + (3 * t) * stride;
         int acc = 0;
 #pragma unroll 1
         for (int k8 = tid * 8; k8 < Kpad; k8 += kGemvThreads * 8) {
-            int X[8];
+            const int j = (k8 >> 5) & 7;
+            uint32_t Y[8];  // class-shifted operands
             if (k8 < K) {
                 float v[8], s[8];
                 load8<IN_KIND>(jb.in, t * jb.ld_in + k8, v);
                 if (kHasPre) load8<IN_KIND>(jb.pre, k8, s);
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
-                    X[e] = __float2int_rn((kHasPre ? v[e] * s[e] : v[e]) * inv);
-                    acc += X[e];
+                    const int X = __float2int_rn((kHasPre ? v[e] * s[e] : v[e]) * inv);
+                    acc += X;
+                    Y[e] = (uint32_t)class_shift(X, j);
                 }
             } else {
 #pragma unroll
-                for (int e = 0; e < 8; ++e) X[e] = 0;
+                for (int e = 0; e < 8; ++e) Y[e] = 0;
             }
-            // X = 256 * hi + lo with lo the signed low byte: lo = byte 0 of X, hi = byte 1 of X + 128
-            uint32_t lo[2], hi[2];
-#pragma unroll
-            for (int w = 0; w < 2; ++w) {
-                const uint32_t x0 = X[4 * w], x1 = X[4 * w + 1], x2 = X[4 * w + 2], x3 = X[4 * w + 3];
-                lo[w] = __byte_perm(__byte_perm(x0, x1, 0x0040), __byte_perm(x2, x3, 0x0040), 0x5410);
-                hi[w] = __byte_perm(__byte_perm(x0 + 128u, x1 + 128u, 0x0051),
-                                    __byte_perm(x2 + 128u, x3 + 128u, 0x0051), 0x5410);
-            }
-            const int kin = k8 & 255;  // j = kin >> 5, h = (kin >> 4) & 1, q = (kin >> 2) & 3 (0 or 2)
-            const int pos = (k8 & ~255) + (kin & 0xE0) + 2 * (kin & 8) + ((kin & 16) >> 2);
-            *reinterpret_cast<uint32_t*>(rh + pos) = hi[0];
-            *reinterpret_cast<uint32_t*>(rh + pos + 8) = hi[1];
-            *reinterpret_cast<uint32_t*>(rl + pos) = lo[0];
-            *reinterpret_cast<uint32_t*>(rl + pos + 8) = lo[1];
+            store_terms(Y, r0, stride, k8);
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
@@ -281,14 +301,7 @@ __device__ __noinline__ void quantise_scalar(const Job& jb, int T, int scale_kin
         if (lane == 0) red[warp * kMaxTok + t] = m;
     }
     __syncthreads();
-    if (tid < T) {
-        float m = 0.f;
-        for (int w = 0; w < kGemvWarps; ++w) m = fmaxf(m, red[w * kMaxTok + tid]);
-        const bool good = (m > 0.f) && (m < 3.0e38f);
-        red[kGemvWarps * kMaxTok + tid] = good ? (float)kQMax / m : 0.f;
-        delta[tid] = good ? m / (float)kQMax : 0.f;
-        sumx[tid] = 0;
-    }
+    token_scales(T, red, sumx, delta);
     __syncthreads();
 #pragma unroll 1
     for (int t = 0; t < T; ++t) {
@@ -301,10 +314,11 @@ __device__ __noinline__ void quantise_scalar(const Job& jb, int T, int scale_kin
                 X = __float2int_rn(load_as_float(jb.in, t * jb.ld_in + k, jb.in_kind) * s * inv);
             }
             acc += X;
-            const int kin = k & 255;
-            const int pos = (k & ~255) + (kin & 0xE0) + 2 * (kin & 12) + ((kin & 16) >> 2) + (kin & 3);
-            xq[(2 * t) * stride + pos] = (int8_t)((X + 128) >> 8);
-            xq[(2 * t + 1) * stride + pos] = (int8_t)(X & 0xFF);
+            const int y = class_shift(X, (k >> 5) & 7);
+            const int pos = xq_pos(k);
+            xq[(3 * t) * stride + pos] = (int8_t)(y & 0xFF);
+            xq[(3 * t + 1) * stride + pos] = (int8_t)(((y + 0x80) >> 8) & 0xFF);
+            xq[(3 * t + 2) * stride + pos] = (int8_t)(((y + 0x8080) >> 16) & 0xFF);
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
@@ -329,116 +343,158 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-// One phase: every CTA walks the jobs; inside a job it owns the row tiles (32 rows)
-// blockIdx.x, blockIdx.x + gridDim.x, ... and its warps split the K chunks of those
-// tiles.  Each warp streams its (tile, chunk) pairs - 1 KB of packed weights each -
-// through a private ring of kStages shared-memory slots filled with cp.async, so the
-// loop body exists once and stays small enough for the instruction cache.
-__device__ __noinline__ void run_phase(const Phase& ph, const GemvParams& P, unsigned char* smem) {
+// Per-warp cursor over the (tile, chunk) pairs of one job: 1 KB of packed weights per
+// pair (two row groups x 256 columns), pairs tile-major, one contiguous range per warp.
+struct PairStream {
+    int my_items;   // row tiles (32 rows) of this CTA in the job
+    int my_pairs;   // pairs of this warp
+    int begin_il, begin_c;   // first pair of this warp: local tile index, chunk
+    int l_il, l_c, l_n;      // next pair to fetch
+};
+
+__device__ __forceinline__ void stream_issue(PairStream& st, const Job& jb, uint4* ring, int lane) {
+    if (st.l_n < st.my_pairs) {
+        const int row_groups = (jb.rows + 15) >> 4;
+        const int rg = 2 * ((int)blockIdx.x + st.l_il * (int)gridDim.x);
+        const int rgb = (rg + 1 < row_groups) ? rg + 1 : rg;  // odd tail: re-read, result discarded
+        uint4* dst = ring + (st.l_n % kStages) * 64 + lane;
+        cp_async16(dst, jb.tiles + ((size_t)rg * jb.chunks + st.l_c) * 32 + lane);
+        cp_async16(dst + 32, jb.tiles + ((size_t)rgb * jb.chunks + st.l_c) * 32 + lane);
+        if (++st.l_c == jb.chunks) { st.l_c = 0; ++st.l_il; }
+        ++st.l_n;
+    }
+    cp_async_commit();  // always commit so that group counting stays uniform
+}
+
+// Set the cursor up and start the first weight loads of a job.  They do not depend on
+// the job's input vector, so this runs before the input is ready (for a phase-2 job:
+// before the device-wide barrier, which then overlaps with the loads).
+__device__ __forceinline__ void stream_begin(PairStream& st, const Job& jb, uint4* ring, int warp, int lane) {
+    st.my_items = ((int)blockIdx.x < jb.items) ? (jb.items - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+    const int npairs = st.my_items * jb.chunks;
+    const int p_begin = (int)((long long)npairs * warp / kGemvWarps);
+    st.my_pairs = (int)((long long)npairs * (warp + 1) / kGemvWarps) - p_begin;
+    st.begin_il = p_begin / jb.chunks;
+    st.begin_c = p_begin - st.begin_il * jb.chunks;
+    st.l_il = st.begin_il; st.l_c = st.begin_c; st.l_n = 0;
+#pragma unroll
+    for (int d = 0; d < kStages - 1; ++d) stream_issue(st, jb, ring, lane);
+    // the output scales are needed right after the main loop: pull them towards L2 now
+    if (jb.post && (int)threadIdx.x < st.my_items) {
+        const int row = 32 * ((int)blockIdx.x + (int)threadIdx.x * (int)gridDim.x);
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(static_cast<const char*>(jb.post) + 2 * (size_t)row));
+    }
+}
+
+__device__ __forceinline__ bool cta_has_items(const Job& jb) { return (int)blockIdx.x < jb.items; }
+
+// The whole launch for one CTA: the jobs of phase 1, the device-wide barrier, the jobs
+// of phase 2.  CG = column groups of 8 MMA columns (3 columns per token).
+template <int CG>
+__device__ __forceinline__ bool run_all(const Phase* phases, const GemvParams& P, unsigned char* smem) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, q = lane & 3;
+    constexpr int kCols = 8 * CG;
     // shared memory carve-up
-    float* red = reinterpret_cast<float*>(smem);                          // [warps][4]
+    float* red = reinterpret_cast<float*>(smem);                          // [warps][4] + [4]
     int* sumx = reinterpret_cast<int*>(smem + kRedBytes);                 // [4]
     float* delta = reinterpret_cast<float*>(smem + kRedBytes + 16);       // [4]
     uint4* ring = reinterpret_cast<uint4*>(smem + kFixedBytes) + warp * (kStages * 64);  // [stage][2][32]
-    int* s1 = reinterpret_cast<int*>(smem + kFixedBytes + kRingBytes);    // [max_items][4][32]
-    int8_t* xq = reinterpret_cast<int8_t*>(smem + kFixedBytes + kRingBytes + (size_t)P.max_items * 512);
+    int* s1 = reinterpret_cast<int*>(smem + kFixedBytes + kRingBytes);    // [max_items][32 rows][kCols]
+    int8_t* xq = reinterpret_cast<int8_t*>(smem + kFixedBytes + kRingBytes + (size_t)P.max_items * (128 * kCols));
 
+    const int njobs = phases[0].njobs;        // same count in both phases
+    auto job_of = [&](int s) -> const Job& { return phases[s >= njobs].job[s >= njobs ? s - njobs : s]; };
+    auto next_step = [&](int s) {             // first step >= s in which this CTA owns row tiles
+        while (s < 2 * njobs && !cta_has_items(job_of(s))) ++s;
+        return s;
+    };
+    bool barrier_done = false;
+    PairStream st;
+    int s = next_step(0);
+    if (s < 2 * njobs) stream_begin(st, job_of(s), ring, warp, lane);
+    NQ_TRACE(1);
 #pragma unroll 1
-    for (int ji = 0; ji < ph.njobs; ++ji) {
-        const Job& jb = ph.job[ji];
-        const int my_items = ((int)blockIdx.x < jb.items)
-                                 ? (jb.items - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
-        if (my_items == 0) continue;  // uniform per CTA
+    while (true) {
+        if (!barrier_done && s >= njobs) {    // everything of phase 1 is written: publish, then read t
+            NQ_TRACE(8);
+            if (!grid_barrier(P.header, gridDim.x)) return false;
+            barrier_done = true;
+            NQ_TRACE(9);
+        }
+        if (s >= 2 * njobs) break;
+        const Job& jb = job_of(s);
         const int chunks = jb.chunks;
-        const int row_groups = (jb.rows + 15) >> 4;
-        // The CTA's (tile, chunk) pairs, tile-major, are split into one contiguous range per
-        // warp: a warp then streams consecutive memory and folds its partial sums into shared
-        // memory only when it leaves a row tile (at most twice more often than it has tiles).
-        const int npairs = my_items * chunks;
-        const int p_begin = (int)((long long)npairs * warp / kGemvWarps);
-        const int p_end = (int)((long long)npairs * (warp + 1) / kGemvWarps);
-        const int my_pairs = p_end - p_begin;
-
-        // load stream state: (item, chunk) of the next pair to fetch
-        int l_il = p_begin / chunks, l_c = p_begin - l_il * chunks, l_n = 0;
-        auto issue_load = [&]() {
-            if (l_n < my_pairs) {
-                const int rg = 2 * ((int)blockIdx.x + l_il * (int)gridDim.x);
-                const int rgb = (rg + 1 < row_groups) ? rg + 1 : rg;  // odd tail: re-read, result discarded
-                uint4* dst = ring + (l_n % kStages) * 64 + lane;
-                cp_async16(dst, jb.tiles + ((size_t)rg * chunks + l_c) * 32 + lane);
-                cp_async16(dst + 32, jb.tiles + ((size_t)rgb * chunks + l_c) * 32 + lane);
-                if (++l_c == chunks) { l_c = 0; ++l_il; }
-                ++l_n;
-            }
-            cp_async_commit();  // always commit so that group counting stays uniform
-        };
-        // the first weight loads do not depend on the input vector: issue them before it is prepared
-#pragma unroll
-        for (int d = 0; d < kStages - 1; ++d) issue_load();
-
-        NQ_TRACE(1);
-        for (int i = tid; i < my_items * 128; i += kGemvThreads) s1[i] = 0;
+        for (int i = tid; i < st.my_items * (32 * kCols); i += kGemvThreads) s1[i] = 0;
         quantise_input(jb, P.T, P.scale_kind, xq, P.xq_stride, red, sumx, delta);
         NQ_TRACE(5);
 
-        const int brow = (g < 2 * P.T) ? g : (2 * P.T - 1);  // unused MMA columns re-read a valid vector
-        const int8_t* bbase = xq + brow * P.xq_stride + 8 * q;
-
-        int accA[8][4], accB[8][4];
+        // MMA column n = 8*cg + g reads int8 vector n (= 3*tok + term); unused columns re-read a valid one
+        const int8_t* bbase[CG];
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
+        for (int cg = 0; cg < CG; ++cg) {
+            const int n = 8 * cg + g;
+            bbase[cg] = xq + (n < 3 * P.T ? n : 3 * P.T - 1) * P.xq_stride + 8 * q;
+        }
+        int accA[CG][4], accB[CG][4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) { accA[j][i] = 0; accB[j][i] = 0; }
-        int c_il = p_begin / chunks, c_c = p_begin - c_il * chunks;
+        for (int cg = 0; cg < CG; ++cg)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { accA[cg][i] = 0; accB[cg][i] = 0; }
+        int c_il = st.begin_il, c_c = st.begin_c;
 #pragma unroll 1
-        for (int n = 0; n < my_pairs; ++n) {
-            issue_load();
+        for (int n = 0; n < st.my_pairs; ++n) {
+            stream_issue(st, jb, ring, lane);
             cp_async_wait<kStages - 1>();
             __syncwarp();
             const uint4* slot = ring + (n % kStages) * 64 + lane;
             const uint4 ta = slot[0], tb = slot[32];
-            const uint2* bp = reinterpret_cast<const uint2*>(bbase + c_c * 256);
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-                const uint2 b = bp[j * 4];
                 const uint32_t m = 0x01010101u << j;
-                mma_s8(accA[j], ta.x & m, ta.y & m, ta.z & m, ta.w & m, b.x, b.y);
-                mma_s8(accB[j], tb.x & m, tb.y & m, tb.z & m, tb.w & m, b.x, b.y);
+#pragma unroll
+                for (int cg = 0; cg < CG; ++cg) {
+                    const uint2 b = *reinterpret_cast<const uint2*>(bbase[cg] + c_c * 256 + 32 * j);
+                    mma_s8(accA[cg], ta.x & m, ta.y & m, ta.z & m, ta.w & m, b.x, b.y);
+                    mma_s8(accB[cg], tb.x & m, tb.y & m, tb.z & m, tb.w & m, b.x, b.y);
+                }
             }
             __syncwarp();  // every lane has read the slot before it is refilled
-            // when this warp leaves the row tile, fold its partial sums into shared memory
-            if (++c_c == chunks || n + 1 == my_pairs) {
-                // d_j = 2^j * sum (j < 7), -128 * sum (j = 7): exact shifts
-                int v[4] = {0, 0, 0, 0};  // {rows g, g+8 of group A, rows g, g+8 of group B}
+            // when this warp leaves the row tile, fold its partial sums into shared memory:
+            // lane (g, q) holds rows g / g+8 of both row groups, columns 2q, 2q+1 of each column group
+            if (++c_c == chunks || n + 1 == st.my_pairs) {
+                int* dst = s1 + c_il * (32 * kCols);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const int sg = (j == 7) ? -1 : 1;
-                    v[0] += sg * ((accA[j][0] >> j) * 256 + (accA[j][1] >> j));
-                    v[1] += sg * ((accA[j][2] >> j) * 256 + (accA[j][3] >> j));
-                    v[2] += sg * ((accB[j][0] >> j) * 256 + (accB[j][1] >> j));
-                    v[3] += sg * ((accB[j][2] >> j) * 256 + (accB[j][3] >> j));
+                for (int cg = 0; cg < CG; ++cg) {
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) { accA[j][i] = 0; accB[j][i] = 0; }
+                    for (int i = 0; i < 4; ++i) {
+                        const int col = 8 * cg + 2 * q + (i & 1);
+                        const int ra = g + 8 * (i >> 1);
+                        if (accA[cg][i] != 0) atomicAdd(&dst[ra * kCols + col], accA[cg][i]);
+                        if (accB[cg][i] != 0) atomicAdd(&dst[(16 + ra) * kCols + col], accB[cg][i]);
+                        accA[cg][i] = 0;
+                        accB[cg][i] = 0;
+                    }
                 }
-#pragma unroll
-                for (int i = 0; i < 4; ++i)
-                    if (v[i] != 0) atomicAdd(&s1[(c_il * 4 + i) * 32 + lane], v[i]);
                 if (c_c == chunks) { c_c = 0; ++c_il; }
             }
         }
         cp_async_wait<0>();
         __syncthreads();
         NQ_TRACE(6);
-        // finalise: thread -> (item, v, lane); lane (g, q) holds token q of rows g / g+8
-        for (int i = tid; i < my_items * 128; i += kGemvThreads) {
-            const int il = i >> 7, v = (i >> 5) & 3, ln = i & 31;
-            const int tok = ln & 3, gg = ln >> 2;
-            const int row = 32 * ((int)blockIdx.x + il * (int)gridDim.x) + 16 * (v >> 1) + 8 * (v & 1) + gg;
-            if (tok < P.T && row < jb.rows) {
-                const long long r = (long long)sumx[tok] - 2LL * (long long)s1[i];
+        // start the next job's weight stream before this job's epilogue and before any barrier
+        const int my_items = st.my_items;
+        const int s_next = next_step(s + 1);
+        if (s_next < 2 * njobs) stream_begin(st, job_of(s_next), ring, warp, lane);
+        // finalise: thread -> (item, row, token).  The three column sums of a token are the byte terms
+        // of 128 * sum_{bit=1}(X); result = sum(X) - 2 * sum_{bit=1}(X) = sum(X) - terms / 64.
+        for (int i = tid; i < my_items * 32 * P.T; i += kGemvThreads) {
+            const int tok = i % P.T, rr = (i / P.T) & 31, il = i / (32 * P.T);
+            const int row = 32 * ((int)blockIdx.x + il * (int)gridDim.x) + rr;
+            if (row < jb.rows) {
+                const int* c = s1 + il * (32 * kCols) + rr * kCols + 3 * tok;
+                const long long terms = (long long)c[2] * 65536 + (long long)c[1] * 256 + (long long)c[0];
+                const long long r = (long long)sumx[tok] - terms / 64;
                 float val = (float)r * delta[tok];
                 if (jb.post) val *= load_as_float(jb.post, row, P.scale_kind);
                 if (jb.out_kind == KIND_F32) {
@@ -455,9 +511,12 @@ __device__ __noinline__ void run_phase(const Phase& ph, const GemvParams& P, uns
         }
         __syncthreads();  // xq / s1 are reused by the next job
         NQ_TRACE(7);
+        s = s_next;
     }
+    return true;
 }
 
+template <int CG>
 __global__ void __launch_bounds__(kGemvThreads, 1) gemv_group_kernel(const __grid_constant__ GemvParams P) {
     extern __shared__ __align__(16) unsigned char smem[];
     // The descriptors are read with runtime indices; one cooperative copy out of the
@@ -473,16 +532,30 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_group_kernel(const __gri
         for (int i = threadIdx.x; i < (int)(sizeof(Phase) * 2 / 4); i += kGemvThreads) dst[i] = src[i];
         __syncthreads();
     }
-#pragma unroll 1
-    for (int ph = 0; ph < 2; ++ph) {
-        run_phase(sphase[ph], P, smem);
-        NQ_TRACE(8);
-        if (ph == 0 && !grid_barrier(P.header, gridDim.x)) return;
-        NQ_TRACE(9);
-    }
+    run_all<CG>(sphase, P, smem);
 }
 
 static size_t round_up(size_t v, size_t m) { return (v + m - 1) / m * m; }
+
+// Opt-in shared memory limit for both instantiations, set once per device.
+static int dynamic_smem_limit(int dev, int* out) {
+    static int cached[64];
+    if (cached[dev & 63] == 0) {
+        int optin = 0, lim = 1 << 30;
+        NQ_CUDA_TRY(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+        const void* fns[2] = {(const void*)gemv_group_kernel<1>, (const void*)gemv_group_kernel<2>};
+        for (const void* fn : fns) {
+            cudaFuncAttributes fa;
+            NQ_CUDA_TRY(cudaFuncGetAttributes(&fa, fn));
+            const int v = optin - (int)fa.sharedSizeBytes;  // the opt-in limit covers static + dynamic
+            NQ_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, v));
+            lim = v < lim ? v : lim;
+        }
+        cached[dev & 63] = lim;
+    }
+    *out = cached[dev & 63];
+    return NQ_OK;
+}
 
 }  // namespace nq
 
@@ -520,24 +593,18 @@ int nq_gemv_group_fwd(const nq_linear_desc* d, int n_linears, int T, int dtype, 
         if (!L.x || !L.s_in || !L.v_tiles || !L.u_tiles || !L.s_out || !L.y) return NQ_ERR_NULL;
         if (L.N <= 0 || L.R <= 0 || L.M <= 0) return NQ_ERR_SHAPE;
         if (L.ldx < L.N || L.ldy < L.M) return NQ_ERR_SHAPE;
+        if (L.N > kMaxK || L.R > kMaxK) return NQ_ERR_UNSUPPORTED;
         if (!aligned16(L.v_tiles) || !aligned16(L.u_tiles)) return NQ_ERR_ALIGN;
         maxK = L.N > maxK ? L.N : maxK;
         maxK = L.R > maxK ? L.R : maxK;
     }
-    int dev = 0;
+    int dev = 0, smem_limit = 0;
     NQ_CUDA_TRY(cudaGetDevice(&dev));
-    const int sms = sm_count();
-    static int smem_optin[64];
-    if (smem_optin[dev & 63] == 0) {
-        int v = 0;
-        NQ_CUDA_TRY(cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
-        cudaFuncAttributes fa;
-        NQ_CUDA_TRY(cudaFuncGetAttributes(&fa, gemv_group_kernel));
-        v -= (int)fa.sharedSizeBytes;  // the opt-in limit covers static + dynamic shared memory
-        NQ_CUDA_TRY(cudaFuncSetAttribute(gemv_group_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, v));
-        smem_optin[dev & 63] = v;
+    {
+        const int st = dynamic_smem_limit(dev, &smem_limit);
+        if (st != NQ_OK) return st;
     }
-    const int grid = sms;
+    const int grid = sm_count();
     int max_items = 1;
     for (int i = 0; i < n_linears; ++i) {
         const int it1 = ((d[i].R + 31) / 32 + grid - 1) / grid, it2 = ((d[i].M + 31) / 32 + grid - 1) / grid;
@@ -547,11 +614,14 @@ int nq_gemv_group_fwd(const nq_linear_desc* d, int n_linears, int T, int dtype, 
     const int kpad = (maxK + 255) / 256 * 256;
     const int stride = kpad + 32;  // 32 mod 128: conflict-free 64-bit fragment loads
 
-    // tokens are processed in groups that fit the 8 MMA columns and shared memory
+    // tokens are processed in groups that fit the MMA columns (3 per token) and shared memory
+    auto cg_for = [](int t) { return t <= 2 ? 1 : 2; };
+    auto smem_for = [&](int t) {
+        return kFixedBytes + kRingBytes + (size_t)max_items * (128 * 8 * cg_for(t)) + (size_t)3 * t * stride;
+    };
     int tg = T < kMaxTok ? T : kMaxTok;
-    auto smem_for = [&](int t) { return kFixedBytes + kRingBytes + (size_t)max_items * 512 + (size_t)2 * t * stride; };
-    while (tg > 1 && smem_for(tg) > (size_t)smem_optin[dev & 63]) --tg;
-    if (smem_for(tg) > (size_t)smem_optin[dev & 63]) return NQ_ERR_UNSUPPORTED;
+    while (tg > 1 && smem_for(tg) > (size_t)smem_limit) --tg;
+    if (smem_for(tg) > (size_t)smem_limit) return NQ_ERR_UNSUPPORTED;
 
     const size_t esz = 2;
     for (int t0 = 0; t0 < T; t0 += tg) {
@@ -601,8 +671,9 @@ int nq_gemv_group_fwd(const nq_linear_desc* d, int n_linears, int T, int dtype, 
             b.vec = (L.R % 8 == 0);  // the intermediate lives in the 256-byte aligned scratch
         }
         void* args[] = {&P};
-        NQ_CUDA_TRY(cudaLaunchCooperativeKernel((const void*)gemv_group_kernel, dim3(grid), dim3(kGemvThreads),
-                                                args, smem_for(tn), as_stream(stream)));
+        const void* fn = cg_for(tn) == 1 ? (const void*)gemv_group_kernel<1> : (const void*)gemv_group_kernel<2>;
+        NQ_CUDA_TRY(cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(kGemvThreads), args, smem_for(tn),
+                                                as_stream(stream)));
     }
     return NQ_OK;
 }
