@@ -171,6 +171,49 @@ int nq_gemv_group_fwd(const nq_linear_desc* linears_host, int n_linears, int T, 
  * (the scratch must then be zeroed again before reuse). */
 int nq_scratch_status(const void* scratch, nq_stream_t stream);
 
+/* ------------------------------------------------------------------------ *
+ * Prefill GEMM (many tokens) on tcgen05 / tensor memory
+ * ------------------------------------------------------------------------ */
+
+/* Bytes of scratch nq_gemm_fwd needs: a 256-byte header (status word at byte 8,
+ * the same place as in the GEMV scratch) followed by the rank-R intermediate
+ * t[T, R] in the I/O dtype. */
+size_t nq_gemm_scratch_bytes(int T, int N, int R, int M);
+
+/* y[T, M] = s_out * (U . (s_mid * (V . (s_in * x[T, N])))) as two tensor-core
+ * GEMMs.  v_tiles / u_tiles are the same tile layout the GEMV reads.  The
+ * intermediate is rounded to the I/O dtype between the stages, accumulation is
+ * fp32, the products x * (+-s_in) are exact.  Requires N % 8 == 0, R % 8 == 0,
+ * 16-byte aligned x, y, scales and scratch.  The scratch header must be zeroed
+ * once by the caller; a device-side wait that gives up sets its status word
+ * (nq_scratch_status).
+ * replaces: marlin_nanoquant_cuda, src/nanoquant/kernel/cuda/gemm.cpp:112-122
+ * (schema src/nanoquant/kernel/pybind.cpp:99-104) */
+int nq_gemm_fwd(const void* x, const void* s_in, const void* v_tiles, const void* s_mid,
+                const void* u_tiles, const void* s_out, void* y,
+                void* scratch, size_t scratch_bytes,
+                int T, int N, int R, int M, int dtype, nq_stream_t stream);
+
+/* One stage: y[T, Nout] = s_out * (W . (s_in * x[T, K])) with W [Nout, K] in the
+ * tile layout; s_in and s_out may be NULL.  `status_word` points at a zeroed
+ * 16-byte device area (a scratch header works) whose third word receives a
+ * timeout status.
+ * replaces: marlin_onebit_cuda, src/nanoquant/kernel/cuda/gemm.cpp:59-98
+ * (schema src/nanoquant/kernel/pybind.cpp:93-98) */
+int nq_onebit_gemm_fwd(const void* x, const void* tiles, const void* s_in, const void* s_out,
+                       void* y, void* status_word, int T, int K, int Nout, int dtype,
+                       nq_stream_t stream);
+
+/* Token-count dispatch the reference leaves to the caller's `kernel_type`:
+ * the GEMV for T <= nq_gemv_max_tokens(), the GEMM above.  Scratch must satisfy
+ * nq_linear_scratch_bytes(). */
+int nq_gemv_max_tokens(void);
+size_t nq_linear_scratch_bytes(int T, int N, int R, int M);
+int nq_linear_fwd(const void* x, const void* s_in, const void* v_tiles, const void* s_mid,
+                  const void* u_tiles, const void* s_out, void* y,
+                  void* scratch, size_t scratch_bytes,
+                  int T, int N, int R, int M, int dtype, nq_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,493 @@
+// Prefill GEMM for the binary low-rank linear on the 5th-generation tensor cores.
+//
+//   stage 1:  t[T, R] = ((x * s_in) . V^T) * s_mid        (t kept in the I/O dtype)
+//   stage 2:  y[T, M] = (t . U^T) * s_out
+//
+// Each stage is one launch of the same kernel: Out[T, Nout] = (A[T, K] . W[Nout, K]^T) * post,
+// where W = +-pre[k] comes from packed sign bits.  One CTA computes a 128-token x
+// 128-row output tile:
+//
+//   warp 0      TMA producer: the activation tile [128 tokens x 64 k] through a tensor map
+//               (cp.async.bulk.tensor, 128-byte swizzle), the packed sign bits of the
+//               128 weight rows (1-D bulk copies of the GEMV tile layout, one 256-column
+//               chunk = 4 KB at a time) and the 64 input scales of the k block.
+//   warps 2-5   expand the bits to +-pre[k] in bf16/fp16 directly in the K-major
+//               128-byte-swizzled layout the MMA reads (the product x * (+-s_in) is then
+//               exact inside the MMA; pre-scaling x would round it), fence.proxy.async,
+//               signal "weights ready"; afterwards the same warps run the epilogue.
+//   warp 1      one thread issues tcgen05.mma (M = 128 tokens, N = 128 rows, K = 16,
+//               kind::f16, fp32 accumulator in tensor memory) and commits the stage's
+//               buffers back to the producer with tcgen05.commit.
+//   epilogue    tcgen05.ld of the accumulator (lane = token, column = output row),
+//               * post[n], saturate, convert, 16-byte stores.
+//
+// The packed operand is the same tile layout the decode GEMV streams (nq_rows_to_tiles),
+// so a layer keeps one copy of its weights for both kernels.  No TMA multicast is used.
+// Every mbarrier wait is bounded; on expiry a status word is set, the CTA drains and
+// frees its tensor memory.
+//
+// replaces: src/nanoquant/kernel/cuda/gemm_kernel.cu:278-791 (Marlin-derived mma.sync
+// kernel with register-level dequantisation) and src/nanoquant/kernel/cuda/gemm.cpp:59-122
+// of the reference.
+#include <cuda.h>
+
+#include <cstring>
+
+#include "nq_common.cuh"
+
+namespace nq {
+
+constexpr int kBM = 128;            // tokens per tile (MMA M, tensor-memory lanes)
+constexpr int kBN = 128;            // weight rows per tile (MMA N, tensor-memory columns)
+constexpr int kBK = 64;             // k per pipeline stage: 128 bytes of bf16 = one swizzle row
+constexpr int kGemmStages = 3;
+constexpr int kGemmThreads = 192;   // warp 0 producer, warp 1 MMA, warps 2..5 expand + epilogue
+constexpr int kExpandThreads = 128;
+constexpr int kTileBytes = kBM * kBK * 2;          // 16 KB, both operand tiles
+constexpr int kBitsSlotBytes = (kBN / 16) * 512;   // 4 KB: 8 row groups x one 256-column chunk
+constexpr int kPreBytes = kBK * 2;                 // 128 B of input scales per stage
+constexpr unsigned kWaitLimit = 1u << 26;
+
+// shared memory map (offsets from a 1024-byte aligned base)
+constexpr int kOffA = 0;
+constexpr int kOffW = kOffA + kGemmStages * kTileBytes;
+constexpr int kOffBits = kOffW + kGemmStages * kTileBytes;
+constexpr int kOffPre = kOffBits + 2 * kBitsSlotBytes;
+constexpr int kOffBar = kOffPre + kGemmStages * kPreBytes;
+constexpr int kNumBars = 3 * kGemmStages + 2 + 2 + 1;  // full, wready, empty, bits_full, bits_empty, accum
+constexpr int kOffMisc = kOffBar + kNumBars * 8;       // tmem base address, abort flag
+constexpr int kGemmSmemBytes = kOffMisc + 16 + 1024;   // + slack for the 1024-byte alignment
+
+struct GemmParams {
+    CUtensorMap map_a;     // activations [T, K], box 64 x 128, 128-byte swizzle
+    const uint4* tiles;    // packed weights, GEMV tile layout [row_groups][chunks][32]
+    const void* pre;       // [K] input scales (I/O dtype) or nullptr (weights are +-1)
+    const void* post;      // [Nout] output scales (I/O dtype) or nullptr
+    void* out;             // [T, ld_out] I/O dtype
+    long long ld_out;
+    unsigned* status;      // device status word (0 = ok)
+    int T, K, Nout;
+    int chunks, row_groups;
+    int is_bf16;
+    int saturate;          // apply the reference's output saturation bounds
+};
+
+// ---------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Bounded wait on an mbarrier phase.  Returns false when the limit expired or another
+// thread of the CTA already gave up; the caller then leaves its loop.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          unsigned* status) {
+    for (unsigned i = 0; i < kWaitLimit; ++i) {
+        if (mbar_test(bar, parity)) return true;
+        if ((i & 1023u) == 1023u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    atomicExch(status, (unsigned)(-NQ_ERR_TIMEOUT));
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// K-major, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    const uint32_t lo = ((smem_addr >> 4) & 0x3FFFu) | (1u << 16);          // start address, LBO = 1 (unused)
+    const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);             // SBO, version 1, SWIZZLE_128B
+    return ((uint64_t)hi << 32) | lo;
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                         uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// ---------------------------------------------------------------------------
+// the kernel: one 128 x 128 output tile per CTA
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(kGemmThreads) gemm_stage_kernel(const __grid_constant__ GemmParams P) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    const uint32_t sbase = smem_u32(smem);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * kBN;   // first weight row of the tile
+    const int m0 = blockIdx.y * kBM;   // first token of the tile
+    const int nkb = (P.K + kBK - 1) / kBK;
+
+    auto bar_full = [&](int s) { return sbase + kOffBar + 8 * s; };
+    auto bar_wready = [&](int s) { return sbase + kOffBar + 8 * (kGemmStages + s); };
+    auto bar_empty = [&](int s) { return sbase + kOffBar + 8 * (2 * kGemmStages + s); };
+    auto bar_bits_full = [&](int b) { return sbase + kOffBar + 8 * (3 * kGemmStages + b); };
+    auto bar_bits_empty = [&](int b) { return sbase + kOffBar + 8 * (3 * kGemmStages + 2 + b); };
+    const uint32_t bar_accum = sbase + kOffBar + 8 * (3 * kGemmStages + 4);
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + kOffMisc);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kOffMisc + 4);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kGemmStages; ++s) {
+            mbar_init(bar_full(s), 1);
+            mbar_init(bar_wready(s), kExpandThreads);
+            mbar_init(bar_empty(s), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(bar_bits_full(b), 1);
+            mbar_init(bar_bits_empty(b), kExpandThreads);
+        }
+        mbar_init(bar_accum, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    // input-scale slots start finite: a partial last k block leaves older (finite) values behind
+    for (int i = threadIdx.x; i < kGemmStages * kPreBytes / 4; i += kGemmThreads)
+        reinterpret_cast<uint32_t*>(smem + kOffPre)[i] = 0;
+    if (warp == 1) {  // tensor-memory allocation: 128 fp32 columns, by one whole warp
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(const_cast<uint32_t*>(tmem_slot))), "r"((uint32_t)kBN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    int nrg = P.row_groups - (n0 >> 4);          // row groups of this tile that exist
+    nrg = nrg > kBN / 16 ? kBN / 16 : nrg;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ producer
+        if (lane == 0) {
+            for (int kb = 0; kb < nkb; ++kb) {
+                const int s = kb % kGemmStages;
+                const uint32_t ph = (kb / kGemmStages) & 1;
+                if (!mbar_wait(bar_empty(s), ph ^ 1, abort_flag, P.status)) break;
+                if ((kb & 3) == 0) {   // a new 256-column chunk of sign bits
+                    const int c = kb >> 2, b = c & 1;
+                    if (!mbar_wait(bar_bits_empty(b), ((c >> 1) & 1) ^ 1, abort_flag, P.status)) break;
+                    mbar_expect_tx(bar_bits_full(b), (uint32_t)nrg * 512u);
+                    for (int rg = 0; rg < nrg; ++rg)
+                        bulk_load(sbase + kOffBits + b * kBitsSlotBytes + rg * 512,
+                                  P.tiles + ((size_t)((n0 >> 4) + rg) * P.chunks + c) * 32, 512u, bar_bits_full(b));
+                }
+                int pre_bytes = 0;
+                if (P.pre) {
+                    const int left = P.K - kb * kBK;
+                    pre_bytes = (left < kBK ? left : kBK) * 2;
+                }
+                mbar_expect_tx(bar_full(s), (uint32_t)(kTileBytes + pre_bytes));
+                tma_load_2d(sbase + kOffA + s * kTileBytes, &P.map_a, kb * kBK, m0, bar_full(s));
+                if (pre_bytes)
+                    bulk_load(sbase + kOffPre + s * kPreBytes, static_cast<const char*>(P.pre) + (size_t)kb * kBK * 2,
+                              (uint32_t)pre_bytes, bar_full(s));
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const uint32_t fmt = P.is_bf16 ? 1u : 0u;
+            const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(kBN >> 3) << 17) |
+                                   ((uint32_t)(kBM >> 4) << 24);
+            bool ok = true;
+            for (int kb = 0; kb < nkb && ok; ++kb) {
+                const int s = kb % kGemmStages;
+                const uint32_t ph = (kb / kGemmStages) & 1;
+                ok = mbar_wait(bar_wready(s), ph, abort_flag, P.status) &&
+                     mbar_wait(bar_full(s), ph, abort_flag, P.status);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t a_addr = sbase + kOffA + s * kTileBytes, w_addr = sbase + kOffW + s * kTileBytes;
+#pragma unroll
+                for (int k4 = 0; k4 < kBK / 16; ++k4)
+                    umma_f16(tmem_base, umma_desc(a_addr + k4 * 32), umma_desc(w_addr + k4 * 32), idesc,
+                             (kb | k4) != 0 ? 1u : 0u);
+                umma_commit(bar_empty(s));   // the stage's buffers are free once these MMAs have read them
+            }
+            if (ok) umma_commit(bar_accum);
+        }
+    } else {
+        // ------------------------------------------------------------ expand warps
+        const int tu = threadIdx.x - 64;   // 0..127
+        const uint32_t one2 = P.is_bf16 ? 0x3F803F80u : 0x3C003C00u;
+        bool ok = true;
+        for (int kb = 0; kb < nkb && ok; ++kb) {
+            const int s = kb % kGemmStages;
+            const uint32_t ph = (kb / kGemmStages) & 1;
+            const int c = kb >> 2, b = c & 1, sub = kb & 3;
+            if (sub == 0) ok = mbar_wait(bar_bits_full(b), (c >> 1) & 1, abort_flag, P.status);
+            ok = ok && mbar_wait(bar_full(s), ph, abort_flag, P.status);
+            if (!ok) break;
+            const uint4* bits = reinterpret_cast<const uint4*>(smem + kOffBits + b * kBitsSlotBytes);
+            const uint2* pre2 = reinterpret_cast<const uint2*>(smem + kOffPre + s * kPreBytes);
+            unsigned char* wt = smem + kOffW + s * kTileBytes;
+#pragma unroll
+            for (int it = 0; it < 2; ++it) {
+                const int task = tu + it * kExpandThreads;   // (row group, lane of the GEMV tile)
+                const int rg = task >> 5, l = task & 31, g = l >> 2, q = l & 3;
+                const uint4 w4 = bits[rg * 32 + l];
+                const uint32_t comp[4] = {w4.x, w4.y, w4.z, w4.w};   // {row g h0, row g+8 h0, row g h1, row g+8 h1}
+#pragma unroll
+                for (int jj = 0; jj < 2; ++jj) {
+                    const int j = 2 * sub + jj;                      // class of the 32 columns
+#pragma unroll
+                    for (int ci = 0; ci < 4; ++ci) {
+                        const int h = ci >> 1, row = 16 * rg + g + 8 * (ci & 1);
+                        const uint32_t u = (comp[ci] << (7 - j)) & 0x80808080u;   // bit 8b+j -> sign of byte b
+                        uint32_t v0 = __byte_perm(u, 0u, 0x1404);                 // columns 4q, 4q+1
+                        uint32_t v1 = __byte_perm(u, 0u, 0x3424);                 // columns 4q+2, 4q+3
+                        const int kl = 32 * jj + 16 * h + 4 * q;                  // first of the four columns
+                        if (P.pre) {
+                            const uint2 pp = pre2[kl >> 2];
+                            v0 ^= pp.x; v1 ^= pp.y;
+                        } else {
+                            v0 ^= one2; v1 ^= one2;
+                        }
+                        const int c16 = kl >> 3;                                  // 16-byte chunk of the 128-byte row
+                        *reinterpret_cast<uint2*>(wt + row * 128 + ((c16 ^ (row & 7)) << 4) + 8 * (q & 1)) =
+                            make_uint2(v0, v1);
+                    }
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the MMA
+            mbar_arrive(bar_wready(s));
+            if (sub == 3 || kb + 1 == nkb) mbar_arrive(bar_bits_empty(b));
+        }
+        // ------------------------------------------------------------ epilogue
+        if (ok) ok = mbar_wait(bar_accum, 0, abort_flag, P.status);
+        if (ok) {
+            tc_fence_after();
+            const int lq = warp & 3;                 // tensor-memory lane quarter this warp may read
+            const int row = m0 + 32 * lq + lane;     // token
+#pragma unroll 1
+            for (int c0 = 0; c0 < kBN; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((uint32_t)(32 * lq) << 16) + (uint32_t)c0, r);
+                if (row < P.T && n0 + c0 < P.Nout) {
+                    uint32_t packed[16];
+#pragma unroll
+                    for (int e = 0; e < 32; e += 2) {
+                        float v[2];
+#pragma unroll
+                        for (int d = 0; d < 2; ++d) {
+                            const int n = n0 + c0 + e + d;
+                            float f = __uint_as_float(r[e + d]);
+                            if (P.post && n < P.Nout) {
+                                f *= P.is_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(P.post)[n])
+                                               : __half2float(static_cast<const __half*>(P.post)[n]);
+                            }
+                            if (P.saturate) {
+                                const float lim = P.is_bf16 ? 3.3895313892515355e+38f : 64504.0f;
+                                f = fminf(fmaxf(f, -lim), lim);
+                            }
+                            v[d] = f;
+                        }
+                        if (P.is_bf16) {
+                            const __nv_bfloat162 h2 = __floats2bfloat162_rn(v[0], v[1]);
+                            packed[e >> 1] = *reinterpret_cast<const uint32_t*>(&h2);
+                        } else {
+                            const __half2 h2 = __floats2half2_rn(v[0], v[1]);
+                            packed[e >> 1] = *reinterpret_cast<const uint32_t*>(&h2);
+                        }
+                    }
+                    unsigned char* dst = static_cast<unsigned char*>(P.out) + ((size_t)row * P.ld_out + n0 + c0) * 2;
+                    if (n0 + c0 + 32 <= P.Nout && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+#pragma unroll
+                        for (int v4 = 0; v4 < 4; ++v4)
+                            reinterpret_cast<uint4*>(dst)[v4] =
+                                make_uint4(packed[4 * v4], packed[4 * v4 + 1], packed[4 * v4 + 2], packed[4 * v4 + 3]);
+                    } else {
+                        for (int e = 0; e < 32 && n0 + c0 + e < P.Nout; ++e)
+                            reinterpret_cast<uint16_t*>(dst)[e] = (uint16_t)(packed[e >> 1] >> (16 * (e & 1)));
+                    }
+                }
+            }
+        }
+    }
+    // On an expired wait, give this CTA's bulk copies in flight a bounded time to land before
+    // shared memory is released.
+    if (*abort_flag && threadIdx.x == 0) {
+        for (unsigned i = 0; i < (1u << 20); ++i) __nanosleep(64);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kBN)
+                     : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point lookup: no link against libcuda.
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// One stage: out[T, Nout] = (a[T, K] . W^T) * post, W from `tiles` and `pre`.
+static int launch_stage(const void* a, long long lda, const void* tiles, const void* pre, const void* post,
+                        void* out, long long ld_out, int T, int K, int Nout, int dtype, int saturate,
+                        unsigned* status, cudaStream_t stream) {
+    if (!aligned16(a) || (lda % 8) != 0 || (K % 8) != 0) return NQ_ERR_ALIGN;   // TMA: 16-byte base and stride
+    if (pre && !aligned16(pre)) return NQ_ERR_ALIGN;
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return NQ_ERR_UNSUPPORTED;
+    GemmParams P;
+    memset(&P, 0, sizeof(P));
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)T};
+    const cuuint64_t strides[1] = {(cuuint64_t)lda * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)kBM};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = enc(&P.map_a, dtype == NQ_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                           2, const_cast<void*>(a), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return NQ_ERR_UNSUPPORTED;
+    P.tiles = static_cast<const uint4*>(tiles);
+    P.pre = pre;
+    P.post = post;
+    P.out = out;
+    P.ld_out = ld_out;
+    P.status = status;
+    P.T = T; P.K = K; P.Nout = Nout;
+    P.chunks = (K + 255) / 256;
+    P.row_groups = (Nout + 15) / 16;
+    P.is_bf16 = dtype == NQ_BF16;
+    P.saturate = saturate;
+    static bool attr_set[64];
+    int dev = 0;
+    NQ_CUDA_TRY(cudaGetDevice(&dev));
+    if (!attr_set[dev & 63]) {
+        NQ_CUDA_TRY(cudaFuncSetAttribute(gemm_stage_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes));
+        attr_set[dev & 63] = true;
+    }
+    const dim3 grid((Nout + kBN - 1) / kBN, (T + kBM - 1) / kBM);
+    gemm_stage_kernel<<<grid, kGemmThreads, kGemmSmemBytes, stream>>>(P);
+    NQ_LAUNCH_CHECK();
+    return NQ_OK;
+}
+
+}  // namespace nq
+
+using namespace nq;
+
+extern "C" {
+
+size_t nq_gemm_scratch_bytes(int T, int N, int R, int M) {
+    if (T <= 0 || N <= 0 || R <= 0 || M <= 0) return 0;
+    return 256 + ((size_t)T * (size_t)R * 2 + 255) / 256 * 256;
+}
+
+int nq_onebit_gemm_fwd(const void* x, const void* tiles, const void* s_in, const void* s_out, void* y,
+                       void* status_word, int T, int K, int Nout, int dtype, nq_stream_t stream) {
+    if (!x || !tiles || !y || !status_word) return NQ_ERR_NULL;
+    if (T <= 0 || K <= 0 || Nout <= 0) return NQ_ERR_SHAPE;
+    if (dtype != NQ_F16 && dtype != NQ_BF16) return NQ_ERR_DTYPE;
+    if (!aligned16(tiles)) return NQ_ERR_ALIGN;
+    return launch_stage(x, K, tiles, s_in, s_out, y, Nout, T, K, Nout, dtype, 1,
+                        static_cast<unsigned*>(status_word) + 2, as_stream(stream));
+}
+
+int nq_gemm_fwd(const void* x, const void* s_in, const void* v_tiles, const void* s_mid, const void* u_tiles,
+                const void* s_out, void* y, void* scratch, size_t scratch_bytes, int T, int N, int R, int M,
+                int dtype, nq_stream_t stream) {
+    if (!x || !s_in || !v_tiles || !u_tiles || !s_out || !y || !scratch) return NQ_ERR_NULL;
+    if (T <= 0 || N <= 0 || R <= 0 || M <= 0) return NQ_ERR_SHAPE;
+    if (dtype != NQ_F16 && dtype != NQ_BF16) return NQ_ERR_DTYPE;
+    if (N % 8 || R % 8) return NQ_ERR_SHAPE;
+    if (!aligned16(scratch) || !aligned16(v_tiles) || !aligned16(u_tiles)) return NQ_ERR_ALIGN;
+    if (scratch_bytes < nq_gemm_scratch_bytes(T, N, R, M)) return NQ_ERR_SCRATCH;
+    unsigned* status = static_cast<unsigned*>(scratch) + 2;   // same word as the GEMV header's status
+    void* t = static_cast<char*>(scratch) + 256;
+    int st = launch_stage(x, N, v_tiles, s_in, s_mid, t, R, T, N, R, dtype, 0, status, as_stream(stream));
+    if (st != NQ_OK) return st;
+    return launch_stage(t, R, u_tiles, nullptr, s_out, y, M, T, R, M, dtype, 1, status, as_stream(stream));
+}
+
+int nq_gemv_max_tokens(void) { return 8; }
+
+size_t nq_linear_scratch_bytes(int T, int N, int R, int M) {
+    const size_t a = nq_gemv_scratch_bytes(T, N, R, M), b = nq_gemm_scratch_bytes(T, N, R, M);
+    return a > b ? a : b;
+}
+
+int nq_linear_fwd(const void* x, const void* s_in, const void* v_tiles, const void* s_mid, const void* u_tiles,
+                  const void* s_out, void* y, void* scratch, size_t scratch_bytes, int T, int N, int R, int M,
+                  int dtype, nq_stream_t stream) {
+    if (T <= nq_gemv_max_tokens() || (N % 8) || (R % 8))
+        return nq_gemv_fwd(x, s_in, v_tiles, s_mid, u_tiles, s_out, y, scratch, scratch_bytes, T, N, R, M, dtype,
+                           stream);
+    return nq_gemm_fwd(x, s_in, v_tiles, s_mid, u_tiles, s_out, y, scratch, scratch_bytes, T, N, R, M, dtype, stream);
+}
+
+}  // extern "C"
