@@ -13,7 +13,7 @@ from __future__ import annotations
 import torch
 import torch.nn as nn
 
-from ..kernel.utils import (binary_packer, get_kernel_function, pack_tiles, reorder_packed)
+from ..kernel.utils import (binary_packer, get_kernel_function, marlin_nanoquant_packer, pack_tiles)
 
 # tuning arguments the reference passes to its GEMV (modules/linear.py:176-185); validated, then unused
 _GEMV_KWARGS = {
@@ -112,7 +112,17 @@ class NanoQuantLinear(nn.Module):
             self.kernel_forward = get_kernel_function("nanoquant", dtype, kernel_type="dynamic")
             self.kernel_kwargs = dict(_GEMV_KWARGS)
         else:
-            raise NotImplementedError("gemm kernel path is prepared by nanoquant_b200.modules.linear in a later step")
+            # same operands as the reference (Marlin-fragment words + permuted scales, reference
+            # modules/linear.py:186-202); the operator converts them once to the kernels' tile layout
+            if self.scale_mid is None:
+                self.scale_mid = nn.Parameter(torch.ones(self.rank, device=self.scale_pre.device, dtype=dtype),
+                                              requires_grad=False)
+            (self.V_int8, self.U_int8, self.s1, self.s2, self.s3, self.workspace) = marlin_nanoquant_packer(
+                self.V.to(torch.int8).T, self.U.to(torch.int8).T, self.scale_pre, self.scale_mid, self.scale_post)
+            for key in ("U", "V", "scale_pre", "scale_mid", "scale_post"):
+                delattr(self, key)
+            import binary_kernels  # noqa: F401
+            self.kernel_forward = torch.ops.binary_kernels.marlin_nanoquant_forward
 
     def load_packed(self, V_packed, V_shape, U_packed, U_shape, scale_pre, scale_post, scale_mid=None,
                     dtype=torch.bfloat16, device="cuda"):

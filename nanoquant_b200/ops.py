@@ -152,7 +152,7 @@ def _nanoquant_dyn_forward_cuda(x, scale_g, Ubits, scale_l, Vbits, scale_h,
     v_tiles = as_tiles(Ubits, N)
     u_tiles = as_tiles(Vbits, R)
     x2 = x.view(1, N) if x.dim() == 1 else x
-    y = gemv_forward(x2, scale_g, v_tiles, scale_l, u_tiles, scale_h, R)
+    y = linear_forward(x2, scale_g, v_tiles, scale_l, u_tiles, scale_h, R)
     return y.squeeze(0) if x.dim() == 1 else y
 
 
@@ -160,6 +160,129 @@ def _nanoquant_dyn_forward_fake(x, scale_g, Ubits, scale_l, Vbits, scale_h, *arg
     shape = list(x.shape)
     shape[-1] = scale_h.size(0)
     return x.new_empty(shape)
+
+
+def linear_forward(x: torch.Tensor, s_in: torch.Tensor, v_tiles: torch.Tensor, s_mid: Optional[torch.Tensor],
+                   u_tiles: torch.Tensor, s_out: torch.Tensor, R: int) -> torch.Tensor:
+    """``nq_linear_fwd``: GEMV for few tokens, tcgen05 GEMM above; ``x`` is ``[T, N]``."""
+    T, N = x.shape
+    M = s_out.size(0)
+    y = torch.empty((T, M), dtype=x.dtype, device=x.device)
+    if T == 0:
+        return y
+    L = _lib.lib()
+    scratch = scratch_for(x.device, L.nq_linear_scratch_bytes(T, N, R, M))
+    with torch.cuda.device(x.device):
+        st = L.nq_linear_fwd(x.data_ptr(), s_in.data_ptr(), v_tiles.data_ptr(),
+                             s_mid.data_ptr() if s_mid is not None else None,
+                             u_tiles.data_ptr(), s_out.data_ptr(), y.data_ptr(),
+                             scratch.data_ptr(), scratch.numel(), T, N, R, M, _dtype_id(x),
+                             torch.cuda.current_stream(x.device).cuda_stream)
+    _lib.check(st, "nq_linear_fwd")
+    return y
+
+
+# --- Marlin-layout operands -----------------------------------------------------------------
+
+def _marlin_as_tiles(B: torch.Tensor) -> torch.Tensor:
+    """Marlin-fragment words ``[in/16, out/2]`` (what the reference's ``pack_binary_marlin``
+    produces) -> tile layout of the kernels here, cached on the tensor object."""
+    cached = getattr(B, "_nq_tiles", None)
+    if cached is not None and cached[0] == B._version:
+        return cached[1]
+    in_f, out_f = B.size(0) * 16, B.size(1) * 2
+    if in_f % 32 or out_f % 64:
+        raise RuntimeError("Problem shape incompatible")
+    L = _lib.lib()
+    rows = torch.empty((out_f, in_f // 32), dtype=torch.int32, device=B.device)
+    with torch.cuda.device(B.device):
+        _lib.check(L.nq_marlin_to_rows(B.data_ptr(), rows.data_ptr(), out_f, in_f, _lib.NQ_LSB_FIRST,
+                                       torch.cuda.current_stream(B.device).cuda_stream), "nq_marlin_to_rows")
+    tiles = ku.pack_tiles(rows, (out_f, in_f), "lsb_first")
+    B._nq_tiles = (B._version, tiles)
+    return tiles
+
+
+def _unpermuted_scale(s: Optional[torch.Tensor], kind: int) -> Optional[torch.Tensor]:
+    """Undo the Marlin scale permutation (cached on the tensor object)."""
+    if s is None:
+        return None
+    cached = getattr(s, "_nq_plain", None)
+    if cached is not None and cached[0] == s._version:
+        return cached[1]
+    plain = ku._permute_scale(s.contiguous(), kind, inverse=True)
+    s._nq_plain = (s._version, plain)
+    return plain
+
+
+MARLIN_MIN_MAX_PAR = 32  # reference: src/nanoquant/kernel/cuda/gemm.cpp:33
+
+
+def _marlin_checks(A, B, s_in, s_out, workspace):
+    # reference: marlin_onebit_check_and_alloc, src/nanoquant/kernel/cuda/gemm.cpp:36-56
+    prob_n, prob_k = B.size(1) * 2, A.size(1)
+    if prob_k != B.size(0) * 16:
+        raise RuntimeError("k dimension mismatch")
+    if s_in is not None and s_in.size(0) != prob_k:
+        raise RuntimeError("s_in size mismatch")
+    if s_out is not None and s_out.size(0) != prob_n:
+        raise RuntimeError("s_out size mismatch")
+    if workspace.numel() < prob_n // 128 * MARLIN_MIN_MAX_PAR:
+        raise RuntimeError("workspace too small")
+    if A.dtype not in (torch.float16, torch.bfloat16):
+        raise RuntimeError("Unsupported dtype: Marlin only supports Half and BFloat16")
+    return prob_n, prob_k
+
+
+def _status_words(device: torch.device) -> torch.Tensor:
+    return scratch_for(device, 256)
+
+
+def _marlin_onebit_forward_cuda(x, weight, scale_g, scale_h, workspace):
+    prob_n, prob_k = _marlin_checks(x, weight, scale_g, scale_h, workspace)
+    x = x.contiguous()
+    tiles = _marlin_as_tiles(weight)
+    s_in = _unpermuted_scale(scale_g, 0)
+    s_out = _unpermuted_scale(scale_h, 1)
+    T = x.size(0)
+    y = torch.empty((T, prob_n), dtype=x.dtype, device=x.device)
+    if T == 0:
+        return y
+    L = _lib.lib()
+    with torch.cuda.device(x.device):
+        st = L.nq_onebit_gemm_fwd(x.data_ptr(), tiles.data_ptr(),
+                                  s_in.data_ptr() if s_in is not None else None,
+                                  s_out.data_ptr() if s_out is not None else None,
+                                  y.data_ptr(), _status_words(x.device).data_ptr(), T, prob_k, prob_n,
+                                  _dtype_id(x), torch.cuda.current_stream(x.device).cuda_stream)
+    _lib.check(st, "nq_onebit_gemm_fwd")
+    return y
+
+
+def _marlin_onebit_forward_fake(x, weight, scale_g, scale_h, workspace):
+    return x.new_empty((x.size(0), weight.size(1) * 2))
+
+
+def _marlin_nanoquant_forward_cuda(x, weight_u, weight_v, scale_g, scale_l, scale_h, workspace):
+    # `weight_u` is the FIRST stage (module V), `weight_v` the second (reference gemm.cpp:112-122)
+    R, N = _marlin_checks(x, weight_u, scale_g, scale_l, workspace)
+    if scale_g is None or scale_h is None:
+        raise RuntimeError("scale_g and scale_h are required")
+    M = weight_v.size(1) * 2
+    if weight_v.size(0) * 16 != R:
+        raise RuntimeError("k dimension mismatch")
+    if scale_h.size(0) != M:
+        raise RuntimeError("s_out size mismatch")
+    if workspace.numel() < M // 128 * MARLIN_MIN_MAX_PAR:
+        raise RuntimeError("workspace too small")
+    x = x.contiguous()
+    return linear_forward(x, _unpermuted_scale(scale_g, 0), _marlin_as_tiles(weight_u),
+                          _unpermuted_scale(scale_l, 1), _marlin_as_tiles(weight_v),
+                          _unpermuted_scale(scale_h, 1), R)
+
+
+def _marlin_nanoquant_forward_fake(x, weight_u, weight_v, scale_g, scale_l, scale_h, workspace):
+    return x.new_empty((x.size(0), weight_v.size(1) * 2))
 
 
 def define_ops() -> None:
@@ -175,4 +298,15 @@ def define_ops() -> None:
         "int num_pipeline_stage1=2, int num_pipeline_stage2=2) -> Tensor")
     torch.library.impl("binary_kernels::nanoquant_dyn_forward", "CUDA")(_nanoquant_dyn_forward_cuda)
     torch.library.register_fake("binary_kernels::nanoquant_dyn_forward")(_nanoquant_dyn_forward_fake)
+    torch.library.define(
+        "binary_kernels::marlin_onebit_forward",
+        "(Tensor x, Tensor weight, Tensor? scale_g, Tensor? scale_h, Tensor(a!) workspace) -> Tensor")
+    torch.library.impl("binary_kernels::marlin_onebit_forward", "CUDA")(_marlin_onebit_forward_cuda)
+    torch.library.register_fake("binary_kernels::marlin_onebit_forward")(_marlin_onebit_forward_fake)
+    torch.library.define(
+        "binary_kernels::marlin_nanoquant_forward",
+        "(Tensor x, Tensor weight_u, Tensor weight_v, Tensor? scale_g, Tensor? scale_l, Tensor? scale_h, "
+        "Tensor(a!) workspace) -> Tensor")
+    torch.library.impl("binary_kernels::marlin_nanoquant_forward", "CUDA")(_marlin_nanoquant_forward_cuda)
+    torch.library.register_fake("binary_kernels::marlin_nanoquant_forward")(_marlin_nanoquant_forward_fake)
     _DEFINED = True

@@ -1,0 +1,173 @@
+"""Prefill GEMM (tcgen05) through the reference's Marlin-layout operators and through the C ABI,
+against the fp64 oracle on the same seeded inputs."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import nanoquant_oracle as oc
+from tests.util import TOL, exact_np, half2_bits, make_layer
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    import binary_kernels  # noqa: F401
+    return torch.ops.binary_kernels
+
+
+def marlin_operands(L, dtype):
+    """Operands exactly as the reference's fused Marlin packer lays them out (numpy oracle of it)."""
+    npdt = np.float16
+    to_np = lambda t: t.float().cpu().numpy().astype(np.float32)
+    # permutations act on positions only: run them on float32 copies and convert back
+    Vb, Ub, s1, s2, s3, ws = oc.pack_marlin_fused(np.ascontiguousarray(L["V"].T), np.ascontiguousarray(L["U"].T),
+                                                   to_np(L["s_pre"]), to_np(L["s_mid"]), to_np(L["s_post"]))
+    dev = L["x"].device
+    t = lambda a, d=dtype: torch.from_numpy(np.ascontiguousarray(a)).to(d).to(dev)
+    return (t(Vb, torch.int32), t(Ub, torch.int32), t(s1), t(s2), t(s3), t(ws, torch.int32))
+
+
+SHAPES = [
+    (4096, 1536, 4096, 128),    # 4096 -> 4096, r = 1536, 128 tokens
+    (4096, 608, 1024, 200),     # rank padded to 768 by the Marlin packer, ragged token count
+    (4096, 2432, 12288, 512),
+    (12288, 2432, 4096, 77),
+    (4096, 2944, 11008, 256),   # a shape the reference's Marlin kernel rejects (11008 % 512 != 0)
+    (2048, 992, 2048, 2048),
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_marlin_nanoquant_forward_vs_oracle(ops, shape, dtype):
+    N, R, M, T = shape
+    L = make_layer(N, R, M, T, dtype, seed=N + R + T)
+    Vb, Ub, s1, s2, s3, ws = marlin_operands(L, dtype)
+    y = ops.marlin_nanoquant_forward(L["x"], Vb, Ub, s1, s2, s3, ws)
+    assert y.shape == (T, M) and y.dtype == dtype
+    assert oc.rel_err(exact_np(y), L["y64"]) <= TOL[dtype]
+    assert torch.equal(y, ops.marlin_nanoquant_forward(L["x"], Vb, Ub, s1, s2, s3, ws))   # deterministic
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_marlin_onebit_forward_vs_oracle(ops, dtype):
+    # one stage: y = s_out * (W . (s_in * x)), W [n, k]
+    n, k, T = 1024, 2048, 300
+    g = np.random.default_rng(5)
+    W = (g.integers(0, 2, size=(n, k), dtype=np.int8) * 2 - 1).astype(np.int8)
+    dev = "cuda"
+    s_in = ((torch.rand(k) + 0.5) * 0.01).to(dtype).to(dev)
+    s_out = ((torch.rand(n) + 0.5) * 0.01).to(dtype).to(dev)
+    x = torch.randn(T, k).to(dtype).to(dev)
+    B, si, so, wsz = oc.pack_marlin(W, s_in.float().cpu().numpy(), s_out.float().cpu().numpy())
+    t = lambda a, d=dtype: torch.from_numpy(np.ascontiguousarray(a)).to(d).to(dev)
+    ws = torch.zeros(wsz, dtype=torch.int32, device=dev)
+    y64 = ((exact_np(x) * exact_np(s_in)) @ W.astype(np.float64).T) * exact_np(s_out)
+    y = ops.marlin_onebit_forward(x, t(B, torch.int32), t(si), t(so), ws)
+    assert oc.rel_err(exact_np(y), y64) <= TOL[dtype]
+    # optional scales
+    y2 = ops.marlin_onebit_forward(x, t(B, torch.int32), None, None, ws)
+    y64b = exact_np(x) @ W.astype(np.float64).T
+    assert oc.rel_err(exact_np(y2), y64b) <= TOL[dtype]
+
+
+def test_marlin_error_behaviour(ops):
+    L = make_layer(256, 256, 128, 16, torch.float16, seed=1)
+    Vb, Ub, s1, s2, s3, ws = marlin_operands(L, torch.float16)
+    with pytest.raises(RuntimeError, match="k dimension mismatch"):
+        ops.marlin_nanoquant_forward(L["x"][:, :128].contiguous(), Vb, Ub, s1, s2, s3, ws)
+    with pytest.raises(RuntimeError, match="s_in size mismatch"):
+        ops.marlin_nanoquant_forward(L["x"], Vb, Ub, s1[:128].contiguous(), s2, s3, ws)
+    with pytest.raises(RuntimeError, match="workspace too small"):
+        ops.marlin_nanoquant_forward(L["x"], Vb, Ub, s1, s2, s3, ws[:1])
+    with pytest.raises(RuntimeError, match="Half and BFloat16"):
+        ops.marlin_nanoquant_forward(L["x"].float(), Vb, Ub, s1, s2, s3, ws)
+
+
+def test_gemv_op_routes_many_tokens_to_the_gemm(ops):
+    L = make_layer(2048, 512, 1024, 130, torch.float16, seed=3)
+    y = ops.nanoquant_dyn_forward(L["x"], L["s_pre"], half2_bits(L["V"]), L["s_mid"], half2_bits(L["U"]),
+                                  L["s_post"], num_acc_stage1=1, num_acc_stage2=1)
+    assert oc.rel_err(exact_np(y), L["y64"]) <= TOL[torch.float16]
+
+
+def test_c_abi_gemm_and_gemv_agree_at_the_dispatch_boundary():
+    from nanoquant_b200 import _lib
+    from nanoquant_b200.kernel import utils as ku
+    Lb = _lib.lib()
+    N, R, M = 1024, 256, 512
+    T = Lb.nq_gemv_max_tokens()
+    L = make_layer(N, R, M, T, torch.float16, seed=9)
+    vt = ku.pack_tiles(half2_bits(L["V"]), (R, N), "half2")
+    ut = ku.pack_tiles(half2_bits(L["U"]), (M, R), "half2")
+    st = torch.cuda.current_stream().cuda_stream
+    outs = []
+    for fn, nbytes in ((Lb.nq_gemv_fwd, Lb.nq_gemv_scratch_bytes(T, N, R, M)),
+                       (Lb.nq_gemm_fwd, Lb.nq_gemm_scratch_bytes(T, N, R, M))):
+        scratch = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+        y = torch.empty(T, M, dtype=torch.float16, device="cuda")
+        _lib.check(fn(L["x"].data_ptr(), L["s_pre"].data_ptr(), vt.data_ptr(), L["s_mid"].data_ptr(), ut.data_ptr(),
+                      L["s_post"].data_ptr(), y.data_ptr(), scratch.data_ptr(), nbytes, T, N, R, M, _lib.NQ_F16, st),
+                   "fwd")
+        assert Lb.nq_scratch_status(scratch.data_ptr(), st) == 0
+        outs.append(y)
+        assert oc.rel_err(exact_np(y), L["y64"]) <= TOL[torch.float16]
+    # two different arithmetic paths, both inside the bar: they agree to twice the bar
+    assert oc.rel_err(exact_np(outs[0]), exact_np(outs[1])) <= 2 * TOL[torch.float16]
+
+
+def test_gemm_linearity_full_size(ops):
+    # size-independent property at a full-size shape: the op is linear in x.  Doubling x doubles every
+    # fp32 partial sum exactly; only intermediate values that fall into the fp16 subnormal range may
+    # round differently, so the two results agree to well below the parity bar, not bit for bit.
+    L = make_layer(4096, 1600, 4096, 256, torch.float16, seed=11)
+    Vb, Ub, s1, s2, s3, ws = marlin_operands(L, torch.float16)
+    s2, s3 = s2 * 64, s3 * 16
+    y = ops.marlin_nanoquant_forward(L["x"], Vb, Ub, s1, s2, s3, ws)
+    y2 = ops.marlin_nanoquant_forward(L["x"] * 2, Vb, Ub, s1, s2, s3, ws)
+    assert oc.rel_err(exact_np(y2), 2 * exact_np(y)) <= 2e-4
+    assert float((y2 == y * 2).float().mean()) > 0.99
+
+
+def test_module_kernel_paths():
+    from nanoquant_b200.modules.linear import NanoQuantLinear
+    N, R, M = 512, 128, 256
+    d = oc.synth_linear(N, R, M, 3, seed=21)
+    for kernel_type, T in (("gemv", 3), ("gemm", 160)):
+        m = NanoQuantLinear(N, M, R, has_scale_mid=True).cuda()
+        with torch.no_grad():
+            m.V.copy_(torch.from_numpy(d["V"]).float())
+            m.U.copy_(torch.from_numpy(d["U"]).float())
+            m.scale_pre.copy_(torch.from_numpy(d["s_pre"]).float()[None])
+            m.scale_mid.copy_(torch.from_numpy(d["s_mid"]).float()[None])
+            m.scale_post.copy_(torch.from_numpy(d["s_post"]).float()[None])
+        with pytest.raises(RuntimeError, match="_prepare_kernel"):
+            m(torch.zeros(1, N, device="cuda"))
+        sd = m.state_dict()
+        assert np.array_equal(sd["V_packed"].cpu().numpy(), oc.pack_rows(d["V"], "lsb_first"))
+        assert tuple(sd["U_shape"].tolist()) == (M, R)
+        # the module keeps its scales in bf16 (like the reference); compare with those exact values
+        sp, sm, so = (exact_np(m.scale_pre)[0], exact_np(m.scale_mid)[0], exact_np(m.scale_post)[0])
+        m._prepare_kernel(kernel_type, torch.bfloat16)
+        x = torch.randn(2, T // 2 if T > 3 else 1, N, device="cuda").to(torch.bfloat16)
+        if T == 3:
+            x = torch.randn(3, N, device="cuda").to(torch.bfloat16)
+        y = m(x)
+        y64 = oc.forward_fp64(exact_np(x).reshape(-1, N), d["V"], d["U"], sp, sm, so)
+        assert y.shape[:-1] == x.shape[:-1] and y.shape[-1] == M
+        assert oc.rel_err(exact_np(y).reshape(-1, M), y64) <= TOL[torch.bfloat16]
+
+
+def test_module_load_packed_checkpoint_tensors():
+    from nanoquant_b200.modules.linear import NanoQuantLinear
+    N, R, M, T = 512, 160, 384, 2
+    d = oc.synth_linear(N, R, M, T, seed=4)
+    m = NanoQuantLinear(N, M, R, has_scale_mid=True)
+    tt = lambda a: torch.from_numpy(np.ascontiguousarray(a))
+    m.load_packed(tt(oc.pack_rows(d["V"], "lsb_first")), (R, N), tt(oc.pack_rows(d["U"], "lsb_first")), (M, R),
+                  tt(d["s_pre"])[None], tt(d["s_post"])[None], tt(d["s_mid"])[None], dtype=torch.float16)
+    x = tt(d["x"]).cuda()
+    y = m(x)
+    y64 = oc.forward_fp64(d["x"], d["V"], d["U"], d["s_pre"], d["s_mid"], d["s_post"])
+    assert oc.rel_err(exact_np(y), y64) <= TOL[torch.float16]
