@@ -4,14 +4,16 @@
 //   stage 2:  y[T, M] = (t . U^T) * s_out
 //
 // Each stage is one launch of the same kernel: Out[T, Nout] = (A[T, K] . W[Nout, K]^T) * post,
-// where W = +-pre[k] comes from packed sign bits.  One CTA computes a 128-token x
-// 128-row output tile:
+// where W = +-pre[k] comes from packed sign bits.  One CTA computes a (128 or 256)-token x
+// 128-row output tile, so that one expanded weight tile feeds up to two MMAs:
 //
-//   warp 0      TMA producer: the activation tile [128 tokens x 64 k] through a tensor map
+//   warp 0      TMA producer: the activation tile [128|256 tokens x 64 k] through a tensor map
 //               (cp.async.bulk.tensor, 128-byte swizzle), the packed sign bits of the
 //               128 weight rows (1-D bulk copies of the GEMV tile layout, one 256-column
-//               chunk = 4 KB at a time) and the 64 input scales of the k block.
-//   warps 2-5   expand the bits to +-pre[k] in bf16/fp16 directly in the K-major
+//               chunk = 4 KB at a time) with the 256 input scales of the chunk.
+//   warp 2      the packed sign bits of the tile's weight rows and the input scales, one 256-column
+//               chunk per step, ahead of the expand warps.
+//   warps 3-10  expand the bits to +-pre[k] in bf16/fp16 directly in the K-major
 //               128-byte-swizzled layout the MMA reads (the product x * (+-s_in) is then
 //               exact inside the MMA; pre-scaling x would round it), fence.proxy.async,
 //               signal "weights ready"; afterwards the same warps run the epilogue.
@@ -37,29 +39,38 @@
 
 namespace nq {
 
-constexpr int kBM = 128;            // tokens per tile (MMA M, tensor-memory lanes)
-constexpr int kBN = 128;            // weight rows per tile (MMA N, tensor-memory columns)
+constexpr int kBM = 128;            // tokens per MMA (MMA M, tensor-memory lanes)
 constexpr int kBK = 64;             // k per pipeline stage: 128 bytes of bf16 = one swizzle row
-constexpr int kGemmStages = 3;
-constexpr int kGemmThreads = 192;   // warp 0 producer, warp 1 MMA, warps 2..5 expand + epilogue
-constexpr int kExpandThreads = 128;
-constexpr int kTileBytes = kBM * kBK * 2;          // 16 KB, both operand tiles
-constexpr int kBitsSlotBytes = (kBN / 16) * 512;   // 4 KB: 8 row groups x one 256-column chunk
-constexpr int kPreBytes = kBK * 2;                 // 128 B of input scales per stage
-constexpr unsigned kWaitLimit = 1u << 26;
+constexpr int kGemmThreads = 352;   // warp 0 activation TMA, warp 1 MMA, warp 2 sign bits, warps 3..10 expand + epilogue
+constexpr int kExpandThreads = 256;
+constexpr int kTileBytes = kBM * kBK * 2;          // 16 KB: one 128-row operand tile
+constexpr int kPreBytes = 256 * 2;                 // input scales of one 256-column chunk
+constexpr unsigned kWaitLimit = 1u << 21;   // attempts of up to ~2 us each
 
-// shared memory map (offsets from a 1024-byte aligned base)
-constexpr int kOffA = 0;
-constexpr int kOffW = kOffA + kGemmStages * kTileBytes;
-constexpr int kOffBits = kOffW + kGemmStages * kTileBytes;
-constexpr int kOffPre = kOffBits + 2 * kBitsSlotBytes;
-constexpr int kOffBar = kOffPre + kGemmStages * kPreBytes;
-constexpr int kNumBars = 3 * kGemmStages + 2 + 2 + 1;  // full, wready, empty, bits_full, bits_empty, accum
-constexpr int kOffMisc = kOffBar + kNumBars * 8;       // tmem base address, abort flag
-constexpr int kGemmSmemBytes = kOffMisc + 16 + 1024;   // + slack for the 1024-byte alignment
+// Tile configuration: MH x 128 tokens by NH x 128 weight rows per CTA.  One expanded weight
+// tile feeds MH MMAs and one activation tile meets 128 * NH weight rows, which sets the
+// expansion work and the L2 traffic per MAC.  Shared memory map: offsets from a
+// 1024-byte aligned base.
+template <int MH, int NH>
+struct GemmCfg {
+    static constexpr int kStages = (MH * NH == 4) ? 3 : (MH * NH == 2 ? 4 : 6);
+    static constexpr int kBN = 128 * NH;                    // MMA N, tensor-memory columns per accumulator
+    static constexpr int kABytes = MH * kTileBytes;
+    static constexpr int kWBytes = NH * kTileBytes;
+    static constexpr int kBitsSlotBytes = (kBN / 16) * 512; // row groups x one 256-column chunk of sign bits
+    static constexpr int kOffA = 0;
+    static constexpr int kOffW = kOffA + kStages * kABytes;
+    static constexpr int kOffBits = kOffW + kStages * kWBytes;
+    static constexpr int kOffPre = kOffBits + 2 * kBitsSlotBytes;   // input scales of a chunk, beside its bits
+    static constexpr int kOffBar = kOffPre + 2 * kPreBytes;
+    static constexpr int kNumBars = 4 * kStages + 2 + 2 + 1;  // full, wready, empty, wfree, bits_full, bits_empty, accum
+    static constexpr int kOffMisc = kOffBar + kNumBars * 8;   // tmem base address, abort flag
+    static constexpr int kSmemBytes = kOffMisc + 16 + 1024;   // + slack for the 1024-byte alignment
+    static constexpr int kTmemCols = MH * kBN;
+};
 
 struct GemmParams {
-    CUtensorMap map_a;     // activations [T, K], box 64 x 128, 128-byte swizzle
+    CUtensorMap map_a;     // activations [T, K], box 64 x (128 * MH), 128-byte swizzle
     const uint4* tiles;    // packed weights, GEMV tile layout [row_groups][chunks][32]
     const void* pre;       // [K] input scales (I/O dtype) or nullptr (weights are +-1)
     const void* post;      // [Nout] output scales (I/O dtype) or nullptr
@@ -86,14 +97,16 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+// One bounded attempt: the hardware suspends the thread until the phase completes or the
+// time hint (ns) runs out, so a waiting warp does not compete for issue slots.
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(2000u)
         : "memory");
     return ok != 0;
 }
@@ -103,8 +116,8 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           unsigned* status) {
     for (unsigned i = 0; i < kWaitLimit; ++i) {
-        if (mbar_test(bar, parity)) return true;
-        if ((i & 1023u) == 1023u && *abort_flag) return false;
+        if (mbar_try(bar, parity)) return true;
+        if (*abort_flag) return false;
     }
     *abort_flag = 1;
     atomicExch(status, (unsigned)(-NQ_ERR_TIMEOUT));
@@ -160,25 +173,40 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+#ifdef NQ_GEMM_TRACE  // development aid: cycle totals of the loop steps of CTA (0,0)
+__device__ long long g_gemm_trace[16];
+#define GT_NOW() clock64()
+#define GT_ADD(i, v) do { if (blockIdx.x == 0 && blockIdx.y == 0) gt[i] += (v); } while (0)
+#else
+#define GT_NOW() 0ll
+#define GT_ADD(i, v) ((void)0)
+#endif
+
 // ---------------------------------------------------------------------------
 // the kernel: one 128 x 128 output tile per CTA
 // ---------------------------------------------------------------------------
+template <int MH, int NH>
 __global__ void __launch_bounds__(kGemmThreads) gemm_stage_kernel(const __grid_constant__ GemmParams P) {
+    using C = GemmCfg<MH, NH>;
+    constexpr int kGemmStages = C::kStages, kBN = C::kBN, kBitsSlotBytes = C::kBitsSlotBytes;
+    constexpr int kOffA = C::kOffA, kOffW = C::kOffW, kOffBits = C::kOffBits, kOffPre = C::kOffPre;
+    constexpr int kOffBar = C::kOffBar, kOffMisc = C::kOffMisc;
     extern __shared__ unsigned char smem_raw[];
-    unsigned char* smem = reinterpret_cast<unsigned char*>(
-        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    // align inside the shared window (pointer + offset keeps the shared address space visible to the compiler)
+    unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     const uint32_t sbase = smem_u32(smem);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * kBN;   // first weight row of the tile
-    const int m0 = blockIdx.y * kBM;   // first token of the tile
+    const int m0 = blockIdx.y * (kBM * MH);   // first token of the tile
     const int nkb = (P.K + kBK - 1) / kBK;
 
     auto bar_full = [&](int s) { return sbase + kOffBar + 8 * s; };
     auto bar_wready = [&](int s) { return sbase + kOffBar + 8 * (kGemmStages + s); };
     auto bar_empty = [&](int s) { return sbase + kOffBar + 8 * (2 * kGemmStages + s); };
-    auto bar_bits_full = [&](int b) { return sbase + kOffBar + 8 * (3 * kGemmStages + b); };
-    auto bar_bits_empty = [&](int b) { return sbase + kOffBar + 8 * (3 * kGemmStages + 2 + b); };
-    const uint32_t bar_accum = sbase + kOffBar + 8 * (3 * kGemmStages + 4);
+    auto bar_wfree = [&](int s) { return sbase + kOffBar + 8 * (3 * kGemmStages + s); };
+    auto bar_bits_full = [&](int b) { return sbase + kOffBar + 8 * (4 * kGemmStages + b); };
+    auto bar_bits_empty = [&](int b) { return sbase + kOffBar + 8 * (4 * kGemmStages + 2 + b); };
+    const uint32_t bar_accum = sbase + kOffBar + 8 * (4 * kGemmStages + 4);
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + kOffMisc);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kOffMisc + 4);
 
@@ -187,6 +215,7 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_stage_kernel(const __grid_c
             mbar_init(bar_full(s), 1);
             mbar_init(bar_wready(s), kExpandThreads);
             mbar_init(bar_empty(s), 1);
+            mbar_init(bar_wfree(s), 1);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(bar_bits_full(b), 1);
@@ -197,11 +226,11 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_stage_kernel(const __grid_c
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     // input-scale slots start finite: a partial last k block leaves older (finite) values behind
-    for (int i = threadIdx.x; i < kGemmStages * kPreBytes / 4; i += kGemmThreads)
+    for (int i = threadIdx.x; i < 2 * kPreBytes / 4; i += kGemmThreads)
         reinterpret_cast<uint32_t*>(smem + kOffPre)[i] = 0;
-    if (warp == 1) {  // tensor-memory allocation: 128 fp32 columns, by one whole warp
+    if (warp == 1) {  // tensor-memory allocation: 128 fp32 columns per accumulator, by one whole warp
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_u32(const_cast<uint32_t*>(tmem_slot))), "r"((uint32_t)kBN) : "memory");
+                     ::"r"(smem_u32(const_cast<uint32_t*>(tmem_slot))), "r"((uint32_t)C::kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
@@ -219,24 +248,30 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_stage_kernel(const __grid_c
                 const int s = kb % kGemmStages;
                 const uint32_t ph = (kb / kGemmStages) & 1;
                 if (!mbar_wait(bar_empty(s), ph ^ 1, abort_flag, P.status)) break;
-                if ((kb & 3) == 0) {   // a new 256-column chunk of sign bits
-                    const int c = kb >> 2, b = c & 1;
-                    if (!mbar_wait(bar_bits_empty(b), ((c >> 1) & 1) ^ 1, abort_flag, P.status)) break;
-                    mbar_expect_tx(bar_bits_full(b), (uint32_t)nrg * 512u);
-                    for (int rg = 0; rg < nrg; ++rg)
-                        bulk_load(sbase + kOffBits + b * kBitsSlotBytes + rg * 512,
-                                  P.tiles + ((size_t)((n0 >> 4) + rg) * P.chunks + c) * 32, 512u, bar_bits_full(b));
-                }
+                mbar_expect_tx(bar_full(s), (uint32_t)(MH * kTileBytes));
+                tma_load_2d(sbase + kOffA + s * (C::kABytes), &P.map_a, kb * kBK, m0, bar_full(s));
+            }
+        }
+    } else if (warp == 2) {
+        // ------------------------------------------------------------ sign bits + input scales, one 256-column
+        // chunk per step, running ahead of the expand warps by the two chunk slots
+        if (lane == 0) {
+            const int nchunks = (nkb + 3) >> 2;
+            for (int c = 0; c < nchunks; ++c) {
+                const int b = c & 1;
+                if (!mbar_wait(bar_bits_empty(b), ((c >> 1) & 1) ^ 1, abort_flag, P.status)) break;
                 int pre_bytes = 0;
                 if (P.pre) {
-                    const int left = P.K - kb * kBK;
-                    pre_bytes = (left < kBK ? left : kBK) * 2;
+                    const int left = P.K - c * 256;
+                    pre_bytes = (left < 256 ? left : 256) * 2;
                 }
-                mbar_expect_tx(bar_full(s), (uint32_t)(kTileBytes + pre_bytes));
-                tma_load_2d(sbase + kOffA + s * kTileBytes, &P.map_a, kb * kBK, m0, bar_full(s));
+                mbar_expect_tx(bar_bits_full(b), (uint32_t)nrg * 512u + (uint32_t)pre_bytes);
+                for (int rg = 0; rg < nrg; ++rg)
+                    bulk_load(sbase + kOffBits + b * kBitsSlotBytes + rg * 512,
+                              P.tiles + ((size_t)((n0 >> 4) + rg) * P.chunks + c) * 32, 512u, bar_bits_full(b));
                 if (pre_bytes)
-                    bulk_load(sbase + kOffPre + s * kPreBytes, static_cast<const char*>(P.pre) + (size_t)kb * kBK * 2,
-                              (uint32_t)pre_bytes, bar_full(s));
+                    bulk_load(sbase + kOffPre + b * kPreBytes, static_cast<const char*>(P.pre) + (size_t)c * 512,
+                              (uint32_t)pre_bytes, bar_bits_full(b));
             }
         }
     } else if (warp == 1) {
@@ -246,43 +281,68 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_stage_kernel(const __grid_c
             const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(kBN >> 3) << 17) |
                                    ((uint32_t)(kBM >> 4) << 24);
             bool ok = true;
+            long long gt[4] = {0, 0, 0, 0};
             for (int kb = 0; kb < nkb && ok; ++kb) {
                 const int s = kb % kGemmStages;
                 const uint32_t ph = (kb / kGemmStages) & 1;
+                const long long t0 = GT_NOW();
                 ok = mbar_wait(bar_wready(s), ph, abort_flag, P.status) &&
                      mbar_wait(bar_full(s), ph, abort_flag, P.status);
                 if (!ok) break;
+                const long long t1 = GT_NOW();
+                GT_ADD(0, t1 - t0);
                 tc_fence_after();
-                const uint32_t a_addr = sbase + kOffA + s * kTileBytes, w_addr = sbase + kOffW + s * kTileBytes;
+                const uint32_t a_addr = sbase + kOffA + s * (C::kABytes);
+                const uint32_t w_addr = sbase + kOffW + s * C::kWBytes;
 #pragma unroll
-                for (int k4 = 0; k4 < kBK / 16; ++k4)
-                    umma_f16(tmem_base, umma_desc(a_addr + k4 * 32), umma_desc(w_addr + k4 * 32), idesc,
-                             (kb | k4) != 0 ? 1u : 0u);
-                umma_commit(bar_empty(s));   // the stage's buffers are free once these MMAs have read them
+                for (int mh = 0; mh < MH; ++mh)
+#pragma unroll
+                    for (int k4 = 0; k4 < kBK / 16; ++k4)
+                        umma_f16(tmem_base + (uint32_t)(mh * kBN), umma_desc(a_addr + mh * kTileBytes + k4 * 32),
+                                 umma_desc(w_addr + k4 * 32), idesc, (kb | k4) != 0 ? 1u : 0u);
+                umma_commit(bar_empty(s));   // the stage's buffers are free once these MMAs have read them:
+                umma_commit(bar_wfree(s));   // the activation tile for the producer, the weight tile for the expanders
+                GT_ADD(1, GT_NOW() - t1);
             }
+#ifdef NQ_GEMM_TRACE
+            if (blockIdx.x == 0 && blockIdx.y == 0) { g_gemm_trace[4] = gt[0]; g_gemm_trace[5] = gt[1]; }
+#endif
             if (ok) umma_commit(bar_accum);
         }
     } else {
         // ------------------------------------------------------------ expand warps
-        const int tu = threadIdx.x - 64;   // 0..127
+        const int tu = threadIdx.x - 96;   // 0..255
         const uint32_t one2 = P.is_bf16 ? 0x3F803F80u : 0x3C003C00u;
         bool ok = true;
+        long long gt[4] = {0, 0, 0, 0};
         for (int kb = 0; kb < nkb && ok; ++kb) {
             const int s = kb % kGemmStages;
             const uint32_t ph = (kb / kGemmStages) & 1;
             const int c = kb >> 2, b = c & 1, sub = kb & 3;
+            const long long t0 = GT_NOW();
             if (sub == 0) ok = mbar_wait(bar_bits_full(b), (c >> 1) & 1, abort_flag, P.status);
-            ok = ok && mbar_wait(bar_full(s), ph, abort_flag, P.status);
+            ok = ok && mbar_wait(bar_wfree(s), ph ^ 1, abort_flag, P.status);   // not on the activation tile
             if (!ok) break;
+            const long long t1 = GT_NOW();
+            GT_ADD(0, t1 - t0);
             const uint4* bits = reinterpret_cast<const uint4*>(smem + kOffBits + b * kBitsSlotBytes);
-            const uint2* pre2 = reinterpret_cast<const uint2*>(smem + kOffPre + s * kPreBytes);
-            unsigned char* wt = smem + kOffW + s * kTileBytes;
+            const uint2* pre2 = reinterpret_cast<const uint2*>(smem + kOffPre + b * kPreBytes + sub * (kBK * 2));
+            unsigned char* wt = smem + kOffW + s * C::kWBytes;
+            // all shared-memory reads of the k block first, then the stores
+            uint4 w4[NH];
 #pragma unroll
-            for (int it = 0; it < 2; ++it) {
-                const int task = tu + it * kExpandThreads;   // (row group, lane of the GEMV tile)
-                const int rg = task >> 5, l = task & 31, g = l >> 2, q = l & 3;
-                const uint4 w4 = bits[rg * 32 + l];
-                const uint32_t comp[4] = {w4.x, w4.y, w4.z, w4.w};   // {row g h0, row g+8 h0, row g h1, row g+8 h1}
+            for (int it = 0; it < NH; ++it) w4[it] = bits[tu + it * kExpandThreads];
+            const int l = tu & 31, g = l >> 2, q = l & 3;   // lane of the GEMV tile (same for every task)
+            uint2 pp[4];                                      // input scales of columns 32*jj + 16*h + 4q .. +3
+#pragma unroll
+            for (int c4 = 0; c4 < 4; ++c4) {
+                if (P.pre) pp[c4] = pre2[(32 * (c4 >> 1) + 16 * (c4 & 1) + 4 * q) >> 2];
+                else pp[c4] = make_uint2(one2, one2);
+            }
+#pragma unroll
+            for (int it = 0; it < NH; ++it) {
+                const int rg = (tu + it * kExpandThreads) >> 5;   // row group of the task
+                const uint32_t comp[4] = {w4[it].x, w4[it].y, w4[it].z, w4[it].w};   // {row g h0, row g+8 h0, row g h1, row g+8 h1}
 #pragma unroll
                 for (int jj = 0; jj < 2; ++jj) {
                     const int j = 2 * sub + jj;                      // class of the 32 columns
@@ -290,35 +350,35 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_stage_kernel(const __grid_c
                     for (int ci = 0; ci < 4; ++ci) {
                         const int h = ci >> 1, row = 16 * rg + g + 8 * (ci & 1);
                         const uint32_t u = (comp[ci] << (7 - j)) & 0x80808080u;   // bit 8b+j -> sign of byte b
-                        uint32_t v0 = __byte_perm(u, 0u, 0x1404);                 // columns 4q, 4q+1
-                        uint32_t v1 = __byte_perm(u, 0u, 0x3424);                 // columns 4q+2, 4q+3
-                        const int kl = 32 * jj + 16 * h + 4 * q;                  // first of the four columns
-                        if (P.pre) {
-                            const uint2 pp = pre2[kl >> 2];
-                            v0 ^= pp.x; v1 ^= pp.y;
-                        } else {
-                            v0 ^= one2; v1 ^= one2;
-                        }
-                        const int c16 = kl >> 3;                                  // 16-byte chunk of the 128-byte row
+                        const uint32_t v0 = __byte_perm(u, 0u, 0x1404) ^ pp[2 * jj + h].x;   // columns 4q, 4q+1
+                        const uint32_t v1 = __byte_perm(u, 0u, 0x3424) ^ pp[2 * jj + h].y;   // columns 4q+2, 4q+3
+                        const int c16 = (32 * jj + 16 * h + 4 * q) >> 3;          // 16-byte chunk of the 128-byte row
                         *reinterpret_cast<uint2*>(wt + row * 128 + ((c16 ^ (row & 7)) << 4) + 8 * (q & 1)) =
                             make_uint2(v0, v1);
                     }
                 }
             }
+            const long long t2 = GT_NOW();
+            GT_ADD(1, t2 - t1);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the MMA
             mbar_arrive(bar_wready(s));
             if (sub == 3 || kb + 1 == nkb) mbar_arrive(bar_bits_empty(b));
+            GT_ADD(2, GT_NOW() - t2);
         }
+#ifdef NQ_GEMM_TRACE
+        if (blockIdx.x == 0 && blockIdx.y == 0 && tu == 0) { g_gemm_trace[0] = gt[0]; g_gemm_trace[1] = gt[1]; g_gemm_trace[2] = gt[2]; g_gemm_trace[3] = nkb; }
+#endif
         // ------------------------------------------------------------ epilogue
         if (ok) ok = mbar_wait(bar_accum, 0, abort_flag, P.status);
-        if (ok) {
+        const int mh = (warp - 3) >> 2;              // which 128-token accumulator this warp drains
+        if (ok && mh < MH) {
             tc_fence_after();
             const int lq = warp & 3;                 // tensor-memory lane quarter this warp may read
-            const int row = m0 + 32 * lq + lane;     // token
+            const int row = m0 + kBM * mh + 32 * lq + lane;     // token
 #pragma unroll 1
             for (int c0 = 0; c0 < kBN; c0 += 32) {
                 uint32_t r[32];
-                tmem_ld32(tmem_base + ((uint32_t)(32 * lq) << 16) + (uint32_t)c0, r);
+                tmem_ld32(tmem_base + ((uint32_t)(32 * lq) << 16) + (uint32_t)(mh * kBN + c0), r);
                 if (row < P.T && n0 + c0 < P.Nout) {
                     uint32_t packed[16];
 #pragma unroll
@@ -369,7 +429,7 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_stage_kernel(const __grid_c
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kBN)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)C::kTmemCols)
                      : "memory");
     }
 }
@@ -406,7 +466,11 @@ static int launch_stage(const void* a, long long lda, const void* tiles, const v
     memset(&P, 0, sizeof(P));
     const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)T};
     const cuuint64_t strides[1] = {(cuuint64_t)lda * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)kBM};
+    // tile shape: 256 tokens when there are that many; 256 weight rows when the grid still fills the GPU
+    const int mh = T > kBM ? 2 : 1;
+    const int m_tiles = (T + kBM * mh - 1) / (kBM * mh);
+    const int nh = (mh == 2 && ((Nout + 255) / 256) * m_tiles >= (sm_count() * 3) / 4) ? 2 : 1;
+    const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)(kBM * mh)};
     const cuuint32_t estr[2] = {1, 1};
     const CUresult r = enc(&P.map_a, dtype == NQ_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
                            2, const_cast<void*>(a), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -428,11 +492,18 @@ static int launch_stage(const void* a, long long lda, const void* tiles, const v
     int dev = 0;
     NQ_CUDA_TRY(cudaGetDevice(&dev));
     if (!attr_set[dev & 63]) {
-        NQ_CUDA_TRY(cudaFuncSetAttribute(gemm_stage_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes));
+        NQ_CUDA_TRY(cudaFuncSetAttribute(gemm_stage_kernel<1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         GemmCfg<1, 1>::kSmemBytes));
+        NQ_CUDA_TRY(cudaFuncSetAttribute(gemm_stage_kernel<2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         GemmCfg<2, 1>::kSmemBytes));
+        NQ_CUDA_TRY(cudaFuncSetAttribute(gemm_stage_kernel<2, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         GemmCfg<2, 2>::kSmemBytes));
         attr_set[dev & 63] = true;
     }
-    const dim3 grid((Nout + kBN - 1) / kBN, (T + kBM - 1) / kBM);
-    gemm_stage_kernel<<<grid, kGemmThreads, kGemmSmemBytes, stream>>>(P);
+    const dim3 grid((Nout + 128 * nh - 1) / (128 * nh), m_tiles);
+    if (mh == 1) gemm_stage_kernel<1, 1><<<grid, kGemmThreads, GemmCfg<1, 1>::kSmemBytes, stream>>>(P);
+    else if (nh == 1) gemm_stage_kernel<2, 1><<<grid, kGemmThreads, GemmCfg<2, 1>::kSmemBytes, stream>>>(P);
+    else gemm_stage_kernel<2, 2><<<grid, kGemmThreads, GemmCfg<2, 2>::kSmemBytes, stream>>>(P);
     NQ_LAUNCH_CHECK();
     return NQ_OK;
 }
@@ -473,6 +544,14 @@ int nq_gemm_fwd(const void* x, const void* s_in, const void* v_tiles, const void
     if (st != NQ_OK) return st;
     return launch_stage(t, R, u_tiles, nullptr, s_out, y, M, T, R, M, dtype, 1, status, as_stream(stream));
 }
+
+#ifdef NQ_GEMM_TRACE
+int nq_debug_read_gemm_trace(long long* host_out) {
+    NQ_CUDA_TRY(cudaDeviceSynchronize());
+    NQ_CUDA_TRY(cudaMemcpyFromSymbol(host_out, g_gemm_trace, sizeof(long long) * 16));
+    return NQ_OK;
+}
+#endif
 
 int nq_gemv_max_tokens(void) { return 8; }
 
