@@ -166,6 +166,23 @@ int nq_gemv_fwd(const void* x, const void* s_in, const void* v_tiles, const void
 int nq_gemv_group_fwd(const nq_linear_desc* linears_host, int n_linears, int T, int dtype,
                       void* scratch, size_t scratch_bytes, nq_stream_t stream);
 
+/* nq_gemv_fwd for callers that cannot hand the library any device memory of their own
+ * beyond inputs and outputs: code running where allocation is forbidden or already frozen
+ * (inside a serving loop whose memory plan is fixed, a plugin host that owns the allocator,
+ * a capture-only phase).  It has NO counterpart in the reference.  The intermediate and the
+ * barrier words live in a fixed array inside the library image (about 128 KB, present on
+ * every GPU that loads the library until the process exits); nothing is allocated or freed,
+ * here or in any library it calls.  Limits: rank R <= nq_gemv_static_max_rank() (8192),
+ * otherwise NQ_ERR_TOO_LARGE; T > 4 runs as several launches like nq_gemv_fwd.
+ * The first call on a device looks the array's device address up (cudaGetSymbolAddress);
+ * make that first call outside any stream capture.  Every call clears the barrier / status
+ * words on `stream` first and then reuses the same array, so two calls that can overlap on
+ * the GPU (different streams, or threads, without ordering) race on it: order them. */
+int nq_gemv_fwd_static(const void* x, const void* s_in, const void* v_tiles, const void* s_mid,
+                       const void* u_tiles, const void* s_out, void* y,
+                       int T, int N, int R, int M, int dtype, nq_stream_t stream);
+size_t nq_gemv_static_max_rank(void);
+
 /* Synchronises `stream` and returns the status word of a scratch buffer:
  * NQ_OK, or NQ_ERR_TIMEOUT when a device-wide wait of an earlier launch gave up
  * (the scratch must then be zeroed again before reuse). */

@@ -557,6 +557,34 @@ static int dynamic_smem_limit(int dev, int* out) {
     return NQ_OK;
 }
 
+
+// ---------------------------------------------------------------------------
+// GEMV without caller-provided scratch
+// ---------------------------------------------------------------------------
+// Scratch of nq_gemv_fwd_static: lives in the library image on every GPU that loads it, until
+// the process exits.  256-byte header + fp32 intermediate for up to 4 tokens x rank 8192.
+constexpr int kStaticMaxRank = 8192;
+constexpr size_t kStaticScratchBytes = kHeaderBytes + (size_t)kMaxTok * kStaticMaxRank * sizeof(float);
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// Device address of g_static_scratch on the current device.  In host code the symbol name is
+// only a handle: the address a kernel can use comes from cudaGetSymbolAddress, looked up once
+// per device with that device current.
+static int static_scratch_ptr(void** out) {
+    static void* cached[64];
+    int dev = 0;
+    NQ_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return NQ_ERR_UNSUPPORTED;
+    if (!cached[dev]) {
+        void* p = nullptr;
+        NQ_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_scratch));
+        if (!p) return NQ_ERR_CUDA;
+        cached[dev] = p;
+    }
+    *out = cached[dev];
+    return NQ_OK;
+}
+
 }  // namespace nq
 
 using namespace nq;
@@ -686,6 +714,22 @@ int nq_gemv_fwd(const void* x, const void* s_in, const void* v_tiles, const void
     d.y = y; d.N = N; d.R = R; d.M = M; d.ldx = N; d.ldy = M;
     return nq_gemv_group_fwd(&d, 1, T, dtype, scratch, scratch_bytes, stream);
 }
+
+int nq_gemv_fwd_static(const void* x, const void* s_in, const void* v_tiles, const void* s_mid,
+                       const void* u_tiles, const void* s_out, void* y,
+                       int T, int N, int R, int M, int dtype, nq_stream_t stream) {
+    if (T <= 0 || N <= 0 || R <= 0 || M <= 0) return NQ_ERR_SHAPE;
+    if (R > kStaticMaxRank || nq_gemv_scratch_bytes(T, N, R, M) > kStaticScratchBytes) return NQ_ERR_TOO_LARGE;
+    void* scratch = nullptr;
+    const int st = static_scratch_ptr(&scratch);   // first call on a device: symbol lookup
+    if (st != NQ_OK) return st;
+    // the array keeps whatever the previous call left: the barrier / status words must start at zero
+    NQ_CUDA_TRY(cudaMemsetAsync(scratch, 0, 16, as_stream(stream)));
+    return nq_gemv_fwd(x, s_in, v_tiles, s_mid, u_tiles, s_out, y, scratch, kStaticScratchBytes, T, N, R, M, dtype,
+                       stream);
+}
+
+size_t nq_gemv_static_max_rank(void) { return (size_t)kStaticMaxRank; }
 
 #ifdef NQ_GEMV_TRACE
 int nq_debug_read_trace(unsigned long long* host_out) {
