@@ -362,6 +362,129 @@ def gpu_arm(args):
         dist.destroy_process_group()
 
 
+
+# --------------------------------------------------------------------------------------------
+# tensor-parallel arm (--mode tp): Llama-3-70B-shaped linears, U split by output rows, NCCL all-gather
+# --------------------------------------------------------------------------------------------
+TP_HIDDEN, TP_INTER, TP_LAYERS, TP_KV = 8192, 28672, 80, 1024
+
+
+def tp_layer_linears():
+    spec = [("q", TP_HIDDEN, TP_HIDDEN, "h", 0), ("k", TP_HIDDEN, TP_KV, "h", 0), ("v", TP_HIDDEN, TP_KV, "h", 0),
+            ("o", TP_HIDDEN, TP_HIDDEN, "h", 1), ("gate", TP_HIDDEN, TP_INTER, "h", 2), ("up", TP_HIDDEN, TP_INTER, "h", 2),
+            ("down", TP_INTER, TP_HIDDEN, "i", 3)]
+    return [(n, N, rank_for_bits(N, M, BPW), M, src, grp) for (n, N, M, src, grp) in spec]
+
+
+def tp_arm(args):
+    """One decode step of the 70B-shaped linears with every U sharded over the ranks: per launch
+    group the local GEMV, then one NCCL all-gather per linear of its [T, M/G] shard.  Strong scaling."""
+    import torch
+    import torch.distributed as dist
+    from nanoquant_b200 import _lib
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    L = _lib.lib()
+    T, dtype, layers = args.batch, torch.bfloat16, args.tp_layers
+    g = torch.Generator(device=device).manual_seed(0)   # same seed on every rank: replicated tensors agree
+    rnd_bits = lambda rows, cols: torch.randint(-2**31, 2**31 - 1, ((rows + 15) // 16, (cols + 255) // 256, 128),
+                                                generator=g, device=device, dtype=torch.int32)
+    scale = lambda n: ((torch.rand(n, generator=g, device=device) + 0.5) * 0.01).to(dtype)
+    x = {"h": torch.randn(T, TP_HIDDEN, generator=g, device=device).to(dtype),
+         "i": torch.randn(T, TP_INTER, generator=g, device=device).to(dtype)}
+    keep, steps, nbytes, scratch_bytes = [], [], 0, 0
+    for _ in range(layers):
+        groups = {}
+        for (name, N, R, M, src, grp) in tp_layer_linears():
+            m = M // world
+            t = dict(v=rnd_bits(R, N), u=rnd_bits(m, R), s_in=scale(N), s_mid=scale(R), s_out=scale(m),
+                     y=torch.empty(T, m, device=device, dtype=dtype), full=torch.empty(world * T, m, device=device, dtype=dtype))
+            keep.append(t)
+            d = _lib.LinearDesc(x[src].data_ptr(), t["s_in"].data_ptr(), t["v"].data_ptr(), t["s_mid"].data_ptr(),
+                                t["u"].data_ptr(), t["s_out"].data_ptr(), t["y"].data_ptr(), N, R, m, N, m)
+            groups.setdefault(grp, []).append((d, t))
+            nbytes += R * N // 8 + R * m // 8 + 2 * (N + R + m) + 2 * T * (N + m)
+        for grp in sorted(groups):
+            arr = (_lib.LinearDesc * len(groups[grp]))(*[d for d, _ in groups[grp]])
+            scratch_bytes = max(scratch_bytes, L.nq_gemv_group_scratch_bytes(arr, len(arr), T))
+            steps.append((arr, [t for _, t in groups[grp]]))
+    scratch = torch.zeros(scratch_bytes, dtype=torch.uint8, device=device)
+
+    def run():
+        st = torch.cuda.current_stream(device).cuda_stream
+        for arr, ts in steps:
+            _lib.check(L.nq_gemv_group_fwd(arr, len(arr), T, _lib.NQ_BF16, scratch.data_ptr(), scratch.numel(), st), "gemv")
+            if world > 1:
+                for t in ts:
+                    dist.all_gather_into_tensor(t["full"], t["y"])
+
+    # One GPU: the step is replayed as a CUDA graph.  Several GPUs: the launches and the NCCL calls are
+    # issued eagerly in stream order.  (The GEMV kernel holds a device-wide barrier and needs all its
+    # CTAs resident; it must never share the GPU with a collective kernel that is itself waiting for a
+    # peer, so the collectives are kept strictly ordered with it instead of being captured in a graph.)
+    graph = None
+    for _ in range(2):
+        run()
+    torch.cuda.synchronize(device)
+    if world == 1:
+        s = torch.cuda.Stream(device)
+        s.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(s):
+            run()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=s):
+                run()
+        torch.cuda.current_stream(device).wait_stream(s)
+        torch.cuda.synchronize(device)
+    replay = graph.replay if graph is not None else run
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+    for _ in range(max(args.warmup, 3)):
+        replay()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        replay()
+    e1.record()
+    barrier()
+    ms = torch.tensor([e0.elapsed_time(e1)], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    if L.nq_scratch_status(scratch.data_ptr(), torch.cuda.current_stream(device).cuda_stream) != 0:
+        raise SystemExit("bench.py: a device-wide wait timed out inside the GEMV kernel")
+    if rank == 0:
+        step_s = ms.item() * 1e-3 / args.steps * (TP_LAYERS / layers)
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except (OSError, ValueError):
+            pass
+        peak = float(peaks.get("hbm_gbs", 6650.0))
+        per_gpu = nbytes * (TP_LAYERS / layers) / step_s / 1e9
+        print(json.dumps({
+            "mode": "tp", "metric": "decode tok/s (quantised linears of one decode step)", "value": T / step_s,
+            "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "s8 mma / s32 accumulate; bf16 in/out", "data": "synthetic",
+            "config": {"workload": f"llama-3-70b-shaped decoder linears at {BPW} bpw, decode batch {T}, U split by output "
+                                   f"rows over {world} GPUs + NCCL all-gather per linear",
+                       "layers_timed": layers, "layers": TP_LAYERS, "parallelism": f"tp{world}"},
+            "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s per GPU", "frac": per_gpu / peak,
+                         "traffic": None},
+            "gpu_launches": len(steps) * args.steps}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -370,9 +493,14 @@ def main():
     ap.add_argument("--batch", type=int, default=1, help="tokens per decode step (1, 4 or 16 in the workload)")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--mode", default="replica", choices=["replica", "tp"],
+                    help="N > 1: independent replicas of the 8B-shaped step (default) or the 70B-shaped TP step")
+    ap.add_argument("--tp-layers", type=int, default=TP_LAYERS, help="layers actually timed in --mode tp")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)
+    elif args.mode == "tp":
+        tp_arm(args)
     else:
         gpu_arm(args)
 

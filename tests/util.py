@@ -36,5 +36,5 @@ def make_layer(N, R, M, T, dtype, seed=0, has_mid=True, device="cuda"):
     return L
 
 
-def half2_bits(w, device="cuda"):
+def half2_bits(w, device="cuda"):  # noqa: D401
     return torch.from_numpy(oc.pack_rows(w, "half2")).to(device)
