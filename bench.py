@@ -192,9 +192,9 @@ def workload_config(T):
 # GPU arm
 # --------------------------------------------------------------------------------------------
 class Step:
-    """Device-resident weights of the 36 layers and the launch list of one decode step."""
+    """Device-resident weights of the decoder layers and the launch list of one decode step."""
 
-    def __init__(self, T, dtype, device):
+    def __init__(self, T, dtype, device, layers=LAYERS):
         import torch
         from nanoquant_b200 import _lib
         self.torch, self.lib, self.L = torch, _lib, _lib.lib()
@@ -208,7 +208,7 @@ class Step:
                   "i": torch.randn(T, INTER, generator=g, device=device).to(dtype)}
         self.keep, self.launches, self.bytes = [], [], 0
         scratch_bytes = 0
-        for _ in range(LAYERS):
+        for _ in range(layers):
             groups = {}
             for (name, N, R, M, src, grp) in layer_linears():
                 t = dict(v=rnd_bits(R, N), u=rnd_bits(M, R), s_in=scale(N), s_mid=scale(R), s_out=scale(M),
@@ -265,7 +265,7 @@ def gpu_arm(args):
         dist.init_process_group("nccl", device_id=device)
     T = args.batch
     dtype = torch.bfloat16
-    step = Step(T, dtype, device)
+    step = Step(T, dtype, device, args.layers)
     step.capture()
 
     def barrier():
@@ -282,11 +282,13 @@ def gpu_arm(args):
         time.sleep(0.3)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    torch.cuda.profiler.start()   # lets `ncu --profile-from-start off` see exactly the timed region
     e0.record()
     for _ in range(args.steps):
         step.graph.replay()
     e1.record()
     barrier()
+    torch.cuda.profiler.stop()
     ms = e0.elapsed_time(e1)
     # keep the clocks sample meaningful for short runs: load for at least ~1 s in total
     t_extra = time.perf_counter() + max(0.0, 1.0 - ms * 1e-3)
@@ -335,13 +337,18 @@ def gpu_arm(args):
     peak_src = "measured (MEASURED_PEAKS.json hbm_gbs)" if "hbm_gbs" in peaks else "fallback 6650 GB/s"
     step_s = ms * 1e-3 / args.steps
     achieved = step.bytes / step_s / 1e9
+    if args.layers != LAYERS:   # profiling aid: fewer layers resident; report per-step numbers of what ran
+        out_note = f"{args.layers} of {LAYERS} layers timed (profiling run, not a benchmark value)"
+    else:
+        out_note = None
     launch_us = step_s / step.kernels_per_step * 1e6
     out = {
         "metric": "decode tok/s (quantised linears of one decode step)", "value": world * T / step_s,
         "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "s8 mma / s32 accumulate on 16-bit fixed point; bf16 in/out", "data": "synthetic",
-        "config": dict(workload_config(T), parallelism=("single gpu" if world == 1 else f"{world} independent replicas")),
+        "config": dict(workload_config(T), layers_timed=args.layers,
+                       parallelism=("single gpu" if world == 1 else f"{world} independent replicas")),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": None, "kernel": "gemv_group_kernel",
                      "bytes_per_launch": step.bytes / step.kernels_per_step, "us_per_launch": launch_us,
@@ -352,6 +359,8 @@ def gpu_arm(args):
         "gpu_launches": step.kernels_per_step * args.steps,
         "clocks": clocks,
     }
+    if out_note:
+        out["note"] = out_note
     if not args.no_cpu_baseline:
         cpu = CpuLayer(T)
         t_layer, reps = cpu.timed(budget_s=12.0)
@@ -485,6 +494,85 @@ def tp_arm(args):
         dist.destroy_process_group()
 
 
+# --------------------------------------------------------------------------------------------
+# prefill arm (--mode prefill): Llama-2-7B-shaped layer GEMMs at 1.0 bpw, T tokens per GEMM
+# --------------------------------------------------------------------------------------------
+def prefill_arm(args):
+    """TFLOP/s of the tcgen05 GEMM path (nq_gemm_fwd) on the 7 linears of Llama-2-7B-shaped layers
+    (hidden 4096, intermediate 11008, ranks from the rank formula at 1.0 bpw), `--tokens` tokens per GEMM."""
+    import torch
+    from nanoquant_b200 import _lib
+    L = _lib.lib()
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(device)
+    T, dtype = args.tokens, torch.bfloat16
+    H, I = 4096, 11008
+    shapes = [(H, H)] * 4 + [(H, I), (H, I), (I, H)]
+    g = torch.Generator(device=device).manual_seed(0)
+    rnd_bits = lambda rows, cols: torch.randint(-2**31, 2**31 - 1, ((rows + 15) // 16, (cols + 255) // 256, 128),
+                                                generator=g, device=device, dtype=torch.int32)
+    scale = lambda n: ((torch.rand(n, generator=g, device=device) + 0.5) * 0.01).to(dtype)
+    xs = {H: torch.randn(T, H, generator=g, device=device).to(dtype), I: torch.randn(T, I, generator=g, device=device).to(dtype)}
+    calls, flops, scratch_bytes = [], 0.0, 0
+    for _ in range(args.layers if args.layers != LAYERS else 4):
+        for (N, M) in shapes:
+            R = rank_for_bits(N, M, 1.0)
+            t = dict(v=rnd_bits(R, N), u=rnd_bits(M, R), a=scale(N), b=scale(R), c=scale(M),
+                     y=torch.empty(T, M, device=device, dtype=dtype))
+            calls.append((t, N, R, M))
+            flops += 2.0 * T * R * (N + M)
+            scratch_bytes = max(scratch_bytes, L.nq_gemm_scratch_bytes(T, N, R, M))
+    scratch = torch.zeros(scratch_bytes, dtype=torch.uint8, device=device)
+    st = torch.cuda.current_stream(device).cuda_stream
+
+    def run():
+        for (t, N, R, M) in calls:
+            _lib.check(L.nq_gemm_fwd(xs[N].data_ptr(), t["a"].data_ptr(), t["v"].data_ptr(), t["b"].data_ptr(),
+                                     t["u"].data_ptr(), t["c"].data_ptr(), t["y"].data_ptr(), scratch.data_ptr(),
+                                     scratch.numel(), T, N, R, M, _lib.NQ_BF16, st), "nq_gemm_fwd")
+    for _ in range(max(args.warmup, 3)):
+        run()
+    torch.cuda.synchronize(device)
+    sampler = ClockSampler(device.index)
+    sampler.start()
+    time.sleep(0.3)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.profiler.start()
+    e0.record()
+    for _ in range(args.steps):
+        run()
+    e1.record()
+    torch.cuda.synchronize(device)
+    torch.cuda.profiler.stop()
+    ms = e0.elapsed_time(e1) / args.steps
+    t_end = time.perf_counter() + max(0.0, 1.0 - ms * args.steps * 1e-3)
+    while time.perf_counter() < t_end:
+        run()
+        torch.cuda.synchronize(device)
+    clocks = sampler.stop()
+    if L.nq_scratch_status(scratch.data_ptr(), st) != 0:
+        raise SystemExit("bench.py: a device-side wait timed out inside the GEMM kernel")
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except (OSError, ValueError):
+        pass
+    peak = float(peaks.get("bf16_tflops_sustained", 1400.0))
+    tf = flops / (ms * 1e-3) / 1e12
+    print(json.dumps({
+        "mode": "prefill", "metric": "prefill TFLOP/s (quantised linears, 2*T*R*(N+M) flops)", "value": tf,
+        "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 (fp32 accumulate)",
+        "data": "synthetic",
+        "config": {"workload": f"llama-2-7b-shaped layer GEMMs at 1.0 bpw, {T} tokens per GEMM, {len(calls) // 7} layers",
+                   "tokens": T},
+        "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak,
+                     "traffic": None, "kernel": "gemm_stage_kernel",
+                     "peak_source": "measured (MEASURED_PEAKS.json bf16_tflops_sustained)" if peaks else "fallback 1400"},
+        "tokens_per_s": T * (len(calls) // 7) / (ms * 1e-3) / (len(calls) // 7),
+        "gpu_launches": 2 * len(calls) * args.steps, "clocks": clocks}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -493,14 +581,19 @@ def main():
     ap.add_argument("--batch", type=int, default=1, help="tokens per decode step (1, 4 or 16 in the workload)")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--mode", default="replica", choices=["replica", "tp"],
-                    help="N > 1: independent replicas of the 8B-shaped step (default) or the 70B-shaped TP step")
+    ap.add_argument("--mode", default="replica", choices=["replica", "tp", "prefill"],
+                    help="replica: the decode step (N > 1: independent replicas); tp: 70B-shaped TP decode step; "
+                         "prefill: GEMM TFLOP/s on Llama-2-7B-shaped layers")
+    ap.add_argument("--tokens", type=int, default=2048, help="tokens per GEMM in --mode prefill")
+    ap.add_argument("--layers", type=int, default=LAYERS, help="decoder layers resident (fewer only for profiling)")
     ap.add_argument("--tp-layers", type=int, default=TP_LAYERS, help="layers actually timed in --mode tp")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)
     elif args.mode == "tp":
         tp_arm(args)
+    elif args.mode == "prefill":
+        prefill_arm(args)
     else:
         gpu_arm(args)
 
