@@ -65,7 +65,9 @@ struct GemmCfg {
     static constexpr int kOffBar = kOffPre + 2 * kPreBytes;
     static constexpr int kNumBars = 4 * kStages + 2 + 2 + 1;  // full, wready, empty, wfree, bits_full, bits_empty, accum
     static constexpr int kOffMisc = kOffBar + kNumBars * 8;   // tmem base address, abort flag
-    static constexpr int kSmemBytes = kOffMisc + 16 + 1024;   // + slack for the 1024-byte alignment
+    static constexpr int kOffPost = (kOffMisc + 16 + 15) & ~15;   // output scales of the tile as fp32 (read as float4)
+    static_assert(kOffPost % 16 == 0 && kOffBar % 8 == 0 && kOffBits % 16 == 0 && kOffPre % 16 == 0, "shared memory map alignment");
+    static constexpr int kSmemBytes = kOffPost + kBN * 4 + 1024;   // + slack for the 1024-byte alignment
     static constexpr int kTmemCols = MH * kBN;
 };
 
@@ -190,7 +192,7 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_stage_kernel(const __grid_c
     using C = GemmCfg<MH, NH>;
     constexpr int kGemmStages = C::kStages, kBN = C::kBN, kBitsSlotBytes = C::kBitsSlotBytes;
     constexpr int kOffA = C::kOffA, kOffW = C::kOffW, kOffBits = C::kOffBits, kOffPre = C::kOffPre;
-    constexpr int kOffBar = C::kOffBar, kOffMisc = C::kOffMisc;
+    constexpr int kOffBar = C::kOffBar, kOffMisc = C::kOffMisc, kOffPost = C::kOffPost;
     extern __shared__ unsigned char smem_raw[];
     // align inside the shared window (pointer + offset keeps the shared address space visible to the compiler)
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -228,6 +230,13 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_stage_kernel(const __grid_c
     // input-scale slots start finite: a partial last k block leaves older (finite) values behind
     for (int i = threadIdx.x; i < 2 * kPreBytes / 4; i += kGemmThreads)
         reinterpret_cast<uint32_t*>(smem + kOffPre)[i] = 0;
+    for (int i = threadIdx.x; i < kBN; i += kGemmThreads) {   // output scales of this tile, once, as fp32
+        float f = 1.f;
+        if (P.post && n0 + i < P.Nout)
+            f = P.is_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(P.post)[n0 + i])
+                          : __half2float(static_cast<const __half*>(P.post)[n0 + i]);
+        reinterpret_cast<float*>(smem + kOffPost)[i] = f;
+    }
     if (warp == 1) {  // tensor-memory allocation: 128 fp32 columns per accumulator, by one whole warp
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                      ::"r"(smem_u32(const_cast<uint32_t*>(tmem_slot))), "r"((uint32_t)C::kTmemCols) : "memory");
@@ -375,47 +384,42 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_stage_kernel(const __grid_c
             tc_fence_after();
             const int lq = warp & 3;                 // tensor-memory lane quarter this warp may read
             const int row = m0 + kBM * mh + 32 * lq + lane;     // token
+            const float lim = P.saturate ? (P.is_bf16 ? 3.3895313892515355e+38f : 64504.0f) : 3.4e38f;
+            const float4* post4 = reinterpret_cast<const float4*>(smem + kOffPost);
 #pragma unroll 1
             for (int c0 = 0; c0 < kBN; c0 += 32) {
                 uint32_t r[32];
                 tmem_ld32(tmem_base + ((uint32_t)(32 * lq) << 16) + (uint32_t)(mh * kBN + c0), r);
-                if (row < P.T && n0 + c0 < P.Nout) {
-                    uint32_t packed[16];
+                if (row >= P.T || n0 + c0 >= P.Nout) continue;
+                uint32_t packed[16];
 #pragma unroll
-                    for (int e = 0; e < 32; e += 2) {
-                        float v[2];
-#pragma unroll
-                        for (int d = 0; d < 2; ++d) {
-                            const int n = n0 + c0 + e + d;
-                            float f = __uint_as_float(r[e + d]);
-                            if (P.post && n < P.Nout) {
-                                f *= P.is_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(P.post)[n])
-                                               : __half2float(static_cast<const __half*>(P.post)[n]);
-                            }
-                            if (P.saturate) {
-                                const float lim = P.is_bf16 ? 3.3895313892515355e+38f : 64504.0f;
-                                f = fminf(fmaxf(f, -lim), lim);
-                            }
-                            v[d] = f;
-                        }
-                        if (P.is_bf16) {
-                            const __nv_bfloat162 h2 = __floats2bfloat162_rn(v[0], v[1]);
-                            packed[e >> 1] = *reinterpret_cast<const uint32_t*>(&h2);
-                        } else {
-                            const __half2 h2 = __floats2half2_rn(v[0], v[1]);
-                            packed[e >> 1] = *reinterpret_cast<const uint32_t*>(&h2);
-                        }
-                    }
-                    unsigned char* dst = static_cast<unsigned char*>(P.out) + ((size_t)row * P.ld_out + n0 + c0) * 2;
-                    if (n0 + c0 + 32 <= P.Nout && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
-#pragma unroll
-                        for (int v4 = 0; v4 < 4; ++v4)
-                            reinterpret_cast<uint4*>(dst)[v4] =
-                                make_uint4(packed[4 * v4], packed[4 * v4 + 1], packed[4 * v4 + 2], packed[4 * v4 + 3]);
+                for (int e4 = 0; e4 < 8; ++e4) {
+                    const float4 sc = post4[(c0 >> 2) + e4];          // same address in every lane: broadcast
+                    const float v0 = fminf(fmaxf(__uint_as_float(r[4 * e4 + 0]) * sc.x, -lim), lim);
+                    const float v1 = fminf(fmaxf(__uint_as_float(r[4 * e4 + 1]) * sc.y, -lim), lim);
+                    const float v2 = fminf(fmaxf(__uint_as_float(r[4 * e4 + 2]) * sc.z, -lim), lim);
+                    const float v3 = fminf(fmaxf(__uint_as_float(r[4 * e4 + 3]) * sc.w, -lim), lim);
+                    if (P.is_bf16) {
+                        const __nv_bfloat162 a2 = __floats2bfloat162_rn(v0, v1), b2 = __floats2bfloat162_rn(v2, v3);
+                        packed[2 * e4] = *reinterpret_cast<const uint32_t*>(&a2);
+                        packed[2 * e4 + 1] = *reinterpret_cast<const uint32_t*>(&b2);
                     } else {
-                        for (int e = 0; e < 32 && n0 + c0 + e < P.Nout; ++e)
-                            reinterpret_cast<uint16_t*>(dst)[e] = (uint16_t)(packed[e >> 1] >> (16 * (e & 1)));
+                        const __half2 a2 = __floats2half2_rn(v0, v1), b2 = __floats2half2_rn(v2, v3);
+                        packed[2 * e4] = *reinterpret_cast<const uint32_t*>(&a2);
+                        packed[2 * e4 + 1] = *reinterpret_cast<const uint32_t*>(&b2);
                     }
+                }
+                unsigned char* dst = static_cast<unsigned char*>(P.out) + ((size_t)row * P.ld_out + n0 + c0) * 2;
+                if (n0 + c0 + 32 <= P.Nout && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+#pragma unroll
+                    for (int v4 = 0; v4 < 4; ++v4)
+                        reinterpret_cast<uint4*>(dst)[v4] =
+                            make_uint4(packed[4 * v4], packed[4 * v4 + 1], packed[4 * v4 + 2], packed[4 * v4 + 3]);
+                } else {   // ragged edge or unaligned row: element stores, statically indexed
+#pragma unroll
+                    for (int e = 0; e < 32; ++e)
+                        if (n0 + c0 + e < P.Nout)
+                            reinterpret_cast<uint16_t*>(dst)[e] = (uint16_t)(packed[e >> 1] >> (16 * (e & 1)));
                 }
             }
         }
