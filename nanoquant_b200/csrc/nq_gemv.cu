@@ -89,11 +89,13 @@ struct Job {
     int items;            // ceil(rows / 32)
     int in_kind, out_kind;
     int vec;              // rows of `in` / `pre` are 16-byte aligned and K % 8 == 0
+    int tile_start;       // index of this job's row tile 0 in the phase's flattened tile list
 };
 
 struct Phase {
     Job job[kMaxJobs];
     int njobs;
+    int total_tiles;      // row tiles (32 rows) of all jobs of the phase
 };
 
 struct GemvParams {
@@ -347,15 +349,29 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 // pair (two row groups x 256 columns), pairs tile-major, one contiguous range per warp.
 struct PairStream {
     int my_items;   // row tiles (32 rows) of this CTA in the job
+    int first;      // the first of them (they are consecutive)
     int my_pairs;   // pairs of this warp
     int begin_il, begin_c;   // first pair of this warp: local tile index, chunk
     int l_il, l_c, l_n;      // next pair to fetch
 };
 
+// The row tiles (32 rows) of all jobs of a phase form one flattened list that is cut into gridDim.x
+// contiguous ranges, one per CTA.  A CTA therefore prepares the input of one job only, unless its range
+// crosses a job boundary, and streams consecutive memory.  Returns the CTA's tiles of `jb`: first tile, count.
+__device__ __forceinline__ int my_tiles(const Job& jb, int total_tiles, int& first) {
+    const int lo = (int)(((long long)total_tiles * (int)blockIdx.x) / (int)gridDim.x);
+    const int hi = (int)(((long long)total_tiles * ((int)blockIdx.x + 1)) / (int)gridDim.x);
+    const int a = lo > jb.tile_start ? lo : jb.tile_start;
+    const int e = jb.tile_start + jb.items;
+    const int b = hi < e ? hi : e;
+    first = a - jb.tile_start;
+    return b > a ? b - a : 0;
+}
+
 __device__ __forceinline__ void stream_issue(PairStream& st, const Job& jb, uint4* ring, int lane) {
     if (st.l_n < st.my_pairs) {
         const int row_groups = (jb.rows + 15) >> 4;
-        const int rg = 2 * ((int)blockIdx.x + st.l_il * (int)gridDim.x);
+        const int rg = 2 * (st.first + st.l_il);
         const int rgb = (rg + 1 < row_groups) ? rg + 1 : rg;  // odd tail: re-read, result discarded
         uint4* dst = ring + (st.l_n % kStages) * 64 + lane;
         cp_async16(dst, jb.tiles + ((size_t)rg * jb.chunks + st.l_c) * 32 + lane);
@@ -369,8 +385,9 @@ __device__ __forceinline__ void stream_issue(PairStream& st, const Job& jb, uint
 // Set the cursor up and start the first weight loads of a job.  They do not depend on
 // the job's input vector, so this runs before the input is ready (for a phase-2 job:
 // before the device-wide barrier, which then overlaps with the loads).
-__device__ __forceinline__ void stream_begin(PairStream& st, const Job& jb, uint4* ring, int warp, int lane) {
-    st.my_items = ((int)blockIdx.x < jb.items) ? (jb.items - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+__device__ __forceinline__ void stream_begin(PairStream& st, const Job& jb, int total_tiles, uint4* ring, int warp,
+                                             int lane) {
+    st.my_items = my_tiles(jb, total_tiles, st.first);
     const int npairs = st.my_items * jb.chunks;
     const int p_begin = (int)((long long)npairs * warp / kGemvWarps);
     st.my_pairs = (int)((long long)npairs * (warp + 1) / kGemvWarps) - p_begin;
@@ -381,12 +398,15 @@ __device__ __forceinline__ void stream_begin(PairStream& st, const Job& jb, uint
     for (int d = 0; d < kStages - 1; ++d) stream_issue(st, jb, ring, lane);
     // the output scales are needed right after the main loop: pull them towards L2 now
     if (jb.post && (int)threadIdx.x < st.my_items) {
-        const int row = 32 * ((int)blockIdx.x + (int)threadIdx.x * (int)gridDim.x);
+        const int row = 32 * (st.first + (int)threadIdx.x);
         asm volatile("prefetch.global.L2 [%0];" ::"l"(static_cast<const char*>(jb.post) + 2 * (size_t)row));
     }
 }
 
-__device__ __forceinline__ bool cta_has_items(const Job& jb) { return (int)blockIdx.x < jb.items; }
+__device__ __forceinline__ bool cta_has_items(const Job& jb, int total_tiles) {
+    int f;
+    return my_tiles(jb, total_tiles, f) > 0;
+}
 
 // The whole launch for one CTA: the jobs of phase 1, the device-wide barrier, the jobs
 // of phase 2.  CG = column groups of 8 MMA columns (3 columns per token).
@@ -406,13 +426,13 @@ __device__ __forceinline__ bool run_all(const Phase* phases, const GemvParams& P
     const int njobs = phases[0].njobs;        // same count in both phases
     auto job_of = [&](int s) -> const Job& { return phases[s >= njobs].job[s >= njobs ? s - njobs : s]; };
     auto next_step = [&](int s) {             // first step >= s in which this CTA owns row tiles
-        while (s < 2 * njobs && !cta_has_items(job_of(s))) ++s;
+        while (s < 2 * njobs && !cta_has_items(job_of(s), phases[s >= njobs].total_tiles)) ++s;
         return s;
     };
     bool barrier_done = false;
     PairStream st;
     int s = next_step(0);
-    if (s < 2 * njobs) stream_begin(st, job_of(s), ring, warp, lane);
+    if (s < 2 * njobs) stream_begin(st, job_of(s), phases[s >= njobs].total_tiles, ring, warp, lane);
     NQ_TRACE(1);
 #pragma unroll 1
     while (true) {
@@ -485,12 +505,13 @@ __device__ __forceinline__ bool run_all(const Phase* phases, const GemvParams& P
         // start the next job's weight stream before this job's epilogue and before any barrier
         const int my_items = st.my_items;
         const int s_next = next_step(s + 1);
-        if (s_next < 2 * njobs) stream_begin(st, job_of(s_next), ring, warp, lane);
+        const int first_tile_of_job = st.first;
+        if (s_next < 2 * njobs) stream_begin(st, job_of(s_next), phases[s_next >= njobs].total_tiles, ring, warp, lane);
         // finalise: thread -> (item, row, token).  The three column sums of a token are the byte terms
         // of 128 * sum_{bit=1}(X); result = sum(X) - 2 * sum_{bit=1}(X) = sum(X) - terms / 64.
         for (int i = tid; i < my_items * 32 * P.T; i += kGemvThreads) {
             const int tok = i % P.T, rr = (i / P.T) & 31, il = i / (32 * P.T);
-            const int row = 32 * ((int)blockIdx.x + il * (int)gridDim.x) + rr;
+            const int row = 32 * (first_tile_of_job + il) + rr;
             if (row < jb.rows) {
                 const int* c = s1 + il * (32 * kCols) + rr * kCols + 3 * tok;
                 const long long terms = (long long)c[2] * 65536 + (long long)c[1] * 256 + (long long)c[0];
@@ -633,12 +654,13 @@ int nq_gemv_group_fwd(const nq_linear_desc* d, int n_linears, int T, int dtype, 
         if (st != NQ_OK) return st;
     }
     const int grid = sm_count();
-    int max_items = 1;
+    int tot1 = 0, tot2 = 0;
     for (int i = 0; i < n_linears; ++i) {
-        const int it1 = ((d[i].R + 31) / 32 + grid - 1) / grid, it2 = ((d[i].M + 31) / 32 + grid - 1) / grid;
-        max_items = it1 > max_items ? it1 : max_items;
-        max_items = it2 > max_items ? it2 : max_items;
+        tot1 += (d[i].R + 31) / 32;
+        tot2 += (d[i].M + 31) / 32;
     }
+    const int tot = tot1 > tot2 ? tot1 : tot2;
+    const int max_items = (tot + grid - 1) / grid + 1;   // longest contiguous range a CTA can get
     const int kpad = (maxK + 255) / 256 * 256;
     const int stride = kpad + 32;  // 32 mod 128: conflict-free 64-bit fragment loads
 
@@ -663,6 +685,7 @@ int nq_gemv_group_fwd(const nq_linear_desc* d, int n_linears, int T, int dtype, 
         P.max_items = max_items;
         P.phase[0].njobs = P.phase[1].njobs = n_linears;
         size_t off = kHeaderBytes;
+        int tiles_a = 0, tiles_b = 0;   // running tile counts of the two phases
         for (int i = 0; i < n_linears; ++i) {
             const nq_linear_desc& L = d[i];
             float* tbuf = reinterpret_cast<float*>(static_cast<char*>(scratch) + off);
@@ -682,6 +705,8 @@ int nq_gemv_group_fwd(const nq_linear_desc* d, int n_linears, int T, int dtype, 
             a.in_kind = dtype;
             a.out_kind = KIND_F32;
             a.vec = (L.N % 8 == 0) && (L.ldx % 8 == 0) && aligned16(a.in) && aligned16(L.s_in);
+            a.tile_start = tiles_a;
+            tiles_a += a.items;
             Job& b = P.phase[1].job[i];
             b.tiles = static_cast<const uint4*>(L.u_tiles);
             b.in = tbuf;
@@ -697,7 +722,11 @@ int nq_gemv_group_fwd(const nq_linear_desc* d, int n_linears, int T, int dtype, 
             b.in_kind = KIND_F32;
             b.out_kind = dtype;
             b.vec = (L.R % 8 == 0);  // the intermediate lives in the 256-byte aligned scratch
+            b.tile_start = tiles_b;
+            tiles_b += b.items;
         }
+        P.phase[0].total_tiles = tiles_a;
+        P.phase[1].total_tiles = tiles_b;
         void* args[] = {&P};
         const void* fn = cg_for(tn) == 1 ? (const void*)gemv_group_kernel<1> : (const void*)gemv_group_kernel<2>;
         NQ_CUDA_TRY(cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(kGemvThreads), args, smem_for(tn),
