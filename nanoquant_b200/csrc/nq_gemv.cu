@@ -433,6 +433,10 @@ __device__ __forceinline__ bool run_all(const Phase* phases, const GemvParams& P
     PairStream st;
     int s = next_step(0);
     if (s < 2 * njobs) stream_begin(st, job_of(s), phases[s >= njobs].total_tiles, ring, warp, lane);
+    // Programmatic dependent launch: everything above (descriptor copy, first weight loads) may overlap
+    // with the tail of the previous kernel in the stream; the activations and the scratch (shared with
+    // that kernel) are only touched after it has completed.  No-ops without the launch attribute.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     NQ_TRACE(1);
 #pragma unroll 1
     while (true) {
@@ -440,6 +444,9 @@ __device__ __forceinline__ bool run_all(const Phase* phases, const GemvParams& P
             NQ_TRACE(8);
             if (!grid_barrier(P.header, gridDim.x)) return false;
             barrier_done = true;
+            // Every CTA of this grid is resident now, so CTAs of the next kernel that start early cannot
+            // keep one of ours from being scheduled: let the next kernel begin its prologue.
+            asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
             NQ_TRACE(9);
         }
         if (s >= 2 * njobs) break;
@@ -729,8 +736,31 @@ int nq_gemv_group_fwd(const nq_linear_desc* d, int n_linears, int T, int dtype, 
         P.phase[1].total_tiles = tiles_b;
         void* args[] = {&P};
         const void* fn = cg_for(tn) == 1 ? (const void*)gemv_group_kernel<1> : (const void*)gemv_group_kernel<2>;
-        NQ_CUDA_TRY(cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(kGemvThreads), args, smem_for(tn),
-                                                as_stream(stream)));
+        // Cooperative launch (all CTAs co-resident for the device-wide barrier) plus programmatic stream
+        // serialization, so that this kernel's prologue overlaps the previous kernel's tail.  If the driver
+        // refuses the combination once, plain cooperative launches are used from then on.
+        static bool pdl_ok = true;
+        cudaLaunchConfig_t cfg;
+        memset(&cfg, 0, sizeof(cfg));
+        cfg.gridDim = dim3(grid);
+        cfg.blockDim = dim3(kGemvThreads);
+        cfg.dynamicSmemBytes = smem_for(tn);
+        cfg.stream = as_stream(stream);
+        cudaLaunchAttribute attrs[2];
+        attrs[0].id = cudaLaunchAttributeCooperative;
+        attrs[0].val.cooperative = 1;
+        attrs[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attrs[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attrs;
+        cfg.numAttrs = pdl_ok ? 2 : 1;
+        cudaError_t e = cudaLaunchKernelExC(&cfg, fn, args);
+        if (e != cudaSuccess && pdl_ok) {
+            (void)cudaGetLastError();
+            pdl_ok = false;
+            cfg.numAttrs = 1;
+            e = cudaLaunchKernelExC(&cfg, fn, args);
+        }
+        NQ_CUDA_TRY(e);
     }
     return NQ_OK;
 }
