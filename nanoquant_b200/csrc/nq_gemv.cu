@@ -286,6 +286,58 @@ __device__ __noinline__ void quantise_vec(const Job& jb, int T, int8_t* xq, int 
     __syncthreads();
 }
 
+// Vector path for inputs with at most one 8-column block per thread (T * Kpad / 8 <= threads, e.g. one token of
+// 4096 columns): each value is loaded once and stays in registers between the max pass and the conversion, so
+// the phase pays a single memory round trip for its input.  Kpad / 8 is a multiple of 32: a warp serves one token.
+template <int IN_KIND>
+__device__ __noinline__ void quantise_one(const Job& jb, int T, int8_t* xq, int stride, float* red,
+                                          int* sumx, float* delta) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int K = jb.K, nv8 = jb.chunks * 32;
+    constexpr bool kHasPre = (IN_KIND != KIND_F32);
+    const int t = tid / nv8, k8 = (tid - t * nv8) * 8;
+    const bool active = t < T;
+    float p[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) p[e] = 0.f;
+    if (active && k8 < K) {
+        load8<IN_KIND>(jb.in, t * jb.ld_in + k8, p);
+        if (kHasPre) {
+            float s[8];
+            load8<IN_KIND>(jb.pre, k8, s);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) p[e] *= s[e];
+        }
+    }
+    float m = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) m = fmaxf(m, fabsf(p[e]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    // per-warp maxima in the [warp][token] table the scale step reads: a warp contributes to its token only
+    if (lane < kMaxTok) red[warp * kMaxTok + lane] = (active && lane == t) ? m : 0.f;
+    __syncthreads();
+    token_scales(T, red, sumx, delta);
+    __syncthreads();
+    if (active) {
+        const float inv = red[kGemvWarps * kMaxTok + t];
+        const int j = (k8 >> 5) & 7;
+        uint32_t Y[8];
+        int acc = 0;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const int X = __float2int_rn(p[e] * inv);
+            acc += X;
+            Y[e] = (uint32_t)class_shift(X, j);
+        }
+        store_terms(Y, xq + (3 * t) * stride, stride, k8);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (lane == 0 && acc != 0) atomicAdd(&sumx[t], acc);
+    }
+    __syncthreads();
+}
+
 // Scalar path for unaligned or ragged inputs (any K, any alignment).
 __device__ __noinline__ void quantise_scalar(const Job& jb, int T, int scale_kind, int8_t* xq, int stride,
                                              float* red, int* sumx, float* delta) {
@@ -332,6 +384,11 @@ __device__ __noinline__ void quantise_scalar(const Job& jb, int T, int scale_kin
 __device__ __forceinline__ void quantise_input(const Job& jb, int T, int scale_kind, int8_t* xq, int stride,
                                                float* red, int* sumx, float* delta) {
     if (!jb.vec) quantise_scalar(jb, T, scale_kind, xq, stride, red, sumx, delta);
+    else if (T * jb.chunks * 32 <= kGemvThreads) {
+        if (jb.in_kind == KIND_F32) quantise_one<KIND_F32>(jb, T, xq, stride, red, sumx, delta);
+        else if (jb.in_kind == KIND_F16) quantise_one<KIND_F16>(jb, T, xq, stride, red, sumx, delta);
+        else quantise_one<KIND_BF16>(jb, T, xq, stride, red, sumx, delta);
+    }
     else if (jb.in_kind == KIND_F32) quantise_vec<KIND_F32>(jb, T, xq, stride, red, sumx, delta);
     else if (jb.in_kind == KIND_F16) quantise_vec<KIND_F16>(jb, T, xq, stride, red, sumx, delta);
     else quantise_vec<KIND_BF16>(jb, T, xq, stride, red, sumx, delta);
