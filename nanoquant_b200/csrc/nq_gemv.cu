@@ -90,6 +90,7 @@ struct Job {
     int in_kind, out_kind;
     int vec;              // rows of `in` / `pre` are 16-byte aligned and K % 8 == 0
     int tile_start;       // index of this job's row tile 0 in the phase's flattened tile list
+    int post_vec;         // `post` is 16-byte aligned and rows % 8 == 0: staged in shared memory with 16-byte copies
 };
 
 struct Phase {
@@ -410,6 +411,7 @@ struct PairStream {
     int my_pairs;   // pairs of this warp
     int begin_il, begin_c;   // first pair of this warp: local tile index, chunk
     int l_il, l_c, l_n;      // next pair to fetch
+    int slot;                // which half of the output-scale staging buffer this job uses
 };
 
 // The row tiles (32 rows) of all jobs of a phase form one flattened list that is cut into gridDim.x
@@ -443,7 +445,7 @@ __device__ __forceinline__ void stream_issue(PairStream& st, const Job& jb, uint
 // the job's input vector, so this runs before the input is ready (for a phase-2 job:
 // before the device-wide barrier, which then overlaps with the loads).
 __device__ __forceinline__ void stream_begin(PairStream& st, const Job& jb, int total_tiles, uint4* ring, int warp,
-                                             int lane) {
+                                             int lane, uint16_t* post_s, int max_items) {
     st.my_items = my_tiles(jb, total_tiles, st.first);
     const int npairs = st.my_items * jb.chunks;
     const int p_begin = (int)((long long)npairs * warp / kGemvWarps);
@@ -451,13 +453,19 @@ __device__ __forceinline__ void stream_begin(PairStream& st, const Job& jb, int 
     st.begin_il = p_begin / jb.chunks;
     st.begin_c = p_begin - st.begin_il * jb.chunks;
     st.l_il = st.begin_il; st.l_c = st.begin_c; st.l_n = 0;
+    st.slot ^= 1;
+    // The output scales of this CTA's rows are needed right after the main loop: copy them into shared
+    // memory now (part of this thread's first copy group, complete when the main loop has drained).
+    if (jb.post_vec) {
+        const int row0 = 32 * st.first;
+        const int nrows = min(32 * st.my_items, jb.rows - row0);
+        const int i = (int)threadIdx.x;
+        if (8 * i < nrows)
+            cp_async16(post_s + st.slot * (32 * max_items) + 8 * i,
+                       static_cast<const uint16_t*>(jb.post) + row0 + 8 * i);
+    }
 #pragma unroll
     for (int d = 0; d < kStages - 1; ++d) stream_issue(st, jb, ring, lane);
-    // the output scales are needed right after the main loop: pull them towards L2 now
-    if (jb.post && (int)threadIdx.x < st.my_items) {
-        const int row = 32 * (st.first + (int)threadIdx.x);
-        asm volatile("prefetch.global.L2 [%0];" ::"l"(static_cast<const char*>(jb.post) + 2 * (size_t)row));
-    }
 }
 
 __device__ __forceinline__ bool cta_has_items(const Job& jb, int total_tiles) {
@@ -479,6 +487,8 @@ __device__ __forceinline__ bool run_all(const Phase* phases, const GemvParams& P
     uint4* ring = reinterpret_cast<uint4*>(smem + kFixedBytes) + warp * (kStages * 64);  // [stage][2][32]
     int* s1 = reinterpret_cast<int*>(smem + kFixedBytes + kRingBytes);    // [max_items][32 rows][kCols]
     int8_t* xq = reinterpret_cast<int8_t*>(smem + kFixedBytes + kRingBytes + (size_t)P.max_items * (128 * kCols));
+    // output scales of the current and the next job: [2][max_items][32] two-byte entries behind the int8 vectors
+    uint16_t* post_s = reinterpret_cast<uint16_t*>(xq + (size_t)3 * P.T * P.xq_stride);
 
     const int njobs = phases[0].njobs;        // same count in both phases
     auto job_of = [&](int s) -> const Job& { return phases[s >= njobs].job[s >= njobs ? s - njobs : s]; };
@@ -488,8 +498,15 @@ __device__ __forceinline__ bool run_all(const Phase* phases, const GemvParams& P
     };
     bool barrier_done = false;
     PairStream st;
+    st.slot = 0;
     int s = next_step(0);
-    if (s < 2 * njobs) stream_begin(st, job_of(s), phases[s >= njobs].total_tiles, ring, warp, lane);
+    if (s < 2 * njobs) {
+        const Job& j0 = job_of(s);
+        stream_begin(st, j0, phases[s >= njobs].total_tiles, ring, warp, lane, post_s, P.max_items);
+        // the input scales are constants of the layer: pull them towards L2 while the previous kernel drains
+        if (s < njobs && j0.pre && tid * 64 < j0.K)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(static_cast<const char*>(j0.pre) + 128 * (size_t)tid));
+    }
     // Programmatic dependent launch: everything above (descriptor copy, first weight loads) may overlap
     // with the tail of the previous kernel in the stream; the activations and the scratch (shared with
     // that kernel) are only touched after it has completed.  No-ops without the launch attribute.
@@ -570,7 +587,9 @@ __device__ __forceinline__ bool run_all(const Phase* phases, const GemvParams& P
         const int my_items = st.my_items;
         const int s_next = next_step(s + 1);
         const int first_tile_of_job = st.first;
-        if (s_next < 2 * njobs) stream_begin(st, job_of(s_next), phases[s_next >= njobs].total_tiles, ring, warp, lane);
+        const uint16_t* my_post = post_s + st.slot * (32 * P.max_items);
+        if (s_next < 2 * njobs)
+            stream_begin(st, job_of(s_next), phases[s_next >= njobs].total_tiles, ring, warp, lane, post_s, P.max_items);
         // finalise: thread -> (item, row, token).  The three column sums of a token are the byte terms
         // of 128 * sum_{bit=1}(X); result = sum(X) - 2 * sum_{bit=1}(X) = sum(X) - terms / 64.
         for (int i = tid; i < my_items * 32 * P.T; i += kGemvThreads) {
@@ -581,7 +600,8 @@ __device__ __forceinline__ bool run_all(const Phase* phases, const GemvParams& P
                 const long long terms = (long long)c[2] * 65536 + (long long)c[1] * 256 + (long long)c[0];
                 const long long r = (long long)sumx[tok] - terms / 64;
                 float val = (float)r * delta[tok];
-                if (jb.post) val *= load_as_float(jb.post, row, P.scale_kind);
+                if (jb.post) val *= jb.post_vec ? load_as_float(my_post, il * 32 + rr, P.scale_kind)
+                                                : load_as_float(jb.post, row, P.scale_kind);
                 if (jb.out_kind == KIND_F32) {
                     static_cast<float*>(jb.out)[tok * jb.ld_out + row] = val;
                 } else if (jb.out_kind == KIND_F16) {
@@ -731,7 +751,8 @@ int nq_gemv_group_fwd(const nq_linear_desc* d, int n_linears, int T, int dtype, 
     // tokens are processed in groups that fit the MMA columns (3 per token) and shared memory
     auto cg_for = [](int t) { return t <= 2 ? 1 : 2; };
     auto smem_for = [&](int t) {
-        return kFixedBytes + kRingBytes + (size_t)max_items * (128 * 8 * cg_for(t)) + (size_t)3 * t * stride;
+        return kFixedBytes + kRingBytes + (size_t)max_items * (128 * 8 * cg_for(t)) + (size_t)3 * t * stride +
+               (size_t)max_items * 128;   // + output scales of two jobs
     };
     int tg = T < kMaxTok ? T : kMaxTok;
     while (tg > 1 && smem_for(tg) > (size_t)smem_limit) --tg;
@@ -769,6 +790,7 @@ int nq_gemv_group_fwd(const nq_linear_desc* d, int n_linears, int T, int dtype, 
             a.in_kind = dtype;
             a.out_kind = KIND_F32;
             a.vec = (L.N % 8 == 0) && (L.ldx % 8 == 0) && aligned16(a.in) && aligned16(L.s_in);
+            a.post_vec = L.s_mid && (L.R % 8 == 0) && aligned16(L.s_mid);
             a.tile_start = tiles_a;
             tiles_a += a.items;
             Job& b = P.phase[1].job[i];
@@ -786,6 +808,7 @@ int nq_gemv_group_fwd(const nq_linear_desc* d, int n_linears, int T, int dtype, 
             b.in_kind = KIND_F32;
             b.out_kind = dtype;
             b.vec = (L.R % 8 == 0);  // the intermediate lives in the 256-byte aligned scratch
+            b.post_vec = (L.M % 8 == 0) && aligned16(L.s_out);
             b.tile_start = tiles_b;
             tiles_b += b.items;
         }
