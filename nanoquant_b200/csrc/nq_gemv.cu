@@ -46,6 +46,9 @@ namespace nq {
 #ifndef NQ_GEMV_STAGES
 #define NQ_GEMV_STAGES 4
 #endif
+#ifndef NQ_GEMV_MIN_CTAS
+#define NQ_GEMV_MIN_CTAS 1
+#endif
 constexpr int kGemvThreads = NQ_GEMV_THREADS;
 constexpr int kGemvWarps = kGemvThreads / 32;
 constexpr int kMaxJobs = 4;         // linears per launch
@@ -53,7 +56,7 @@ constexpr int kMaxTok = 4;          // tokens per launch (3 byte terms each, 8 M
 constexpr int kQMax = 64000;        // |X| bound: X * 2^7 splits into three signed bytes
 constexpr int kMaxK = 32768;        // keeps sum(X) and every accumulator inside int32
 constexpr int kStages = NQ_GEMV_STAGES;          // 1 KB weight slots in flight per warp
-constexpr size_t kRedBytes = 384;   // per-warp maxima (kGemvWarps * 4 floats) + 4 inverse scales
+constexpr size_t kRedBytes = 384;   // per-warp maxima: kMaxTok * kGemvWarps floats (16-byte aligned rows)
 constexpr size_t kFixedBytes = 512;
 constexpr size_t kRingBytes = (size_t)kGemvWarps * kStages * 1024;
 constexpr unsigned kSpinLimit = 4000000u;
@@ -97,6 +100,7 @@ struct Phase {
     Job job[kMaxJobs];
     int njobs;
     int total_tiles;      // row tiles (32 rows) of all jobs of the phase
+    int tiles_q, tiles_r; // total_tiles = tiles_q * gridDim.x + tiles_r: CTA b owns tiles_q (+1 if b < tiles_r) tiles
 };
 
 struct GemvParams {
@@ -124,17 +128,24 @@ __device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, ui
 // Bounded device-wide barrier on {count, generation} words.  Returns false when the
 // wait expired (a status word is set and the caller returns).  One thread per CTA
 // arrives with a release and polls with acquires; the CTA barrier before and after
-// extends the ordering to every thread of the CTA.
-__device__ bool grid_barrier(unsigned* header, unsigned nblocks) {
+// extends the ordering to every thread of the CTA.  `my_gen` is the generation thread 0
+// read (barrier_generation) any time after the previous launch on these words completed
+// and before this arrival: it cannot change until every CTA has arrived, and reading it
+// early keeps one memory round trip off the critical path.  The count wraps to zero with
+// the last arrival (atom.inc), so the words need no reset between launches.
+__device__ __forceinline__ unsigned barrier_generation(const unsigned* header) {
+    unsigned g;
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(g) : "l"(header + 1) : "memory");
+    return g;
+}
+__device__ bool grid_barrier(unsigned* header, unsigned nblocks, unsigned my_gen) {
     __shared__ int ok;
     __syncthreads();
     if (threadIdx.x == 0) {
         ok = 1;
-        unsigned my_gen, old;
-        asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(my_gen) : "l"(header + 1) : "memory");
-        asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(old) : "l"(header) : "memory");
+        unsigned old;
+        asm volatile("atom.inc.acq_rel.gpu.global.u32 %0, [%1], %2;" : "=r"(old) : "l"(header), "r"(nblocks - 1) : "memory");
         if (old == nblocks - 1) {
-            asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(header), "r"(0u) : "memory");
             asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(header + 1) : "memory");
         } else {
             unsigned spins = 0, cur;
@@ -187,19 +198,29 @@ __device__ __forceinline__ int xq_pos(int k) {
     return (k & ~255) + (kin & 0xE0) + 2 * (kin & 12) + ((kin & 16) >> 2) + (kin & 3);
 }
 
-// red[warp * 4 + t] holds per-warp maxima of token t; thread t < T turns them into the
-// fixed-point scale of the token.
-__device__ __forceinline__ void token_scales(int T, float* red, int* sumx, float* delta) {
-    const int tid = threadIdx.x;
-    if (tid < T) {
-        float m = 0.f;
-        for (int w = 0; w < kGemvWarps; ++w) m = fmaxf(m, red[w * kMaxTok + tid]);
-        // a non-finite or zero maximum quantises everything to zero
-        const bool good = (m > 0.f) && (m < 3.0e38f);
-        red[kGemvWarps * kMaxTok + tid] = good ? (float)kQMax / m : 0.f;
-        delta[tid] = good ? m / (float)kQMax : 0.f;
-        sumx[tid] = 0;
+// red[t * kGemvWarps + warp] holds the per-warp maxima of token t.  Every thread derives the fixed-point
+// scale of its token from them itself (a few broadcast reads), which saves a serial step and a CTA barrier.
+__device__ __forceinline__ float token_max(const float* red, int t) {
+    const float4* r = reinterpret_cast<const float4*>(red + t * kGemvWarps);
+    float m = 0.f;
+#pragma unroll
+    for (int i = 0; i < kGemvWarps / 4; ++i) {
+        const float4 v = r[i];
+        m = fmaxf(m, fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)));
     }
+    return m;
+}
+// Units per value (0 when the maximum is zero or not finite: everything quantises to zero); the thread
+// for which `writer` holds records the value of one unit for the epilogue.
+__device__ __forceinline__ float token_inv(const float* red, int t, bool writer, float* delta) {
+    const float m = token_max(red, t);
+    const bool good = (m > 0.f) && (m < 3.0e38f);
+    if (writer) delta[t] = good ? m / (float)kQMax : 0.f;
+    return good ? (float)kQMax / m : 0.f;
+}
+// Warp-wide maximum of non-negative floats / sum of ints with one reduction instruction each.
+__device__ __forceinline__ float warp_max_abs(float m) {
+    return __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(m)));
 }
 
 // Write eight class-shifted operands (columns k8..k8+7 of one token) as three byte vectors.
@@ -247,17 +268,15 @@ __device__ __noinline__ void quantise_vec(const Job& jb, int T, int8_t* xq, int 
 #pragma unroll
             for (int e = 0; e < 8; ++e) m = fmaxf(m, fabsf(kHasPre ? v[e] * s[e] : v[e]));
         }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-        if (lane == 0) red[warp * kMaxTok + t] = m;
+        m = warp_max_abs(m);
+        if (lane == 0) red[t * kGemvWarps + warp] = m;
     }
-    __syncthreads();
-    token_scales(T, red, sumx, delta);
+    if (tid < kMaxTok) sumx[tid] = 0;
     __syncthreads();
     // pass 2: |p * inv| <= kQMax + 2^-7 by construction (same products as in pass 1), no clamp needed
 #pragma unroll 1
     for (int t = 0; t < T; ++t) {
-        const float inv = red[kGemvWarps * kMaxTok + t];
+        const float inv = token_inv(red, t, tid == 0, delta);
         int8_t* r0 = xq + (3 * t) * stride;
         int acc = 0;
 #pragma unroll 1
@@ -280,8 +299,7 @@ __device__ __noinline__ void quantise_vec(const Job& jb, int T, int8_t* xq, int 
             }
             store_terms(Y, r0, stride, k8);
         }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        acc = __reduce_add_sync(0xffffffffu, acc);
         if (lane == 0 && acc != 0) atomicAdd(&sumx[t], acc);
     }
     __syncthreads();
@@ -313,15 +331,13 @@ __device__ __noinline__ void quantise_one(const Job& jb, int T, int8_t* xq, int 
     float m = 0.f;
 #pragma unroll
     for (int e = 0; e < 8; ++e) m = fmaxf(m, fabsf(p[e]));
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-    // per-warp maxima in the [warp][token] table the scale step reads: a warp contributes to its token only
-    if (lane < kMaxTok) red[warp * kMaxTok + lane] = (active && lane == t) ? m : 0.f;
-    __syncthreads();
-    token_scales(T, red, sumx, delta);
+    m = warp_max_abs(m);
+    // per-warp maxima in the [token][warp] table: a warp contributes to its token only
+    if (lane < kMaxTok) red[lane * kGemvWarps + warp] = (active && lane == t) ? m : 0.f;
+    if (tid < kMaxTok) sumx[tid] = 0;
     __syncthreads();
     if (active) {
-        const float inv = red[kGemvWarps * kMaxTok + t];
+        const float inv = token_inv(red, t, k8 == 0, delta);
         const int j = (k8 >> 5) & 7;
         uint32_t Y[8];
         int acc = 0;
@@ -332,8 +348,7 @@ __device__ __noinline__ void quantise_one(const Job& jb, int T, int8_t* xq, int 
             Y[e] = (uint32_t)class_shift(X, j);
         }
         store_terms(Y, xq + (3 * t) * stride, stride, k8);
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        acc = __reduce_add_sync(0xffffffffu, acc);
         if (lane == 0 && acc != 0) atomicAdd(&sumx[t], acc);
     }
     __syncthreads();
@@ -351,16 +366,14 @@ __device__ __noinline__ void quantise_scalar(const Job& jb, int T, int scale_kin
             const float s = jb.pre ? load_as_float(jb.pre, k, scale_kind) : 1.f;
             m = fmaxf(m, fabsf(load_as_float(jb.in, t * jb.ld_in + k, jb.in_kind) * s));
         }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-        if (lane == 0) red[warp * kMaxTok + t] = m;
+        m = warp_max_abs(m);
+        if (lane == 0) red[t * kGemvWarps + warp] = m;
     }
-    __syncthreads();
-    token_scales(T, red, sumx, delta);
+    if (tid < kMaxTok) sumx[tid] = 0;
     __syncthreads();
 #pragma unroll 1
     for (int t = 0; t < T; ++t) {
-        const float inv = red[kGemvWarps * kMaxTok + t];
+        const float inv = token_inv(red, t, tid == 0, delta);
         int acc = 0;
         for (int k = tid; k < Kpad; k += kGemvThreads) {
             int X = 0;
@@ -375,8 +388,7 @@ __device__ __noinline__ void quantise_scalar(const Job& jb, int T, int scale_kin
             xq[(3 * t + 1) * stride + pos] = (int8_t)(((y + 0x80) >> 8) & 0xFF);
             xq[(3 * t + 2) * stride + pos] = (int8_t)(((y + 0x8080) >> 16) & 0xFF);
         }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        acc = __reduce_add_sync(0xffffffffu, acc);
         if (lane == 0 && acc != 0) atomicAdd(&sumx[t], acc);
     }
     __syncthreads();
@@ -415,16 +427,18 @@ struct PairStream {
 };
 
 // The row tiles (32 rows) of all jobs of a phase form one flattened list that is cut into gridDim.x
-// contiguous ranges, one per CTA.  A CTA therefore prepares the input of one job only, unless its range
-// crosses a job boundary, and streams consecutive memory.  Returns the CTA's tiles of `jb`: first tile, count.
-__device__ __forceinline__ int my_tiles(const Job& jb, int total_tiles, int& first) {
-    const int lo = (int)(((long long)total_tiles * (int)blockIdx.x) / (int)gridDim.x);
-    const int hi = (int)(((long long)total_tiles * ((int)blockIdx.x + 1)) / (int)gridDim.x);
-    const int a = lo > jb.tile_start ? lo : jb.tile_start;
-    const int e = jb.tile_start + jb.items;
-    const int b = hi < e ? hi : e;
+// contiguous ranges, one per CTA (the first tiles_r CTAs get one tile more).  A CTA therefore prepares the
+// input of one job only, unless its range crosses a job boundary, and streams consecutive memory.  The split
+// is precomputed on the host: this runs on the latency-critical path between two jobs.
+// Returns the CTA's tiles of `jb`: first tile, count.
+__device__ __forceinline__ int my_tiles(const Job& jb, const Phase& ph, int& first) {
+    const int b = (int)blockIdx.x;
+    const int lo = ph.tiles_q * b + min(b, ph.tiles_r);
+    const int hi = lo + ph.tiles_q + (b < ph.tiles_r ? 1 : 0);
+    const int a = max(lo, jb.tile_start);
+    const int e = min(hi, jb.tile_start + jb.items);
     first = a - jb.tile_start;
-    return b > a ? b - a : 0;
+    return e > a ? e - a : 0;
 }
 
 __device__ __forceinline__ void stream_issue(PairStream& st, const Job& jb, uint4* ring, int lane) {
@@ -444,14 +458,15 @@ __device__ __forceinline__ void stream_issue(PairStream& st, const Job& jb, uint
 // Set the cursor up and start the first weight loads of a job.  They do not depend on
 // the job's input vector, so this runs before the input is ready (for a phase-2 job:
 // before the device-wide barrier, which then overlaps with the loads).
-__device__ __forceinline__ void stream_begin(PairStream& st, const Job& jb, int total_tiles, uint4* ring, int warp,
+__device__ __forceinline__ void stream_begin(PairStream& st, const Job& jb, const Phase& ph, uint4* ring, int warp,
                                              int lane, uint16_t* post_s, int max_items) {
-    st.my_items = my_tiles(jb, total_tiles, st.first);
-    const int npairs = st.my_items * jb.chunks;
-    const int p_begin = (int)((long long)npairs * warp / kGemvWarps);
-    st.my_pairs = (int)((long long)npairs * (warp + 1) / kGemvWarps) - p_begin;
-    st.begin_il = p_begin / jb.chunks;
-    st.begin_c = p_begin - st.begin_il * jb.chunks;
+    st.my_items = my_tiles(jb, ph, st.first);
+    const int npairs = st.my_items * jb.chunks;            // < 2^27: the products below fit 32 bits
+    const int p_begin = npairs * warp / kGemvWarps;
+    st.my_pairs = npairs * (warp + 1) / kGemvWarps - p_begin;
+    st.begin_il = 0;
+    st.begin_c = p_begin;
+    while (st.begin_c >= jb.chunks) { st.begin_c -= jb.chunks; ++st.begin_il; }   // at most my_items steps
     st.l_il = st.begin_il; st.l_c = st.begin_c; st.l_n = 0;
     st.slot ^= 1;
     // The output scales of this CTA's rows are needed right after the main loop: copy them into shared
@@ -468,9 +483,9 @@ __device__ __forceinline__ void stream_begin(PairStream& st, const Job& jb, int 
     for (int d = 0; d < kStages - 1; ++d) stream_issue(st, jb, ring, lane);
 }
 
-__device__ __forceinline__ bool cta_has_items(const Job& jb, int total_tiles) {
+__device__ __forceinline__ bool cta_has_items(const Job& jb, const Phase& ph) {
     int f;
-    return my_tiles(jb, total_tiles, f) > 0;
+    return my_tiles(jb, ph, f) > 0;
 }
 
 // The whole launch for one CTA: the jobs of phase 1, the device-wide barrier, the jobs
@@ -493,7 +508,7 @@ __device__ __forceinline__ bool run_all(const Phase* phases, const GemvParams& P
     const int njobs = phases[0].njobs;        // same count in both phases
     auto job_of = [&](int s) -> const Job& { return phases[s >= njobs].job[s >= njobs ? s - njobs : s]; };
     auto next_step = [&](int s) {             // first step >= s in which this CTA owns row tiles
-        while (s < 2 * njobs && !cta_has_items(job_of(s), phases[s >= njobs].total_tiles)) ++s;
+        while (s < 2 * njobs && !cta_has_items(job_of(s), phases[s >= njobs])) ++s;
         return s;
     };
     bool barrier_done = false;
@@ -502,7 +517,7 @@ __device__ __forceinline__ bool run_all(const Phase* phases, const GemvParams& P
     int s = next_step(0);
     if (s < 2 * njobs) {
         const Job& j0 = job_of(s);
-        stream_begin(st, j0, phases[s >= njobs].total_tiles, ring, warp, lane, post_s, P.max_items);
+        stream_begin(st, j0, phases[s >= njobs], ring, warp, lane, post_s, P.max_items);
         // the input scales are constants of the layer: pull them towards L2 while the previous kernel drains
         if (s < njobs && j0.pre && tid * 64 < j0.K)
             asm volatile("prefetch.global.L2 [%0];" ::"l"(static_cast<const char*>(j0.pre) + 128 * (size_t)tid));
@@ -511,12 +526,13 @@ __device__ __forceinline__ bool run_all(const Phase* phases, const GemvParams& P
     // with the tail of the previous kernel in the stream; the activations and the scratch (shared with
     // that kernel) are only touched after it has completed.  No-ops without the launch attribute.
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    const unsigned my_gen = tid == 0 ? barrier_generation(P.header) : 0u;
     NQ_TRACE(1);
 #pragma unroll 1
     while (true) {
         if (!barrier_done && s >= njobs) {    // everything of phase 1 is written: publish, then read t
             NQ_TRACE(8);
-            if (!grid_barrier(P.header, gridDim.x)) return false;
+            if (!grid_barrier(P.header, gridDim.x, my_gen)) return false;
             barrier_done = true;
             // Every CTA of this grid is resident now, so CTAs of the next kernel that start early cannot
             // keep one of ours from being scheduled: let the next kernel begin its prologue.
@@ -589,28 +605,31 @@ __device__ __forceinline__ bool run_all(const Phase* phases, const GemvParams& P
         const int first_tile_of_job = st.first;
         const uint16_t* my_post = post_s + st.slot * (32 * P.max_items);
         if (s_next < 2 * njobs)
-            stream_begin(st, job_of(s_next), phases[s_next >= njobs].total_tiles, ring, warp, lane, post_s, P.max_items);
-        // finalise: thread -> (item, row, token).  The three column sums of a token are the byte terms
-        // of 128 * sum_{bit=1}(X); result = sum(X) - 2 * sum_{bit=1}(X) = sum(X) - terms / 64.
-        for (int i = tid; i < my_items * 32 * P.T; i += kGemvThreads) {
-            const int tok = i % P.T, rr = (i / P.T) & 31, il = i / (32 * P.T);
-            const int row = 32 * (first_tile_of_job + il) + rr;
-            if (row < jb.rows) {
-                const int* c = s1 + il * (32 * kCols) + rr * kCols + 3 * tok;
-                const long long terms = (long long)c[2] * 65536 + (long long)c[1] * 256 + (long long)c[0];
-                const long long r = (long long)sumx[tok] - terms / 64;
-                float val = (float)r * delta[tok];
-                if (jb.post) val *= jb.post_vec ? load_as_float(my_post, il * 32 + rr, P.scale_kind)
-                                                : load_as_float(jb.post, row, P.scale_kind);
-                if (jb.out_kind == KIND_F32) {
-                    static_cast<float*>(jb.out)[tok * jb.ld_out + row] = val;
-                } else if (jb.out_kind == KIND_F16) {
-                    // same saturation bounds as the reference epilogue
-                    val = fminf(fmaxf(val, -64504.0f), 64504.0f);
-                    static_cast<__half*>(jb.out)[tok * jb.ld_out + row] = __float2half(val);
-                } else {
-                    val = fminf(fmaxf(val, -3.3895313892515355e+38f), 3.3895313892515355e+38f);
-                    static_cast<__nv_bfloat16*>(jb.out)[tok * jb.ld_out + row] = __float2bfloat16(val);
+            stream_begin(st, job_of(s_next), phases[s_next >= njobs], ring, warp, lane, post_s, P.max_items);
+        // finalise: thread -> (token slot, row slot); tokens beyond the slot count and rows beyond the 128 row
+        // slots are covered by the strides.  The three column sums of a token are the byte terms of
+        // 128 * sum_{bit=1}(X); result = sum(X) - 2 * sum_{bit=1}(X) = sum(X) - terms / 64 (terms is a multiple of 128).
+        for (int tok = tid >> 7; tok < P.T; tok += kGemvThreads >> 7) {
+            const long long sx = sumx[tok];
+            const float dl = delta[tok];
+            for (int idx = tid & 127; idx < my_items * 32; idx += 128) {
+                const int row = 32 * first_tile_of_job + idx;
+                if (row < jb.rows) {
+                    const int* c = s1 + idx * kCols + 3 * tok;
+                    const long long terms = (long long)c[2] * 65536 + (long long)c[1] * 256 + (long long)c[0];
+                    float val = (float)(sx - (terms >> 6)) * dl;
+                    if (jb.post) val *= jb.post_vec ? load_as_float(my_post, idx, P.scale_kind)
+                                                    : load_as_float(jb.post, row, P.scale_kind);
+                    if (jb.out_kind == KIND_F32) {
+                        static_cast<float*>(jb.out)[tok * jb.ld_out + row] = val;
+                    } else if (jb.out_kind == KIND_F16) {
+                        // same saturation bounds as the reference epilogue
+                        val = fminf(fmaxf(val, -64504.0f), 64504.0f);
+                        static_cast<__half*>(jb.out)[tok * jb.ld_out + row] = __float2half(val);
+                    } else {
+                        val = fminf(fmaxf(val, -3.3895313892515355e+38f), 3.3895313892515355e+38f);
+                        static_cast<__nv_bfloat16*>(jb.out)[tok * jb.ld_out + row] = __float2bfloat16(val);
+                    }
                 }
             }
         }
@@ -622,7 +641,7 @@ __device__ __forceinline__ bool run_all(const Phase* phases, const GemvParams& P
 }
 
 template <int CG>
-__global__ void __launch_bounds__(kGemvThreads, 1) gemv_group_kernel(const __grid_constant__ GemvParams P) {
+__global__ void __launch_bounds__(kGemvThreads, NQ_GEMV_MIN_CTAS) gemv_group_kernel(const __grid_constant__ GemvParams P) {
     extern __shared__ __align__(16) unsigned char smem[];
     // The descriptors are read with runtime indices; one cooperative copy out of the
     // parameter bank into shared memory replaces many serial constant-cache misses.
@@ -744,7 +763,7 @@ int nq_gemv_group_fwd(const nq_linear_desc* d, int n_linears, int T, int dtype, 
         tot2 += (d[i].M + 31) / 32;
     }
     const int tot = tot1 > tot2 ? tot1 : tot2;
-    const int max_items = (tot + grid - 1) / grid + 1;   // longest contiguous range a CTA can get
+    const int max_items = (tot + grid - 1) / grid;       // longest contiguous range a CTA can get
     const int kpad = (maxK + 255) / 256 * 256;
     const int stride = kpad + 32;  // 32 mod 128: conflict-free 64-bit fragment loads
 
@@ -814,6 +833,10 @@ int nq_gemv_group_fwd(const nq_linear_desc* d, int n_linears, int T, int dtype, 
         }
         P.phase[0].total_tiles = tiles_a;
         P.phase[1].total_tiles = tiles_b;
+        for (int ph = 0; ph < 2; ++ph) {
+            P.phase[ph].tiles_q = P.phase[ph].total_tiles / grid;
+            P.phase[ph].tiles_r = P.phase[ph].total_tiles % grid;
+        }
         void* args[] = {&P};
         const void* fn = cg_for(tn) == 1 ? (const void*)gemv_group_kernel<1> : (const void*)gemv_group_kernel<2>;
         // Cooperative launch (all CTAs co-resident for the device-wide barrier) plus programmatic stream
