@@ -212,6 +212,12 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_stage_kernel(const __grid_c
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + kOffMisc);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kOffMisc + 4);
 
+    // Programmatic dependent launch: the next kernel of the stream (normally the second stage, or the next
+    // linear's first stage) may start its prologue and its weight expansion on SMs this grid leaves idle.
+    // It needs no resource of this grid to finish.  In turn this kernel touches memory that an earlier kernel
+    // may still use only behind griddepcontrol.wait: the activation loads (warp 0) and the output stores.
+    // Weights and scales are constants of the layer.  Both instructions are no-ops without the launch attribute.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (threadIdx.x == 0) {
         for (int s = 0; s < kGemmStages; ++s) {
             mbar_init(bar_full(s), 1);
@@ -253,6 +259,7 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_stage_kernel(const __grid_c
     if (warp == 0) {
         // ------------------------------------------------------------ producer
         if (lane == 0) {
+            asm volatile("griddepcontrol.wait;" ::: "memory");   // the activations come from the previous kernel
             for (int kb = 0; kb < nkb; ++kb) {
                 const int s = kb % kGemmStages;
                 const uint32_t ph = (kb / kGemmStages) & 1;
@@ -379,6 +386,9 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_stage_kernel(const __grid_c
 #endif
         // ------------------------------------------------------------ epilogue
         if (ok) ok = mbar_wait(bar_accum, 0, abort_flag, P.status);
+        // the output buffer may still be read by the kernel before the previous one (its input): the accumulator
+        // is complete only after warp 0 passed its wait, but each thread has to order its own stores
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         const int mh = (warp - 3) >> 2;              // which 128-token accumulator this warp drains
         if (ok && mh < MH) {
             tc_fence_after();
@@ -470,10 +480,25 @@ static int launch_stage(const void* a, long long lda, const void* tiles, const v
     memset(&P, 0, sizeof(P));
     const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)T};
     const cuuint64_t strides[1] = {(cuuint64_t)lda * 2};
-    // tile shape: 256 tokens when there are that many; 256 weight rows when the grid still fills the GPU
-    const int mh = T > kBM ? 2 : 1;
+    // Tile shape (128*mh tokens x 128*nh weight rows) by a small cost model.  Per 64-column step a CTA spends
+    // 256*mh*nh cycles in the tensor pipe and moves 32 KB*(mh+nh) through shared memory (operand reads, TMA
+    // and expansion writes) at 128 B/cycle, i.e. 256*(mh+nh) cycles; the grid runs in ceil(tiles/SMs) waves,
+    // each with a fixed prologue/epilogue cost.
+    int mh = 1, nh = 1;
+    {
+        static const int cand[3][2] = {{1, 1}, {2, 1}, {2, 2}};
+        const long long sms = sm_count(), steps = (K + kBK - 1) / kBK;
+        long long best = -1;
+        for (const auto& c : cand) {
+            if (c[0] == 2 && T <= kBM) continue;
+            const long long tiles = (long long)((T + kBM * c[0] - 1) / (kBM * c[0])) * ((Nout + 128 * c[1] - 1) / (128 * c[1]));
+            const long long waves = (tiles + sms - 1) / sms;
+            const long long per_step = 256LL * (c[0] * c[1] > c[0] + c[1] ? c[0] * c[1] : c[0] + c[1]);
+            const long long cost = waves * (steps * per_step + 6000 + 2000LL * c[0] * c[1]);
+            if (best < 0 || cost < best) { best = cost; mh = c[0]; nh = c[1]; }
+        }
+    }
     const int m_tiles = (T + kBM * mh - 1) / (kBM * mh);
-    const int nh = (mh == 2 && ((Nout + 255) / 256) * m_tiles >= (sm_count() * 3) / 4) ? 2 : 1;
     const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)(kBM * mh)};
     const cuuint32_t estr[2] = {1, 1};
     const CUresult r = enc(&P.map_a, dtype == NQ_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
@@ -504,11 +529,35 @@ static int launch_stage(const void* a, long long lda, const void* tiles, const v
                                          GemmCfg<2, 2>::kSmemBytes));
         attr_set[dev & 63] = true;
     }
-    const dim3 grid((Nout + 128 * nh - 1) / (128 * nh), m_tiles);
-    if (mh == 1) gemm_stage_kernel<1, 1><<<grid, kGemmThreads, GemmCfg<1, 1>::kSmemBytes, stream>>>(P);
-    else if (nh == 1) gemm_stage_kernel<2, 1><<<grid, kGemmThreads, GemmCfg<2, 1>::kSmemBytes, stream>>>(P);
-    else gemm_stage_kernel<2, 2><<<grid, kGemmThreads, GemmCfg<2, 2>::kSmemBytes, stream>>>(P);
-    NQ_LAUNCH_CHECK();
+    const void* fn;
+    size_t smem_bytes;
+    if (mh == 1) { fn = (const void*)gemm_stage_kernel<1, 1>; smem_bytes = GemmCfg<1, 1>::kSmemBytes; }
+    else if (nh == 1) { fn = (const void*)gemm_stage_kernel<2, 1>; smem_bytes = GemmCfg<2, 1>::kSmemBytes; }
+    else { fn = (const void*)gemm_stage_kernel<2, 2>; smem_bytes = GemmCfg<2, 2>::kSmemBytes; }
+    // Programmatic stream serialization lets this grid start while the previous kernel of the stream drains
+    // (see the kernel's griddepcontrol instructions).  If the driver refuses the attribute once, plain
+    // launches are used from then on.
+    static bool pdl_ok = true;
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3((Nout + 128 * nh - 1) / (128 * nh), m_tiles);
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = pdl_ok ? 1 : 0;
+    void* args[] = {&P};
+    cudaError_t e = cudaLaunchKernelExC(&cfg, fn, args);
+    if (e != cudaSuccess && pdl_ok) {
+        (void)cudaGetLastError();
+        pdl_ok = false;
+        cfg.numAttrs = 0;
+        e = cudaLaunchKernelExC(&cfg, fn, args);
+    }
+    NQ_CUDA_TRY(e);
     return NQ_OK;
 }
 
