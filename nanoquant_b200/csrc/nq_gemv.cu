@@ -68,11 +68,12 @@ enum : int { KIND_F16 = 0, KIND_BF16 = 1, KIND_F32 = 2 };
 __device__ unsigned long long g_trace[148 * 64];
 __device__ int g_trace_n[148];
 __device__ __forceinline__ void trace_mark(int id) {
+    __shared__ int s_n;          // record count of this CTA (thread 0 only); no memory round trip per mark
     if (threadIdx.x == 0) {
         unsigned long long t;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        const int n = g_trace_n[blockIdx.x];
-        if (n < 64) { g_trace[blockIdx.x * 64 + n] = (t << 8) | (unsigned)id; g_trace_n[blockIdx.x] = n + 1; }
+        const int n = id == 0 ? 0 : s_n;
+        if (n < 64) { g_trace[blockIdx.x * 64 + n] = (t << 8) | (unsigned)id; s_n = n + 1; g_trace_n[blockIdx.x] = n + 1; }
     }
 }
 #define NQ_TRACE(id) trace_mark(id)
@@ -105,7 +106,7 @@ struct Phase {
 
 struct GemvParams {
     Phase phase[2];
-    unsigned* header;     // [0] barrier count, [1] barrier generation, [2] status
+    unsigned* header;     // [0] barrier arrival counter, [1] unused, [2] status
     int T;
     int scale_kind;       // dtype of the scale vectors (KIND_F16 / KIND_BF16)
     int xq_stride;        // bytes between the int8 vectors in shared memory
@@ -125,38 +126,37 @@ __device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, ui
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// Bounded device-wide barrier on {count, generation} words.  Returns false when the
-// wait expired (a status word is set and the caller returns).  One thread per CTA
-// arrives with a release and polls with acquires; the CTA barrier before and after
-// extends the ordering to every thread of the CTA.  `my_gen` is the generation thread 0
-// read (barrier_generation) any time after the previous launch on these words completed
-// and before this arrival: it cannot change until every CTA has arrived, and reading it
-// early keeps one memory round trip off the critical path.  The count wraps to zero with
-// the last arrival (atom.inc), so the words need no reset between launches.
-__device__ __forceinline__ unsigned barrier_generation(const unsigned* header) {
-    unsigned g;
-    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(g) : "l"(header + 1) : "memory");
-    return g;
+// Bounded device-wide barrier on one arrival counter.  Returns false when the wait expired (a status
+// word is set and the caller returns).  Every launch advances the counter by exactly kBarrierSpan (a power
+// of two): CTA 0 adds kBarrierSpan - (nblocks - 1), every other CTA adds 1, so the bits above the span
+// count launches, they change at the moment the last CTA arrives, and 32-bit wrap-around is harmless.
+// Arrival is a release reduction without a return value and the waiters poll the counter itself: the last
+// arrival reaches them in one hop.  `base` is the launch count thread 0 read (barrier_base) after the
+// previous launch on this counter completed and before its own arrival; fewer than a span's worth of
+// arrivals can precede that read, so the upper bits are still those of the launch start.  Reading it
+// early keeps a memory round trip off the critical path.  One thread per CTA arrives and polls; the CTA
+// barrier before and after extends the ordering to every thread of the CTA.
+constexpr unsigned kBarrierSpan = 1u << 16;
+__device__ __forceinline__ unsigned barrier_base(const unsigned* header) {
+    unsigned c;
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(c) : "l"(header) : "memory");
+    return c & ~(kBarrierSpan - 1);
 }
-__device__ bool grid_barrier(unsigned* header, unsigned nblocks, unsigned my_gen) {
+__device__ bool grid_barrier(unsigned* header, unsigned nblocks, unsigned base) {
     __shared__ int ok;
     __syncthreads();
     if (threadIdx.x == 0) {
         ok = 1;
-        unsigned old;
-        asm volatile("atom.inc.acq_rel.gpu.global.u32 %0, [%1], %2;" : "=r"(old) : "l"(header), "r"(nblocks - 1) : "memory");
-        if (old == nblocks - 1) {
-            asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(header + 1) : "memory");
-        } else {
-            unsigned spins = 0, cur;
-            while (true) {
-                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(cur) : "l"(header + 1) : "memory");
-                if (cur != my_gen) break;
-                if (++spins > kSpinLimit) {
-                    atomicExch(header + 2, (unsigned)(-NQ_ERR_TIMEOUT));
-                    ok = 0;
-                    break;
-                }
+        const unsigned w = blockIdx.x == 0 ? kBarrierSpan - (nblocks - 1) : 1u;
+        asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(header), "r"(w) : "memory");
+        unsigned spins = 0, cur;
+        while (true) {
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(cur) : "l"(header) : "memory");
+            if ((cur & ~(kBarrierSpan - 1)) != base) break;
+            if (++spins > kSpinLimit) {
+                atomicExch(header + 2, (unsigned)(-NQ_ERR_TIMEOUT));
+                ok = 0;
+                break;
             }
         }
     }
@@ -180,6 +180,40 @@ __device__ __forceinline__ void load8(const void* base, long long i, float (&v)[
                 const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[e]));
                 v[2 * e] = f.x; v[2 * e + 1] = f.y;
             } else {  // bf16 -> fp32 is a 16-bit shift
+                v[2 * e] = __uint_as_float(w[e] << 16);
+                v[2 * e + 1] = __uint_as_float(w[e] & 0xFFFF0000u);
+            }
+        }
+    }
+}
+
+// The same split in two: the raw 128-bit loads of a block (so that several blocks can be in flight before
+// the first conversion) and the conversion.
+template <int KIND>
+struct Raw8 { uint4 a, b; };   // b: second half of an fp32 block
+template <int KIND>
+__device__ __forceinline__ void load_raw(const void* base, long long i, Raw8<KIND>& r) {
+    if (KIND == KIND_F32) {
+        const uint4* p = reinterpret_cast<const uint4*>(static_cast<const float*>(base) + i);
+        r.a = __ldcg(p);
+        r.b = __ldcg(p + 1);
+    } else {
+        r.a = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(base) + i);
+    }
+}
+template <int KIND>
+__device__ __forceinline__ void to_float8(const Raw8<KIND>& r, float (&v)[8]) {
+    if (KIND == KIND_F32) {
+        v[0] = __uint_as_float(r.a.x); v[1] = __uint_as_float(r.a.y); v[2] = __uint_as_float(r.a.z); v[3] = __uint_as_float(r.a.w);
+        v[4] = __uint_as_float(r.b.x); v[5] = __uint_as_float(r.b.y); v[6] = __uint_as_float(r.b.z); v[7] = __uint_as_float(r.b.w);
+    } else {
+        const uint32_t w[4] = {r.a.x, r.a.y, r.a.z, r.a.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            if (KIND == KIND_F16) {
+                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[e]));
+                v[2 * e] = f.x; v[2 * e + 1] = f.y;
+            } else {
                 v[2 * e] = __uint_as_float(w[e] << 16);
                 v[2 * e + 1] = __uint_as_float(w[e] & 0xFFFF0000u);
             }
@@ -215,8 +249,10 @@ __device__ __forceinline__ float token_max(const float* red, int t) {
 __device__ __forceinline__ float token_inv(const float* red, int t, bool writer, float* delta) {
     const float m = token_max(red, t);
     const bool good = (m > 0.f) && (m < 3.0e38f);
-    if (writer) delta[t] = good ? m / (float)kQMax : 0.f;
-    return good ? (float)kQMax / m : 0.f;
+    // A rounded reciprocal times kQMax instead of a division: every thread computes the same value,
+    // |p * inv| stays within kQMax (1 + 2^-22), and the unit differs from 1 / inv by a relative 2^-22 at most.
+    if (writer) delta[t] = good ? m * (1.0f / (float)kQMax) : 0.f;
+    return good ? (float)kQMax * __frcp_rn(m) : 0.f;
 }
 // Warp-wide maximum of non-negative floats / sum of ints with one reduction instruction each.
 __device__ __forceinline__ float warp_max_abs(float m) {
@@ -256,17 +292,33 @@ __device__ __noinline__ void quantise_vec(const Job& jb, int T, int8_t* xq, int 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int K = jb.K, Kpad = jb.chunks * 256;
     constexpr bool kHasPre = (IN_KIND != KIND_F32);
+    constexpr int kBatch = 4;                       // blocks whose loads are issued before the first use:
+    constexpr int kStep = kGemvThreads * 8;         // one memory round trip per batch instead of one per block
     // pass 1: per-token max |in * pre|
 #pragma unroll 1
     for (int t = 0; t < T; ++t) {
         float m = 0.f;
 #pragma unroll 1
-        for (int k8 = tid * 8; k8 < K; k8 += kGemvThreads * 8) {
-            float v[8], s[8];
-            load8<IN_KIND>(jb.in, t * jb.ld_in + k8, v);
-            if (kHasPre) load8<IN_KIND>(jb.pre, k8, s);
+        for (int k0 = tid * 8; k0 < K; k0 += kStep * kBatch) {
+            Raw8<IN_KIND> x[kBatch], sc[kBatch];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) m = fmaxf(m, fabsf(kHasPre ? v[e] * s[e] : v[e]));
+            for (int u = 0; u < kBatch; ++u) {
+                const int k8 = k0 + u * kStep;
+                x[u].a = x[u].b = make_uint4(0u, 0u, 0u, 0u);     // a zero block does not move the maximum
+                sc[u].a = sc[u].b = make_uint4(0u, 0u, 0u, 0u);
+                if (k8 < K) {
+                    load_raw<IN_KIND>(jb.in, t * jb.ld_in + k8, x[u]);
+                    if (kHasPre) load_raw<IN_KIND>(jb.pre, k8, sc[u]);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+                float v[8], s[8];
+                to_float8<IN_KIND>(x[u], v);
+                if (kHasPre) to_float8<IN_KIND>(sc[u], s);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) m = fmaxf(m, fabsf(kHasPre ? v[e] * s[e] : v[e]));
+            }
         }
         m = warp_max_abs(m);
         if (lane == 0) red[t * kGemvWarps + warp] = m;
@@ -280,24 +332,36 @@ __device__ __noinline__ void quantise_vec(const Job& jb, int T, int8_t* xq, int 
         int8_t* r0 = xq + (3 * t) * stride;
         int acc = 0;
 #pragma unroll 1
-        for (int k8 = tid * 8; k8 < Kpad; k8 += kGemvThreads * 8) {
-            const int j = (k8 >> 5) & 7;
-            uint32_t Y[8];  // class-shifted operands
-            if (k8 < K) {
-                float v[8], s[8];
-                load8<IN_KIND>(jb.in, t * jb.ld_in + k8, v);
-                if (kHasPre) load8<IN_KIND>(jb.pre, k8, s);
+        for (int k0 = tid * 8; k0 < Kpad; k0 += kStep * kBatch) {
+            Raw8<IN_KIND> x[kBatch], sc[kBatch];
 #pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    const int X = __float2int_rn((kHasPre ? v[e] * s[e] : v[e]) * inv);
-                    acc += X;
-                    Y[e] = (uint32_t)class_shift(X, j);
+            for (int u = 0; u < kBatch; ++u) {
+                const int k8 = k0 + u * kStep;
+                x[u].a = x[u].b = make_uint4(0u, 0u, 0u, 0u);     // columns K..Kpad quantise to zero
+                sc[u].a = sc[u].b = make_uint4(0u, 0u, 0u, 0u);
+                if (k8 < K) {
+                    load_raw<IN_KIND>(jb.in, t * jb.ld_in + k8, x[u]);
+                    if (kHasPre) load_raw<IN_KIND>(jb.pre, k8, sc[u]);
                 }
-            } else {
-#pragma unroll
-                for (int e = 0; e < 8; ++e) Y[e] = 0;
             }
-            store_terms(Y, r0, stride, k8);
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+                const int k8 = k0 + u * kStep;
+                if (k8 < Kpad) {
+                    const int j = (k8 >> 5) & 7;
+                    float v[8], s[8];
+                    to_float8<IN_KIND>(x[u], v);
+                    if (kHasPre) to_float8<IN_KIND>(sc[u], s);
+                    uint32_t Y[8];  // class-shifted operands
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        const int X = __float2int_rn((kHasPre ? v[e] * s[e] : v[e]) * inv);
+                        acc += X;
+                        Y[e] = (uint32_t)class_shift(X, j);
+                    }
+                    store_terms(Y, r0, stride, k8);
+                }
+            }
         }
         acc = __reduce_add_sync(0xffffffffu, acc);
         if (lane == 0 && acc != 0) atomicAdd(&sumx[t], acc);
@@ -335,7 +399,9 @@ __device__ __noinline__ void quantise_one(const Job& jb, int T, int8_t* xq, int 
     // per-warp maxima in the [token][warp] table: a warp contributes to its token only
     if (lane < kMaxTok) red[lane * kGemvWarps + warp] = (active && lane == t) ? m : 0.f;
     if (tid < kMaxTok) sumx[tid] = 0;
+    NQ_TRACE(2);
     __syncthreads();
+    NQ_TRACE(3);
     if (active) {
         const float inv = token_inv(red, t, k8 == 0, delta);
         const int j = (k8 >> 5) & 7;
@@ -351,6 +417,7 @@ __device__ __noinline__ void quantise_one(const Job& jb, int T, int8_t* xq, int 
         acc = __reduce_add_sync(0xffffffffu, acc);
         if (lane == 0 && acc != 0) atomicAdd(&sumx[t], acc);
     }
+    NQ_TRACE(4);
     __syncthreads();
 }
 
@@ -526,13 +593,13 @@ __device__ __forceinline__ bool run_all(const Phase* phases, const GemvParams& P
     // with the tail of the previous kernel in the stream; the activations and the scratch (shared with
     // that kernel) are only touched after it has completed.  No-ops without the launch attribute.
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const unsigned my_gen = tid == 0 ? barrier_generation(P.header) : 0u;
+    const unsigned bar_base = tid == 0 ? barrier_base(P.header) : 0u;
     NQ_TRACE(1);
 #pragma unroll 1
     while (true) {
         if (!barrier_done && s >= njobs) {    // everything of phase 1 is written: publish, then read t
             NQ_TRACE(8);
-            if (!grid_barrier(P.header, gridDim.x, my_gen)) return false;
+            if (!grid_barrier(P.header, gridDim.x, bar_base)) return false;
             barrier_done = true;
             // Every CTA of this grid is resident now, so CTAs of the next kernel that start early cannot
             // keep one of ours from being scheduled: let the next kernel begin its prologue.
