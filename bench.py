@@ -208,6 +208,9 @@ class Step:
                   "i": torch.randn(T, INTER, generator=g, device=device).to(dtype)}
         self.keep, self.launches, self.bytes = [], [], 0
         scratch_bytes = 0
+        # more tokens than one decode launch takes: every linear goes through nq_linear_fwd (split-K GEMM)
+        self.per_linear = T > self.L.nq_gemv_max_tokens()
+        self.singles = []
         for _ in range(layers):
             groups = {}
             for (name, N, R, M, src, grp) in layer_linears():
@@ -219,17 +222,28 @@ class Step:
                                     t["y"].data_ptr(), N, R, M, N, M)
                 groups.setdefault(grp, []).append(d)
                 self.bytes += algorithmic_bytes(N, R, M, T)
+                if self.per_linear:
+                    self.singles.append((self.x[src].data_ptr(), t, N, R, M))
+                    scratch_bytes = max(scratch_bytes, self.L.nq_linear_scratch_bytes(T, N, R, M))
             for grp in sorted(groups):
                 arr = (_lib.LinearDesc * len(groups[grp]))(*groups[grp])
                 scratch_bytes = max(scratch_bytes, self.L.nq_gemv_group_scratch_bytes(arr, len(arr), T))
                 self.launches.append(arr)
         self.last_y = self.keep[-1]["y"]
         self.scratch = torch.zeros(scratch_bytes, dtype=torch.uint8, device=device)
-        self.kernels_per_step = len(self.launches) * ((T + 3) // 4)
+        self.kernels_per_step = 2 * len(self.singles) if self.per_linear else len(self.launches)
+        self.kernel_name = "gemm_stage_kernel (split-K)" if self.per_linear else "gemv_group_kernel"
         self.graph = None
 
     def run(self):
         st = self.torch.cuda.current_stream(self.device).cuda_stream
+        if self.per_linear:
+            for (xp, t, N, R, M) in self.singles:
+                rc = self.L.nq_linear_fwd(xp, t["s_in"].data_ptr(), t["v"].data_ptr(), t["s_mid"].data_ptr(),
+                                          t["u"].data_ptr(), t["s_out"].data_ptr(), t["y"].data_ptr(),
+                                          self.scratch.data_ptr(), self.scratch.numel(), self.T, N, R, M, self.dt_id, st)
+                self.lib.check(rc, "nq_linear_fwd")
+            return
         for arr in self.launches:
             rc = self.L.nq_gemv_group_fwd(arr, len(arr), self.T, self.dt_id, self.scratch.data_ptr(),
                                           self.scratch.numel(), st)
@@ -346,11 +360,12 @@ def gpu_arm(args):
         "metric": "decode tok/s (quantised linears of one decode step)", "value": world * T / step_s,
         "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "s8 mma / s32 accumulate on 16-bit fixed point; bf16 in/out", "data": "synthetic",
+        "dtype": ("bf16 tcgen05 mma / f32 accumulate; bf16 in/out" if step.per_linear
+                  else "s8 mma / s32 accumulate on 16-bit fixed point; bf16 in/out"), "data": "synthetic",
         "config": dict(workload_config(T), layers_timed=args.layers,
                        parallelism=("single gpu" if world == 1 else f"{world} independent replicas")),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "kernel": "gemv_group_kernel",
+                     "traffic": None, "kernel": step.kernel_name,
                      "bytes_per_launch": step.bytes / step.kernels_per_step, "us_per_launch": launch_us,
                      "peak_source": peak_src},
         "e2e": {"value": world * T / (e2e_ms * 1e-3 / args.steps), "unit": "tokens/s",

@@ -41,8 +41,12 @@ namespace nq {
 
 constexpr int kBM = 128;            // tokens per MMA (MMA M, tensor-memory lanes)
 constexpr int kBK = 64;             // k per pipeline stage: 128 bytes of bf16 = one swizzle row
-constexpr int kGemmThreads = 352;   // warp 0 activation TMA, warp 1 MMA, warp 2 sign bits, warps 3..10 expand + epilogue
-constexpr int kExpandThreads = 256;
+#ifndef NQ_GEMM_EXPAND_WARPS
+#define NQ_GEMM_EXPAND_WARPS 8
+#endif
+constexpr int kExpandThreads = 32 * NQ_GEMM_EXPAND_WARPS;   // 256 or 512
+constexpr int kGemmThreads = 96 + kExpandThreads;   // warp 0 activation TMA, warp 1 MMA, warp 2 sign bits, then expand + epilogue
+static_assert(kExpandThreads == 256 || kExpandThreads == 512, "expand warps: 8 or 16");
 constexpr int kTileBytes = kBM * kBK * 2;          // 16 KB: one 128-row operand tile
 constexpr int kPreBytes = 256 * 2;                 // input scales of one 256-column chunk
 constexpr unsigned kWaitLimit = 1u << 21;   // attempts of up to ~2 us each
@@ -83,6 +87,12 @@ struct GemmParams {
     int chunks, row_groups;
     int is_bf16;
     int saturate;          // apply the reference's output saturation bounds
+    // split-K (few tokens, few output tiles): grid.z CTAs share an output tile, each over `chunks_per`
+    // 256-column chunks; partial sums go to fp32 slabs [split][Nout][t_pad] and the CTA that arrives last
+    // at the tile's counter adds them up in split order and writes the output.
+    int splits, chunks_per, t_pad;
+    float* slabs;
+    unsigned* counters;    // one per output tile, zero between launches
 };
 
 // ---------------------------------------------------------------------------
@@ -200,7 +210,11 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_stage_kernel(const __grid_c
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * kBN;   // first weight row of the tile
     const int m0 = blockIdx.y * (kBM * MH);   // first token of the tile
-    const int nkb = (P.K + kBK - 1) / kBK;
+    // k range of this CTA (all of K unless the launch is split): whole 256-column chunks
+    const int c_begin = (int)blockIdx.z * P.chunks_per;
+    const int c_end = min(P.chunks, c_begin + P.chunks_per);
+    const int kb_begin = 4 * c_begin;
+    const int nkb = min((P.K + kBK - 1) / kBK, 4 * c_end) - kb_begin;   // k blocks of this CTA
 
     auto bar_full = [&](int s) { return sbase + kOffBar + 8 * s; };
     auto bar_wready = [&](int s) { return sbase + kOffBar + 8 * (kGemmStages + s); };
@@ -265,7 +279,7 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_stage_kernel(const __grid_c
                 const uint32_t ph = (kb / kGemmStages) & 1;
                 if (!mbar_wait(bar_empty(s), ph ^ 1, abort_flag, P.status)) break;
                 mbar_expect_tx(bar_full(s), (uint32_t)(MH * kTileBytes));
-                tma_load_2d(sbase + kOffA + s * (C::kABytes), &P.map_a, kb * kBK, m0, bar_full(s));
+                tma_load_2d(sbase + kOffA + s * (C::kABytes), &P.map_a, (kb_begin + kb) * kBK, m0, bar_full(s));
             }
         }
     } else if (warp == 2) {
@@ -273,9 +287,9 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_stage_kernel(const __grid_c
         // chunk per step, running ahead of the expand warps by the two chunk slots
         if (lane == 0) {
             const int nchunks = (nkb + 3) >> 2;
-            for (int c = 0; c < nchunks; ++c) {
-                const int b = c & 1;
-                if (!mbar_wait(bar_bits_empty(b), ((c >> 1) & 1) ^ 1, abort_flag, P.status)) break;
+            for (int cl = 0; cl < nchunks; ++cl) {
+                const int b = cl & 1, c = c_begin + cl;
+                if (!mbar_wait(bar_bits_empty(b), ((cl >> 1) & 1) ^ 1, abort_flag, P.status)) break;
                 int pre_bytes = 0;
                 if (P.pre) {
                     const int left = P.K - c * 256;
@@ -344,30 +358,39 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_stage_kernel(const __grid_c
             const uint4* bits = reinterpret_cast<const uint4*>(smem + kOffBits + b * kBitsSlotBytes);
             const uint2* pre2 = reinterpret_cast<const uint2*>(smem + kOffPre + b * kPreBytes + sub * (kBK * 2));
             unsigned char* wt = smem + kOffW + s * C::kWBytes;
-            // all shared-memory reads of the k block first, then the stores
-            uint4 w4[NH];
+            // Work items of a k block: (128-bit word of sign bits, class jj of its two 32-column classes),
+            // NH * 512 in all.  A thread always works on the same word index: with 512 expand threads and
+            // NH = 1 two threads share a word (one class each), otherwise a thread does both classes of
+            // NH * 256 / kExpandThreads words.  All shared-memory reads of the k block first, then the stores.
+            constexpr int kWords = NH * 256;                                   // words per k block
+            constexpr int kSplitJ = (kExpandThreads > kWords) ? 1 : 0;         // two threads per word
+            constexpr int kPerThread = kSplitJ ? 1 : kWords / kExpandThreads;  // words per thread
+            uint4 w4[kPerThread];
 #pragma unroll
-            for (int it = 0; it < NH; ++it) w4[it] = bits[tu + it * kExpandThreads];
+            for (int it = 0; it < kPerThread; ++it) w4[it] = bits[(tu & (kWords - 1)) + it * kExpandThreads];
             const int l = tu & 31, g = l >> 2, q = l & 3;   // lane of the GEMV tile (same for every task)
+            const int jj0 = kSplitJ ? (tu / kWords) : 0;    // first (or only) class of this thread
             uint2 pp[4];                                      // input scales of columns 32*jj + 16*h + 4q .. +3
 #pragma unroll
-            for (int c4 = 0; c4 < 4; ++c4) {
-                if (P.pre) pp[c4] = pre2[(32 * (c4 >> 1) + 16 * (c4 & 1) + 4 * q) >> 2];
+            for (int c4 = 0; c4 < (kSplitJ ? 2 : 4); ++c4) {
+                const int jj = jj0 + (c4 >> 1);
+                if (P.pre) pp[c4] = pre2[(32 * jj + 16 * (c4 & 1) + 4 * q) >> 2];
                 else pp[c4] = make_uint2(one2, one2);
             }
 #pragma unroll
-            for (int it = 0; it < NH; ++it) {
-                const int rg = (tu + it * kExpandThreads) >> 5;   // row group of the task
+            for (int it = 0; it < kPerThread; ++it) {
+                const int rg = ((tu & (kWords - 1)) + it * kExpandThreads) >> 5;   // row group of the task
                 const uint32_t comp[4] = {w4[it].x, w4[it].y, w4[it].z, w4[it].w};   // {row g h0, row g+8 h0, row g h1, row g+8 h1}
 #pragma unroll
-                for (int jj = 0; jj < 2; ++jj) {
+                for (int ji = 0; ji < (kSplitJ ? 1 : 2); ++ji) {
+                    const int jj = jj0 + ji;
                     const int j = 2 * sub + jj;                      // class of the 32 columns
 #pragma unroll
                     for (int ci = 0; ci < 4; ++ci) {
                         const int h = ci >> 1, row = 16 * rg + g + 8 * (ci & 1);
                         const uint32_t u = (comp[ci] << (7 - j)) & 0x80808080u;   // bit 8b+j -> sign of byte b
-                        const uint32_t v0 = __byte_perm(u, 0u, 0x1404) ^ pp[2 * jj + h].x;   // columns 4q, 4q+1
-                        const uint32_t v1 = __byte_perm(u, 0u, 0x3424) ^ pp[2 * jj + h].y;   // columns 4q+2, 4q+3
+                        const uint32_t v0 = __byte_perm(u, 0u, 0x1404) ^ pp[2 * ji + h].x;   // columns 4q, 4q+1
+                        const uint32_t v1 = __byte_perm(u, 0u, 0x3424) ^ pp[2 * ji + h].y;   // columns 4q+2, 4q+3
                         const int c16 = (32 * jj + 16 * h + 4 * q) >> 3;          // 16-byte chunk of the 128-byte row
                         *reinterpret_cast<uint2*>(wt + row * 128 + ((c16 ^ (row & 7)) << 4) + 8 * (q & 1)) =
                             make_uint2(v0, v1);
@@ -389,18 +412,27 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_stage_kernel(const __grid_c
         // the output buffer may still be read by the kernel before the previous one (its input): the accumulator
         // is complete only after warp 0 passed its wait, but each thread has to order its own stores
         asm volatile("griddepcontrol.wait;" ::: "memory");
-        const int mh = (warp - 3) >> 2;              // which 128-token accumulator this warp drains
-        if (ok && mh < MH) {
+        // 32-column blocks of the MH accumulators, dealt round-robin to the warps that share a lane quarter
+        if (ok) {
             tc_fence_after();
             const int lq = warp & 3;                 // tensor-memory lane quarter this warp may read
-            const int row = m0 + kBM * mh + 32 * lq + lane;     // token
+            const int sub_w = (warp - 3) >> 2;       // index among the warps of that quarter
             const float lim = P.saturate ? (P.is_bf16 ? 3.3895313892515355e+38f : 64504.0f) : 3.4e38f;
             const float4* post4 = reinterpret_cast<const float4*>(smem + kOffPost);
 #pragma unroll 1
-            for (int c0 = 0; c0 < kBN; c0 += 32) {
+            for (int blk = sub_w; blk < MH * (kBN / 32); blk += kExpandThreads / 128) {
+                const int mh = blk / (kBN / 32), c0 = (blk % (kBN / 32)) * 32;
+                const int row = m0 + kBM * mh + 32 * lq + lane;     // token
                 uint32_t r[32];
                 tmem_ld32(tmem_base + ((uint32_t)(32 * lq) << 16) + (uint32_t)(mh * kBN + c0), r);
                 if (row >= P.T || n0 + c0 >= P.Nout) continue;
+                if (P.splits > 1) {   // partial sums of this k range: a warp writes 32 consecutive tokens per column
+                    float* slab = P.slabs + ((size_t)blockIdx.z * P.Nout + n0 + c0) * P.t_pad + row;
+#pragma unroll
+                    for (int e = 0; e < 32; ++e)
+                        if (n0 + c0 + e < P.Nout) slab[(size_t)e * P.t_pad] = __uint_as_float(r[e]);
+                    continue;
+                }
                 uint32_t packed[16];
 #pragma unroll
                 for (int e4 = 0; e4 < 8; ++e4) {
@@ -430,6 +462,82 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_stage_kernel(const __grid_c
                     for (int e = 0; e < 32; ++e)
                         if (n0 + c0 + e < P.Nout)
                             reinterpret_cast<uint16_t*>(dst)[e] = (uint16_t)(packed[e >> 1] >> (16 * (e & 1)));
+                }
+            }
+        }
+    }
+    if (P.splits > 1 && warp >= 3) {
+        // Split-K tail.  Every expand thread passes both barriers whatever happened before, so an expired wait
+        // elsewhere cannot leave threads behind.  The CTA that finds the other splits' arrivals at the tile's
+        // counter adds the slabs up in split order (the result does not depend on arrival order).
+        volatile int* last_flag = reinterpret_cast<volatile int*>(smem + kOffMisc + 8);
+        const int tu = threadIdx.x - 96;
+        __threadfence();
+        asm volatile("bar.sync 1, %0;" ::"n"(kExpandThreads) : "memory");
+        if (tu == 0) {
+            int last = 0;
+            if (!*abort_flag) {
+                const unsigned old = atomicAdd(P.counters + blockIdx.x, 1u);
+                last = old == (unsigned)(P.splits - 1);
+                if (last) P.counters[blockIdx.x] = 0u;   // ready for the next launch
+            }
+            *last_flag = last;
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(kExpandThreads) : "memory");
+        if (*last_flag) {
+            __threadfence();
+            const int tp4 = P.t_pad >> 2;
+            const int ncols = min(kBN, P.Nout - n0);
+            const float lim = P.saturate ? (P.is_bf16 ? 3.3895313892515355e+38f : 64504.0f) : 3.4e38f;
+            const float* post_s = reinterpret_cast<const float*>(smem + kOffPost);
+            // Items: (column, group of four tokens).  Two items and eight splits per round keep 16 independent
+            // 16-byte loads in flight per thread; the sums are formed in split order.
+            constexpr int kZ = 8;
+            const int nitems = ncols * tp4;
+            for (int it0 = tu; it0 < nitems; it0 += 2 * kExpandThreads) {
+                float4 acc[2];
+                const float* src[2];
+#pragma unroll
+                for (int w = 0; w < 2; ++w) {
+                    const int it = min(it0 + w * kExpandThreads, nitems - 1);   // clamped: a duplicate is not stored
+                    const int col = it / tp4, r4 = it - col * tp4;
+                    src[w] = P.slabs + ((size_t)n0 + col) * P.t_pad + 4 * r4;
+                    acc[w] = make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+                const size_t zstride = (size_t)P.Nout * P.t_pad;
+                for (int z0 = 0; z0 < P.splits; z0 += kZ) {
+                    float4 v[2][kZ];
+#pragma unroll
+                    for (int u = 0; u < kZ; ++u)
+#pragma unroll
+                        for (int w = 0; w < 2; ++w)
+                            v[w][u] = z0 + u < P.splits
+                                          ? __ldcg(reinterpret_cast<const float4*>(src[w] + (size_t)(z0 + u) * zstride))
+                                          : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int u = 0; u < kZ; ++u)
+#pragma unroll
+                        for (int w = 0; w < 2; ++w) {
+                            acc[w].x += v[w][u].x; acc[w].y += v[w][u].y; acc[w].z += v[w][u].z; acc[w].w += v[w][u].w;
+                        }
+                }
+#pragma unroll
+                for (int w = 0; w < 2; ++w) {
+                    const int it = it0 + w * kExpandThreads;
+                    if (it >= nitems) continue;
+                    const int col = it / tp4, r4 = it - col * tp4;
+                    const float sc = post_s[col];
+                    const float o[4] = {acc[w].x, acc[w].y, acc[w].z, acc[w].w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int row = 4 * r4 + j;
+                        if (row < P.T) {
+                            const float v1 = fminf(fmaxf(o[j] * sc, -lim), lim);
+                            const size_t at = (size_t)row * P.ld_out + n0 + col;
+                            if (P.is_bf16) static_cast<__nv_bfloat16*>(P.out)[at] = __float2bfloat16(v1);
+                            else static_cast<__half*>(P.out)[at] = __float2half(v1);
+                        }
+                    }
                 }
             }
         }
@@ -468,10 +576,66 @@ static EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-// One stage: out[T, Nout] = (a[T, K] . W^T) * post, W from `tiles` and `pre`.
+// Tile shape and k split of one stage.
+struct StagePlan {
+    int mh, nh;            // tile: 128*mh tokens x 128*nh weight rows
+    int splits;            // CTAs per output tile along K (1 = no split)
+    int chunks_per;        // 256-column chunks per split
+    int t_pad;             // slab row length (tokens, multiple of 4)
+    int tiles_n;           // output tiles along Nout
+};
+constexpr size_t kMaxSlabBytes = (size_t)16 << 20;
+// The tile counters live in words 8..63 of the 256-byte scratch header, which no other kernel writes
+// (the decode kernel that may share the scratch uses words 0..2 and the bytes behind the header).
+constexpr int kCounterWord0 = 8, kMaxSplitTiles = 56;
+constexpr int kMaxSplitTokens = 64;   // beyond that the serial slab reduction of the last CTA costs more than the split saves
+
+// Tile shape (128*mh tokens x 128*nh weight rows) by a small cost model.  Per 64-column step a CTA spends
+// 256*mh*nh cycles in the tensor pipe and moves 32 KB*(mh+nh) through shared memory (operand reads, TMA
+// and expansion writes) at 128 B/cycle, i.e. 256*(mh+nh) cycles; the grid runs in ceil(tiles/SMs) waves,
+// each with a fixed prologue/epilogue cost.  With at most 128 tokens and few output tiles the k dimension
+// is split over the idle SMs (whole 256-column chunks per CTA), as far as the slab budget allows.
+static StagePlan plan_stage(int T, int K, int Nout, bool allow_split) {
+    StagePlan pl;
+    pl.mh = 1; pl.nh = 1;
+    static const int cand[3][2] = {{1, 1}, {2, 1}, {2, 2}};
+    const long long sms = sm_count(), steps = (K + kBK - 1) / kBK;
+    long long best = -1;
+    for (const auto& c : cand) {
+        if (c[0] == 2 && T <= kBM) continue;
+        const long long tiles = (long long)((T + kBM * c[0] - 1) / (kBM * c[0])) * ((Nout + 128 * c[1] - 1) / (128 * c[1]));
+        const long long waves = (tiles + sms - 1) / sms;
+        const long long per_step = 256LL * (c[0] * c[1] > c[0] + c[1] ? c[0] * c[1] : c[0] + c[1]);
+        const long long cost = waves * (steps * per_step + 6000 + 2000LL * c[0] * c[1]);
+        if (best < 0 || cost < best) { best = cost; pl.mh = c[0]; pl.nh = c[1]; }
+    }
+    pl.tiles_n = (Nout + 128 * pl.nh - 1) / (128 * pl.nh);
+    pl.splits = 1;
+    pl.chunks_per = (K + 255) / 256;
+    pl.t_pad = (T + 3) / 4 * 4;
+    if (allow_split && T <= kMaxSplitTokens && pl.tiles_n <= kMaxSplitTiles) {
+        const int chunks = (K + 255) / 256;
+        long long want = sms / pl.tiles_n;
+        const long long by_mem = (long long)(kMaxSlabBytes / ((size_t)pl.t_pad * (size_t)Nout * sizeof(float)));
+        want = want < by_mem ? want : by_mem;
+        want = want < chunks ? want : chunks;
+        if (want >= 2) {
+            pl.chunks_per = (int)((chunks + want - 1) / want);
+            pl.splits = (chunks + pl.chunks_per - 1) / pl.chunks_per;
+        }
+    }
+    return pl;
+}
+// Slab bytes behind the intermediate in the GEMM scratch.
+static size_t slab_bytes(const StagePlan& pl, int Nout) {
+    return pl.splits > 1 ? (size_t)pl.splits * (size_t)Nout * (size_t)pl.t_pad * sizeof(float) : 0;
+}
+
+// One stage: out[T, Nout] = (a[T, K] . W^T) * post, W from `tiles` and `pre`.  `counters` (zero between
+// launches) and `slabs` may be nullptr: no k split.
 static int launch_stage(const void* a, long long lda, const void* tiles, const void* pre, const void* post,
                         void* out, long long ld_out, int T, int K, int Nout, int dtype, int saturate,
-                        unsigned* status, cudaStream_t stream) {
+                        unsigned* status, unsigned* counters, float* slabs, cudaStream_t stream) {
     if (!aligned16(a) || (lda % 8) != 0 || (K % 8) != 0) return NQ_ERR_ALIGN;   // TMA: 16-byte base and stride
     if (pre && !aligned16(pre)) return NQ_ERR_ALIGN;
     EncodeTiledFn enc = encode_tiled_fn();
@@ -480,24 +644,8 @@ static int launch_stage(const void* a, long long lda, const void* tiles, const v
     memset(&P, 0, sizeof(P));
     const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)T};
     const cuuint64_t strides[1] = {(cuuint64_t)lda * 2};
-    // Tile shape (128*mh tokens x 128*nh weight rows) by a small cost model.  Per 64-column step a CTA spends
-    // 256*mh*nh cycles in the tensor pipe and moves 32 KB*(mh+nh) through shared memory (operand reads, TMA
-    // and expansion writes) at 128 B/cycle, i.e. 256*(mh+nh) cycles; the grid runs in ceil(tiles/SMs) waves,
-    // each with a fixed prologue/epilogue cost.
-    int mh = 1, nh = 1;
-    {
-        static const int cand[3][2] = {{1, 1}, {2, 1}, {2, 2}};
-        const long long sms = sm_count(), steps = (K + kBK - 1) / kBK;
-        long long best = -1;
-        for (const auto& c : cand) {
-            if (c[0] == 2 && T <= kBM) continue;
-            const long long tiles = (long long)((T + kBM * c[0] - 1) / (kBM * c[0])) * ((Nout + 128 * c[1] - 1) / (128 * c[1]));
-            const long long waves = (tiles + sms - 1) / sms;
-            const long long per_step = 256LL * (c[0] * c[1] > c[0] + c[1] ? c[0] * c[1] : c[0] + c[1]);
-            const long long cost = waves * (steps * per_step + 6000 + 2000LL * c[0] * c[1]);
-            if (best < 0 || cost < best) { best = cost; mh = c[0]; nh = c[1]; }
-        }
-    }
+    const StagePlan pl = plan_stage(T, K, Nout, counters != nullptr && slabs != nullptr);
+    const int mh = pl.mh, nh = pl.nh;
     const int m_tiles = (T + kBM * mh - 1) / (kBM * mh);
     const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)(kBM * mh)};
     const cuuint32_t estr[2] = {1, 1};
@@ -517,6 +665,11 @@ static int launch_stage(const void* a, long long lda, const void* tiles, const v
     P.row_groups = (Nout + 15) / 16;
     P.is_bf16 = dtype == NQ_BF16;
     P.saturate = saturate;
+    P.splits = pl.splits;
+    P.chunks_per = pl.chunks_per;
+    P.t_pad = pl.t_pad;
+    P.counters = counters;
+    P.slabs = slabs;
     static bool attr_set[64];
     int dev = 0;
     NQ_CUDA_TRY(cudaGetDevice(&dev));
@@ -540,7 +693,7 @@ static int launch_stage(const void* a, long long lda, const void* tiles, const v
     static bool pdl_ok = true;
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
-    cfg.gridDim = dim3((Nout + 128 * nh - 1) / (128 * nh), m_tiles);
+    cfg.gridDim = dim3((Nout + 128 * nh - 1) / (128 * nh), m_tiles, pl.splits);
     cfg.blockDim = dim3(kGemmThreads);
     cfg.dynamicSmemBytes = smem_bytes;
     cfg.stream = stream;
@@ -569,7 +722,9 @@ extern "C" {
 
 size_t nq_gemm_scratch_bytes(int T, int N, int R, int M) {
     if (T <= 0 || N <= 0 || R <= 0 || M <= 0) return 0;
-    return 256 + ((size_t)T * (size_t)R * 2 + 255) / 256 * 256;
+    // header (status word, tile counters), intermediate t[T, R] (I/O dtype), split-K slabs (shared by the two stages)
+    const size_t a = slab_bytes(plan_stage(T, N, R, true), R), b = slab_bytes(plan_stage(T, R, M, true), M);
+    return 256 + ((size_t)T * (size_t)R * 2 + 255) / 256 * 256 + (a > b ? a : b);
 }
 
 int nq_onebit_gemm_fwd(const void* x, const void* tiles, const void* s_in, const void* s_out, void* y,
@@ -579,7 +734,7 @@ int nq_onebit_gemm_fwd(const void* x, const void* tiles, const void* s_in, const
     if (dtype != NQ_F16 && dtype != NQ_BF16) return NQ_ERR_DTYPE;
     if (!aligned16(tiles)) return NQ_ERR_ALIGN;
     return launch_stage(x, K, tiles, s_in, s_out, y, Nout, T, K, Nout, dtype, 1,
-                        static_cast<unsigned*>(status_word) + 2, as_stream(stream));
+                        static_cast<unsigned*>(status_word) + 2, nullptr, nullptr, as_stream(stream));
 }
 
 int nq_gemm_fwd(const void* x, const void* s_in, const void* v_tiles, const void* s_mid, const void* u_tiles,
@@ -593,9 +748,13 @@ int nq_gemm_fwd(const void* x, const void* s_in, const void* v_tiles, const void
     if (scratch_bytes < nq_gemm_scratch_bytes(T, N, R, M)) return NQ_ERR_SCRATCH;
     unsigned* status = static_cast<unsigned*>(scratch) + 2;   // same word as the GEMV header's status
     void* t = static_cast<char*>(scratch) + 256;
-    int st = launch_stage(x, N, v_tiles, s_in, s_mid, t, R, T, N, R, dtype, 0, status, as_stream(stream));
+    // Both stages use the same counters and slab space: a stage touches them only after the kernel before it
+    // has completed (its stores come behind the dependency wait).
+    unsigned* counters = static_cast<unsigned*>(scratch) + kCounterWord0;
+    float* slabs = reinterpret_cast<float*>(static_cast<char*>(t) + ((size_t)T * (size_t)R * 2 + 255) / 256 * 256);
+    int st = launch_stage(x, N, v_tiles, s_in, s_mid, t, R, T, N, R, dtype, 0, status, counters, slabs, as_stream(stream));
     if (st != NQ_OK) return st;
-    return launch_stage(t, R, u_tiles, nullptr, s_out, y, M, T, R, M, dtype, 1, status, as_stream(stream));
+    return launch_stage(t, R, u_tiles, nullptr, s_out, y, M, T, R, M, dtype, 1, status, counters, slabs, as_stream(stream));
 }
 
 #ifdef NQ_GEMM_TRACE
@@ -606,7 +765,8 @@ int nq_debug_read_gemm_trace(long long* host_out) {
 }
 #endif
 
-int nq_gemv_max_tokens(void) { return 8; }
+// One decode launch handles four tokens; from five tokens on the split-K GEMM is faster than two launches.
+int nq_gemv_max_tokens(void) { return 4; }
 
 size_t nq_linear_scratch_bytes(int T, int N, int R, int M) {
     const size_t a = nq_gemv_scratch_bytes(T, N, R, M), b = nq_gemm_scratch_bytes(T, N, R, M);

@@ -35,6 +35,9 @@ SHAPES = [
     (12288, 2432, 4096, 77),
     (4096, 2944, 11008, 256),   # a shape the reference's Marlin kernel rejects (11008 % 512 != 0)
     (2048, 992, 2048, 2048),
+    (4096, 1600, 4096, 16),     # few tokens, few output tiles: the k dimension is split over the idle SMs
+    (1024, 288, 576, 33),       # split with a ragged token count and a partial last output tile
+    (12288, 2432, 4096, 9),
 ]
 
 
