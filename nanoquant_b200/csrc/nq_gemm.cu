@@ -45,6 +45,8 @@ constexpr int kBK = 64;             // k per pipeline stage: 128 bytes of bf16 =
 #define NQ_GEMM_EXPAND_WARPS 8
 #endif
 constexpr int kExpandThreads = 32 * NQ_GEMM_EXPAND_WARPS;   // 256 or 512
+constexpr int kGroupThreads = 256;                          // expand threads that share one k block
+constexpr int kGroups = kExpandThreads / kGroupThreads;     // groups take alternate k blocks
 constexpr int kGemmThreads = 96 + kExpandThreads;   // warp 0 activation TMA, warp 1 MMA, warp 2 sign bits, then expand + epilogue
 static_assert(kExpandThreads == 256 || kExpandThreads == 512, "expand warps: 8 or 16");
 constexpr int kTileBytes = kBM * kBK * 2;          // 16 KB: one 128-row operand tile
@@ -62,12 +64,15 @@ struct GemmCfg {
     static constexpr int kABytes = MH * kTileBytes;
     static constexpr int kWBytes = NH * kTileBytes;
     static constexpr int kBitsSlotBytes = (kBN / 16) * 512; // row groups x one 256-column chunk of sign bits
+    // chunks of sign bits in flight (a power of two): they come from HBM, and with the small tiles, whose
+    // k blocks are short, two slots cover less than the memory latency
+    static constexpr int kBitsSlots = (MH * NH == 4) ? 2 : 4;
     static constexpr int kOffA = 0;
     static constexpr int kOffW = kOffA + kStages * kABytes;
     static constexpr int kOffBits = kOffW + kStages * kWBytes;
-    static constexpr int kOffPre = kOffBits + 2 * kBitsSlotBytes;   // input scales of a chunk, beside its bits
-    static constexpr int kOffBar = kOffPre + 2 * kPreBytes;
-    static constexpr int kNumBars = 4 * kStages + 2 + 2 + 1;  // full, wready, empty, wfree, bits_full, bits_empty, accum
+    static constexpr int kOffPre = kOffBits + kBitsSlots * kBitsSlotBytes;   // input scales of a chunk, beside its bits
+    static constexpr int kOffBar = kOffPre + kBitsSlots * kPreBytes;
+    static constexpr int kNumBars = 4 * kStages + 2 * kBitsSlots + 1;  // full, wready, empty, wfree, bits_full, bits_empty, accum
     static constexpr int kOffMisc = kOffBar + kNumBars * 8;   // tmem base address, abort flag
     static constexpr int kOffPost = (kOffMisc + 16 + 15) & ~15;   // output scales of the tile as fp32 (read as float4)
     static_assert(kOffPost % 16 == 0 && kOffBar % 8 == 0 && kOffBits % 16 == 0 && kOffPre % 16 == 0, "shared memory map alignment");
@@ -127,6 +132,7 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
 // thread of the CTA already gave up; the caller then leaves its loop.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           unsigned* status) {
+    if (mbar_try(bar, parity)) return true;   // the common case: already complete
     for (unsigned i = 0; i < kWaitLimit; ++i) {
         if (mbar_try(bar, parity)) return true;
         if (*abort_flag) return false;
@@ -201,6 +207,7 @@ template <int MH, int NH>
 __global__ void __launch_bounds__(kGemmThreads) gemm_stage_kernel(const __grid_constant__ GemmParams P) {
     using C = GemmCfg<MH, NH>;
     constexpr int kGemmStages = C::kStages, kBN = C::kBN, kBitsSlotBytes = C::kBitsSlotBytes;
+    constexpr int kBitsSlots = C::kBitsSlots, kSlotShift = (kBitsSlots == 4) ? 2 : 1;
     constexpr int kOffA = C::kOffA, kOffW = C::kOffW, kOffBits = C::kOffBits, kOffPre = C::kOffPre;
     constexpr int kOffBar = C::kOffBar, kOffMisc = C::kOffMisc, kOffPost = C::kOffPost;
     extern __shared__ unsigned char smem_raw[];
@@ -221,8 +228,8 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_stage_kernel(const __grid_c
     auto bar_empty = [&](int s) { return sbase + kOffBar + 8 * (2 * kGemmStages + s); };
     auto bar_wfree = [&](int s) { return sbase + kOffBar + 8 * (3 * kGemmStages + s); };
     auto bar_bits_full = [&](int b) { return sbase + kOffBar + 8 * (4 * kGemmStages + b); };
-    auto bar_bits_empty = [&](int b) { return sbase + kOffBar + 8 * (4 * kGemmStages + 2 + b); };
-    const uint32_t bar_accum = sbase + kOffBar + 8 * (4 * kGemmStages + 4);
+    auto bar_bits_empty = [&](int b) { return sbase + kOffBar + 8 * (4 * kGemmStages + kBitsSlots + b); };
+    const uint32_t bar_accum = sbase + kOffBar + 8 * (4 * kGemmStages + 2 * kBitsSlots);
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + kOffMisc);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kOffMisc + 4);
 
@@ -235,11 +242,11 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_stage_kernel(const __grid_c
     if (threadIdx.x == 0) {
         for (int s = 0; s < kGemmStages; ++s) {
             mbar_init(bar_full(s), 1);
-            mbar_init(bar_wready(s), kExpandThreads);
+            mbar_init(bar_wready(s), kGroupThreads);
             mbar_init(bar_empty(s), 1);
             mbar_init(bar_wfree(s), 1);
         }
-        for (int b = 0; b < 2; ++b) {
+        for (int b = 0; b < kBitsSlots; ++b) {
             mbar_init(bar_bits_full(b), 1);
             mbar_init(bar_bits_empty(b), kExpandThreads);
         }
@@ -248,7 +255,7 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_stage_kernel(const __grid_c
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     // input-scale slots start finite: a partial last k block leaves older (finite) values behind
-    for (int i = threadIdx.x; i < 2 * kPreBytes / 4; i += kGemmThreads)
+    for (int i = threadIdx.x; i < kBitsSlots * kPreBytes / 4; i += kGemmThreads)
         reinterpret_cast<uint32_t*>(smem + kOffPre)[i] = 0;
     for (int i = threadIdx.x; i < kBN; i += kGemmThreads) {   // output scales of this tile, once, as fp32
         float f = 1.f;
@@ -288,8 +295,8 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_stage_kernel(const __grid_c
         if (lane == 0) {
             const int nchunks = (nkb + 3) >> 2;
             for (int cl = 0; cl < nchunks; ++cl) {
-                const int b = cl & 1, c = c_begin + cl;
-                if (!mbar_wait(bar_bits_empty(b), ((cl >> 1) & 1) ^ 1, abort_flag, P.status)) break;
+                const int b = cl & (kBitsSlots - 1), c = c_begin + cl;
+                if (!mbar_wait(bar_bits_empty(b), ((cl >> kSlotShift) & 1) ^ 1, abort_flag, P.status)) break;
                 int pre_bytes = 0;
                 if (P.pre) {
                     const int left = P.K - c * 256;
@@ -316,41 +323,49 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_stage_kernel(const __grid_c
                 const int s = kb % kGemmStages;
                 const uint32_t ph = (kb / kGemmStages) & 1;
                 const long long t0 = GT_NOW();
-                ok = mbar_wait(bar_wready(s), ph, abort_flag, P.status) &&
-                     mbar_wait(bar_full(s), ph, abort_flag, P.status);
+                ok = mbar_wait(bar_wready(s), ph, abort_flag, P.status);
+                const long long tm = GT_NOW();
+                ok = ok && mbar_wait(bar_full(s), ph, abort_flag, P.status);
                 if (!ok) break;
                 const long long t1 = GT_NOW();
-                GT_ADD(0, t1 - t0);
+                if (kb >= kGemmStages) { GT_ADD(0, tm - t0); GT_ADD(2, t1 - tm); GT_ADD(3, 1); }
                 tc_fence_after();
-                const uint32_t a_addr = sbase + kOffA + s * (C::kABytes);
-                const uint32_t w_addr = sbase + kOffW + s * C::kWBytes;
+                // descriptors of the stage; inside the 128-byte swizzle row the k offset (32 bytes per MMA) is
+                // added to the start-address field (units of 16 bytes)
+                const uint64_t a_desc = umma_desc(sbase + kOffA + s * (C::kABytes));
+                const uint64_t w_desc = umma_desc(sbase + kOffW + s * C::kWBytes);
 #pragma unroll
                 for (int mh = 0; mh < MH; ++mh)
 #pragma unroll
                     for (int k4 = 0; k4 < kBK / 16; ++k4)
-                        umma_f16(tmem_base + (uint32_t)(mh * kBN), umma_desc(a_addr + mh * kTileBytes + k4 * 32),
-                                 umma_desc(w_addr + k4 * 32), idesc, (kb | k4) != 0 ? 1u : 0u);
+                        umma_f16(tmem_base + (uint32_t)(mh * kBN), a_desc + (uint64_t)((mh * kTileBytes + k4 * 32) >> 4),
+                                 w_desc + (uint64_t)((k4 * 32) >> 4), idesc, (kb | k4) != 0 ? 1u : 0u);
                 umma_commit(bar_empty(s));   // the stage's buffers are free once these MMAs have read them:
                 umma_commit(bar_wfree(s));   // the activation tile for the producer, the weight tile for the expanders
-                GT_ADD(1, GT_NOW() - t1);
+                if (kb >= kGemmStages) GT_ADD(1, GT_NOW() - t1);
             }
 #ifdef NQ_GEMM_TRACE
-            if (blockIdx.x == 0 && blockIdx.y == 0) { g_gemm_trace[4] = gt[0]; g_gemm_trace[5] = gt[1]; }
+            if (blockIdx.x == 0 && blockIdx.y == 0) { g_gemm_trace[4] = gt[0]; g_gemm_trace[5] = gt[1]; g_gemm_trace[6] = gt[2]; g_gemm_trace[7] = gt[3]; }
 #endif
             if (ok) umma_commit(bar_accum);
         }
     } else {
         // ------------------------------------------------------------ expand warps
-        const int tu = threadIdx.x - 96;   // 0..255
+        // The expansion of one k block is a chain of dependent steps (wait, shared-memory reads, a few ALU
+        // operations, stores, proxy fence, arrive) whose latency, not its instruction count, bounds a
+        // group's rate; with 16 expand warps two groups of eight work on alternate k blocks.
+        const int tu = threadIdx.x - 96;
+        const int grp = tu / kGroupThreads, tl = tu % kGroupThreads;
         const uint32_t one2 = P.is_bf16 ? 0x3F803F80u : 0x3C003C00u;
         bool ok = true;
         long long gt[4] = {0, 0, 0, 0};
-        for (int kb = 0; kb < nkb && ok; ++kb) {
+        int c_seen = -1;
+        for (int kb = grp; kb < nkb && ok; kb += kGroups) {
             const int s = kb % kGemmStages;
             const uint32_t ph = (kb / kGemmStages) & 1;
-            const int c = kb >> 2, b = c & 1, sub = kb & 3;
+            const int c = kb >> 2, b = c & (kBitsSlots - 1), sub = kb & 3;
             const long long t0 = GT_NOW();
-            if (sub == 0) ok = mbar_wait(bar_bits_full(b), (c >> 1) & 1, abort_flag, P.status);
+            if (c != c_seen) { ok = mbar_wait(bar_bits_full(b), (c >> kSlotShift) & 1, abort_flag, P.status); c_seen = c; }
             ok = ok && mbar_wait(bar_wfree(s), ph ^ 1, abort_flag, P.status);   // not on the activation tile
             if (!ok) break;
             const long long t1 = GT_NOW();
@@ -358,39 +373,30 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_stage_kernel(const __grid_c
             const uint4* bits = reinterpret_cast<const uint4*>(smem + kOffBits + b * kBitsSlotBytes);
             const uint2* pre2 = reinterpret_cast<const uint2*>(smem + kOffPre + b * kPreBytes + sub * (kBK * 2));
             unsigned char* wt = smem + kOffW + s * C::kWBytes;
-            // Work items of a k block: (128-bit word of sign bits, class jj of its two 32-column classes),
-            // NH * 512 in all.  A thread always works on the same word index: with 512 expand threads and
-            // NH = 1 two threads share a word (one class each), otherwise a thread does both classes of
-            // NH * 256 / kExpandThreads words.  All shared-memory reads of the k block first, then the stores.
-            constexpr int kWords = NH * 256;                                   // words per k block
-            constexpr int kSplitJ = (kExpandThreads > kWords) ? 1 : 0;         // two threads per word
-            constexpr int kPerThread = kSplitJ ? 1 : kWords / kExpandThreads;  // words per thread
-            uint4 w4[kPerThread];
+            // all shared-memory reads of the k block first, then the stores
+            uint4 w4[NH];
 #pragma unroll
-            for (int it = 0; it < kPerThread; ++it) w4[it] = bits[(tu & (kWords - 1)) + it * kExpandThreads];
-            const int l = tu & 31, g = l >> 2, q = l & 3;   // lane of the GEMV tile (same for every task)
-            const int jj0 = kSplitJ ? (tu / kWords) : 0;    // first (or only) class of this thread
+            for (int it = 0; it < NH; ++it) w4[it] = bits[tl + it * kGroupThreads];
+            const int l = tl & 31, g = l >> 2, q = l & 3;   // lane of the GEMV tile (same for every task)
             uint2 pp[4];                                      // input scales of columns 32*jj + 16*h + 4q .. +3
 #pragma unroll
-            for (int c4 = 0; c4 < (kSplitJ ? 2 : 4); ++c4) {
-                const int jj = jj0 + (c4 >> 1);
-                if (P.pre) pp[c4] = pre2[(32 * jj + 16 * (c4 & 1) + 4 * q) >> 2];
+            for (int c4 = 0; c4 < 4; ++c4) {
+                if (P.pre) pp[c4] = pre2[(32 * (c4 >> 1) + 16 * (c4 & 1) + 4 * q) >> 2];
                 else pp[c4] = make_uint2(one2, one2);
             }
 #pragma unroll
-            for (int it = 0; it < kPerThread; ++it) {
-                const int rg = ((tu & (kWords - 1)) + it * kExpandThreads) >> 5;   // row group of the task
+            for (int it = 0; it < NH; ++it) {
+                const int rg = (tl + it * kGroupThreads) >> 5;   // row group of the task
                 const uint32_t comp[4] = {w4[it].x, w4[it].y, w4[it].z, w4[it].w};   // {row g h0, row g+8 h0, row g h1, row g+8 h1}
 #pragma unroll
-                for (int ji = 0; ji < (kSplitJ ? 1 : 2); ++ji) {
-                    const int jj = jj0 + ji;
+                for (int jj = 0; jj < 2; ++jj) {
                     const int j = 2 * sub + jj;                      // class of the 32 columns
 #pragma unroll
                     for (int ci = 0; ci < 4; ++ci) {
                         const int h = ci >> 1, row = 16 * rg + g + 8 * (ci & 1);
                         const uint32_t u = (comp[ci] << (7 - j)) & 0x80808080u;   // bit 8b+j -> sign of byte b
-                        const uint32_t v0 = __byte_perm(u, 0u, 0x1404) ^ pp[2 * ji + h].x;   // columns 4q, 4q+1
-                        const uint32_t v1 = __byte_perm(u, 0u, 0x3424) ^ pp[2 * ji + h].y;   // columns 4q+2, 4q+3
+                        const uint32_t v0 = __byte_perm(u, 0u, 0x1404) ^ pp[2 * jj + h].x;   // columns 4q, 4q+1
+                        const uint32_t v1 = __byte_perm(u, 0u, 0x3424) ^ pp[2 * jj + h].y;   // columns 4q+2, 4q+3
                         const int c16 = (32 * jj + 16 * h + 4 * q) >> 3;          // 16-byte chunk of the 128-byte row
                         *reinterpret_cast<uint2*>(wt + row * 128 + ((c16 ^ (row & 7)) << 4) + 8 * (q & 1)) =
                             make_uint2(v0, v1);
@@ -401,7 +407,9 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_stage_kernel(const __grid_c
             GT_ADD(1, t2 - t1);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the MMA
             mbar_arrive(bar_wready(s));
-            if (sub == 3 || kb + 1 == nkb) mbar_arrive(bar_bits_empty(b));
+            // this group's last k block of the chunk: release the chunk's bits (both groups arrive, except
+            // that a group without a block in a partial last chunk has nothing to release or to wait for)
+            if (((kb + kGroups) >> 2) != c || kb + kGroups >= nkb) mbar_arrive(bar_bits_empty(b));
             GT_ADD(2, GT_NOW() - t2);
         }
 #ifdef NQ_GEMM_TRACE
