@@ -33,6 +33,7 @@
 // of the reference.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <cstring>
 
 #include "nq_common.cuh"
@@ -66,13 +67,13 @@ struct GemmCfg {
     static constexpr int kBitsSlotBytes = (kBN / 16) * 512; // row groups x one 256-column chunk of sign bits
     // chunks of sign bits in flight (a power of two): they come from HBM, and with the small tiles, whose
     // k blocks are short, two slots cover less than the memory latency
-    static constexpr int kBitsSlots = (MH * NH == 4) ? 2 : 4;
+    static constexpr int kBitsSlots = (NH == 2) ? 2 : 4;
     static constexpr int kOffA = 0;
     static constexpr int kOffW = kOffA + kStages * kABytes;
     static constexpr int kOffBits = kOffW + kStages * kWBytes;
     static constexpr int kOffPre = kOffBits + kBitsSlots * kBitsSlotBytes;   // input scales of a chunk, beside its bits
     static constexpr int kOffBar = kOffPre + kBitsSlots * kPreBytes;
-    static constexpr int kNumBars = 4 * kStages + 2 * kBitsSlots + 1;  // full, wready, empty, wfree, bits_full, bits_empty, accum
+    static constexpr int kNumBars = 2 * kStages + 2 * kBitsSlots + 1;  // ready, free, bits_full, bits_empty, accum
     static constexpr int kOffMisc = kOffBar + kNumBars * 8;   // tmem base address, abort flag
     static constexpr int kOffPost = (kOffMisc + 16 + 15) & ~15;   // output scales of the tile as fp32 (read as float4)
     static_assert(kOffPost % 16 == 0 && kOffBar % 8 == 0 && kOffBits % 16 == 0 && kOffPre % 16 == 0, "shared memory map alignment");
@@ -223,13 +224,15 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_stage_kernel(const __grid_c
     const int kb_begin = 4 * c_begin;
     const int nkb = min((P.K + kBK - 1) / kBK, 4 * c_end) - kb_begin;   // k blocks of this CTA
 
-    auto bar_full = [&](int s) { return sbase + kOffBar + 8 * s; };
-    auto bar_wready = [&](int s) { return sbase + kOffBar + 8 * (kGemmStages + s); };
-    auto bar_empty = [&](int s) { return sbase + kOffBar + 8 * (2 * kGemmStages + s); };
-    auto bar_wfree = [&](int s) { return sbase + kOffBar + 8 * (3 * kGemmStages + s); };
-    auto bar_bits_full = [&](int b) { return sbase + kOffBar + 8 * (4 * kGemmStages + b); };
-    auto bar_bits_empty = [&](int b) { return sbase + kOffBar + 8 * (4 * kGemmStages + kBitsSlots + b); };
-    const uint32_t bar_accum = sbase + kOffBar + 8 * (4 * kGemmStages + 2 * kBitsSlots);
+    // One barrier per stage and direction: "ready" completes when the activation tile has landed (the
+    // producer's expect-tx arrival plus the TMA's bytes) AND the expand group has arrived for the weight
+    // tile, so the MMA thread waits once per k block; "free" is committed once by the MMA thread and both
+    // the producer and the expanders wait on it.
+    auto bar_ready = [&](int s) { return sbase + kOffBar + 8 * s; };
+    auto bar_free = [&](int s) { return sbase + kOffBar + 8 * (kGemmStages + s); };
+    auto bar_bits_full = [&](int b) { return sbase + kOffBar + 8 * (2 * kGemmStages + b); };
+    auto bar_bits_empty = [&](int b) { return sbase + kOffBar + 8 * (2 * kGemmStages + kBitsSlots + b); };
+    const uint32_t bar_accum = sbase + kOffBar + 8 * (2 * kGemmStages + 2 * kBitsSlots);
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + kOffMisc);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kOffMisc + 4);
 
@@ -241,10 +244,8 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_stage_kernel(const __grid_c
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (threadIdx.x == 0) {
         for (int s = 0; s < kGemmStages; ++s) {
-            mbar_init(bar_full(s), 1);
-            mbar_init(bar_wready(s), kGroupThreads);
-            mbar_init(bar_empty(s), 1);
-            mbar_init(bar_wfree(s), 1);
+            mbar_init(bar_ready(s), 1 + kGroupThreads);
+            mbar_init(bar_free(s), 1);
         }
         for (int b = 0; b < kBitsSlots; ++b) {
             mbar_init(bar_bits_full(b), 1);
@@ -284,9 +285,9 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_stage_kernel(const __grid_c
             for (int kb = 0; kb < nkb; ++kb) {
                 const int s = kb % kGemmStages;
                 const uint32_t ph = (kb / kGemmStages) & 1;
-                if (!mbar_wait(bar_empty(s), ph ^ 1, abort_flag, P.status)) break;
-                mbar_expect_tx(bar_full(s), (uint32_t)(MH * kTileBytes));
-                tma_load_2d(sbase + kOffA + s * (C::kABytes), &P.map_a, (kb_begin + kb) * kBK, m0, bar_full(s));
+                if (!mbar_wait(bar_free(s), ph ^ 1, abort_flag, P.status)) break;
+                mbar_expect_tx(bar_ready(s), (uint32_t)(MH * kTileBytes));
+                tma_load_2d(sbase + kOffA + s * (C::kABytes), &P.map_a, (kb_begin + kb) * kBK, m0, bar_ready(s));
             }
         }
     } else if (warp == 2) {
@@ -323,9 +324,8 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_stage_kernel(const __grid_c
                 const int s = kb % kGemmStages;
                 const uint32_t ph = (kb / kGemmStages) & 1;
                 const long long t0 = GT_NOW();
-                ok = mbar_wait(bar_wready(s), ph, abort_flag, P.status);
+                ok = mbar_wait(bar_ready(s), ph, abort_flag, P.status);
                 const long long tm = GT_NOW();
-                ok = ok && mbar_wait(bar_full(s), ph, abort_flag, P.status);
                 if (!ok) break;
                 const long long t1 = GT_NOW();
                 if (kb >= kGemmStages) { GT_ADD(0, tm - t0); GT_ADD(2, t1 - tm); GT_ADD(3, 1); }
@@ -340,8 +340,7 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_stage_kernel(const __grid_c
                     for (int k4 = 0; k4 < kBK / 16; ++k4)
                         umma_f16(tmem_base + (uint32_t)(mh * kBN), a_desc + (uint64_t)((mh * kTileBytes + k4 * 32) >> 4),
                                  w_desc + (uint64_t)((k4 * 32) >> 4), idesc, (kb | k4) != 0 ? 1u : 0u);
-                umma_commit(bar_empty(s));   // the stage's buffers are free once these MMAs have read them:
-                umma_commit(bar_wfree(s));   // the activation tile for the producer, the weight tile for the expanders
+                umma_commit(bar_free(s));   // the stage's buffers are free once these MMAs have read them
                 if (kb >= kGemmStages) GT_ADD(1, GT_NOW() - t1);
             }
 #ifdef NQ_GEMM_TRACE
@@ -366,7 +365,7 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_stage_kernel(const __grid_c
             const int c = kb >> 2, b = c & (kBitsSlots - 1), sub = kb & 3;
             const long long t0 = GT_NOW();
             if (c != c_seen) { ok = mbar_wait(bar_bits_full(b), (c >> kSlotShift) & 1, abort_flag, P.status); c_seen = c; }
-            ok = ok && mbar_wait(bar_wfree(s), ph ^ 1, abort_flag, P.status);   // not on the activation tile
+            ok = ok && mbar_wait(bar_free(s), ph ^ 1, abort_flag, P.status);
             if (!ok) break;
             const long long t1 = GT_NOW();
             GT_ADD(0, t1 - t0);
@@ -406,7 +405,7 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_stage_kernel(const __grid_c
             const long long t2 = GT_NOW();
             GT_ADD(1, t2 - t1);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the MMA
-            mbar_arrive(bar_wready(s));
+            mbar_arrive(bar_ready(s));
             // this group's last k block of the chunk: release the chunk's bits (both groups arrive, except
             // that a group without a block in a partial last chunk has nothing to release or to wait for)
             if (((kb + kGroups) >> 2) != c || kb + kGroups >= nkb) mbar_arrive(bar_bits_empty(b));
@@ -598,22 +597,26 @@ constexpr size_t kMaxSlabBytes = (size_t)16 << 20;
 constexpr int kCounterWord0 = 8, kMaxSplitTiles = 56;
 constexpr int kMaxSplitTokens = 64;   // beyond that the serial slab reduction of the last CTA costs more than the split saves
 
-// Tile shape (128*mh tokens x 128*nh weight rows) by a small cost model.  Per 64-column step a CTA spends
-// 256*mh*nh cycles in the tensor pipe and moves 32 KB*(mh+nh) through shared memory (operand reads, TMA
-// and expansion writes) at 128 B/cycle, i.e. 256*(mh+nh) cycles; the grid runs in ceil(tiles/SMs) waves,
-// each with a fixed prologue/epilogue cost.  With at most 128 tokens and few output tiles the k dimension
-// is split over the idle SMs (whole 256-column chunks per CTA), as far as the slab budget allows.
+// Tile shape (128*mh tokens x 128*nh weight rows) by a small cost model: a CTA needs a measured number of
+// cycles per 64-column step (bounded by the tensor pipe for the 256 x 256 tile, by the per-step waits and
+// MMA issue of the single issuing thread for the smaller ones); the grid runs in ceil(tiles/SMs) waves, each
+// with a fixed prologue/epilogue cost.  With at most 64 tokens and few output tiles the k dimension is
+// split over the idle SMs (whole 256-column chunks per CTA), as far as the slab budget allows.
 static StagePlan plan_stage(int T, int K, int Nout, bool allow_split) {
     StagePlan pl;
     pl.mh = 1; pl.nh = 1;
-    static const int cand[3][2] = {{1, 1}, {2, 1}, {2, 2}};
+    static const int cand[4][2] = {{1, 1}, {2, 1}, {1, 2}, {2, 2}};
+    // development aid: NQ_GEMM_FORCE_CFG=<mh><nh> (e.g. 12) pins the tile shape
+    static const int forced = [] { const char* e = getenv("NQ_GEMM_FORCE_CFG"); return e ? atoi(e) : 0; }();
     const long long sms = sm_count(), steps = (K + kBK - 1) / kBK;
     long long best = -1;
     for (const auto& c : cand) {
-        if (c[0] == 2 && T <= kBM) continue;
+        if (forced && forced != 10 * c[0] + c[1]) continue;
+        if (c[0] == 2 && T <= kBM && !forced) continue;
         const long long tiles = (long long)((T + kBM * c[0] - 1) / (kBM * c[0])) * ((Nout + 128 * c[1] - 1) / (128 * c[1]));
         const long long waves = (tiles + sms - 1) / sms;
-        const long long per_step = 256LL * (c[0] * c[1] > c[0] + c[1] ? c[0] * c[1] : c[0] + c[1]);
+        // measured cycles of the MMA thread per 64-column step (wait + issue, tensor pipe busy)
+        const long long per_step = c[0] * c[1] == 4 ? 970 : (c[0] == 2 ? 740 : (c[1] == 2 ? 830 : 510));
         const long long cost = waves * (steps * per_step + 6000 + 2000LL * c[0] * c[1]);
         if (best < 0 || cost < best) { best = cost; pl.mh = c[0]; pl.nh = c[1]; }
     }
@@ -686,13 +689,16 @@ static int launch_stage(const void* a, long long lda, const void* tiles, const v
                                          GemmCfg<1, 1>::kSmemBytes));
         NQ_CUDA_TRY(cudaFuncSetAttribute(gemm_stage_kernel<2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          GemmCfg<2, 1>::kSmemBytes));
+        NQ_CUDA_TRY(cudaFuncSetAttribute(gemm_stage_kernel<1, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         GemmCfg<1, 2>::kSmemBytes));
         NQ_CUDA_TRY(cudaFuncSetAttribute(gemm_stage_kernel<2, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          GemmCfg<2, 2>::kSmemBytes));
         attr_set[dev & 63] = true;
     }
     const void* fn;
     size_t smem_bytes;
-    if (mh == 1) { fn = (const void*)gemm_stage_kernel<1, 1>; smem_bytes = GemmCfg<1, 1>::kSmemBytes; }
+    if (mh == 1 && nh == 1) { fn = (const void*)gemm_stage_kernel<1, 1>; smem_bytes = GemmCfg<1, 1>::kSmemBytes; }
+    else if (mh == 1) { fn = (const void*)gemm_stage_kernel<1, 2>; smem_bytes = GemmCfg<1, 2>::kSmemBytes; }
     else if (nh == 1) { fn = (const void*)gemm_stage_kernel<2, 1>; smem_bytes = GemmCfg<2, 1>::kSmemBytes; }
     else { fn = (const void*)gemm_stage_kernel<2, 2>; smem_bytes = GemmCfg<2, 2>::kSmemBytes; }
     // Programmatic stream serialization lets this grid start while the previous kernel of the stream drains
