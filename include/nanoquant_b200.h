@@ -193,8 +193,9 @@ int nq_scratch_status(const void* scratch, nq_stream_t stream);
  * ------------------------------------------------------------------------ */
 
 /* Bytes of scratch nq_gemm_fwd needs: a 256-byte header (status word at byte 8,
- * the same place as in the GEMV scratch) followed by the rank-R intermediate
- * t[T, R] in the I/O dtype. */
+ * the same place as in the GEMV scratch; tile counters of the split-K path in
+ * bytes 32..255) followed by the rank-R intermediate t[T, R] in the I/O dtype
+ * and, for up to 64 tokens, the fp32 partial sums of the k splits. */
 size_t nq_gemm_scratch_bytes(int T, int N, int R, int M);
 
 /* y[T, M] = s_out * (U . (s_mid * (V . (s_in * x[T, N])))) as two tensor-core
@@ -202,8 +203,11 @@ size_t nq_gemm_scratch_bytes(int T, int N, int R, int M);
  * intermediate is rounded to the I/O dtype between the stages, accumulation is
  * fp32, the products x * (+-s_in) are exact.  Requires N % 8 == 0, R % 8 == 0,
  * 16-byte aligned x, y, scales and scratch.  The scratch header must be zeroed
- * once by the caller; a device-side wait that gives up sets its status word
- * (nq_scratch_status).
+ * once by the caller (the tile counters return to zero by themselves); a
+ * device-side wait that gives up sets its status word (nq_scratch_status).
+ * Consecutive launches overlap through programmatic dependent launch: a
+ * kernel loads activations and stores results only after the previous kernel
+ * of the stream has completed.
  * replaces: marlin_nanoquant_cuda, src/nanoquant/kernel/cuda/gemm.cpp:112-122
  * (schema src/nanoquant/kernel/pybind.cpp:99-104) */
 int nq_gemm_fwd(const void* x, const void* s_in, const void* v_tiles, const void* s_mid,
