@@ -265,6 +265,55 @@ class Step:
         return self.L.nq_scratch_status(self.scratch.data_ptr(), self.torch.cuda.current_stream(self.device).cuda_stream)
 
 
+def side_numbers(device, dtype):
+    """Short measurements of the workload's other operating points (decode batches 4 and 16, one prefill GEMM
+    size), reported beside the headline line; same kernels, same synthetic weights, CUDA events."""
+    import torch
+    out = {}
+    for T in (4, 16):
+        step = Step(T, dtype, device)
+        step.capture()
+        for _ in range(3):
+            step.graph.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize(device)
+        e0.record()
+        for _ in range(10):
+            step.graph.replay()
+        e1.record()
+        torch.cuda.synchronize(device)
+        if step.status() != 0:
+            raise SystemExit("bench.py: a device-side wait timed out")
+        ms = e0.elapsed_time(e1) / 10
+        out[f"decode_batch{T}"] = {"value": T / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms,
+                                   "kernel": step.kernel_name, "hbm_frac": step.bytes / (ms * 1e-3) / 1e9 / hbm_peak()[0]}
+        del step
+        torch.cuda.empty_cache()
+    tf, ms, _, _ = measure_prefill(2048, 4, 3, 3, device)
+    out["prefill_2048_tokens"] = {"value": tf, "unit": "TFLOP/s", "ms_per_step": ms,
+                                  "frac_of_sustained_bf16_peak": tf / tensor_peak()[0]}
+    return out
+
+
+def _peaks():
+    try:
+        return json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except (OSError, ValueError):
+        return {}
+
+
+def hbm_peak():
+    p = _peaks()
+    return (float(p.get("hbm_gbs", 6650.0)),
+            "measured (MEASURED_PEAKS.json hbm_gbs)" if "hbm_gbs" in p else "fallback 6650 GB/s")
+
+
+def tensor_peak():
+    p = _peaks()
+    return (float(p.get("bf16_tflops_sustained", 1400.0)),
+            "measured (MEASURED_PEAKS.json bf16_tflops_sustained)" if "bf16_tflops_sustained" in p else "fallback 1400")
+
+
 def gpu_arm(args):
     import torch
     import torch.distributed as dist
@@ -342,13 +391,7 @@ def gpu_arm(args):
             dist.destroy_process_group()
         return
 
-    peaks = {}
-    try:
-        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-    except (OSError, ValueError):
-        pass
-    peak = float(peaks.get("hbm_gbs", 6650.0))
-    peak_src = "measured (MEASURED_PEAKS.json hbm_gbs)" if "hbm_gbs" in peaks else "fallback 6650 GB/s"
+    peak, peak_src = hbm_peak()
     step_s = ms * 1e-3 / args.steps
     achieved = step.bytes / step_s / 1e9
     if args.layers != LAYERS:   # profiling aid: fewer layers resident; report per-step numbers of what ran
@@ -376,6 +419,10 @@ def gpu_arm(args):
     }
     if out_note:
         out["note"] = out_note
+    if world == 1 and T == 1 and args.layers == LAYERS and not args.no_side_numbers:
+        del step
+        torch.cuda.empty_cache()
+        out["other_operating_points"] = side_numbers(device, dtype)
     if not args.no_cpu_baseline:
         cpu = CpuLayer(T)
         t_layer, reps = cpu.timed(budget_s=12.0)
@@ -512,15 +559,14 @@ def tp_arm(args):
 # --------------------------------------------------------------------------------------------
 # prefill arm (--mode prefill): Llama-2-7B-shaped layer GEMMs at 1.0 bpw, T tokens per GEMM
 # --------------------------------------------------------------------------------------------
-def prefill_arm(args):
-    """TFLOP/s of the tcgen05 GEMM path (nq_gemm_fwd) on the 7 linears of Llama-2-7B-shaped layers
-    (hidden 4096, intermediate 11008, ranks from the rank formula at 1.0 bpw), `--tokens` tokens per GEMM."""
+def measure_prefill(T, layers, steps, warmup, device, profile=False, min_seconds=0.0):
+    """TFLOP/s of nq_gemm_fwd on the 7 linears of `layers` Llama-2-7B-shaped layers (hidden 4096, intermediate
+    11008, ranks from the rank formula at 1.0 bpw), T tokens per GEMM.  Returns (TFLOP/s, ms per step, launches
+    per step, clock record or None)."""
     import torch
     from nanoquant_b200 import _lib
     L = _lib.lib()
-    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
-    torch.cuda.set_device(device)
-    T, dtype = args.tokens, torch.bfloat16
+    dtype = torch.bfloat16
     H, I = 4096, 11008
     shapes = [(H, H)] * 4 + [(H, I), (H, I), (I, H)]
     g = torch.Generator(device=device).manual_seed(0)
@@ -529,7 +575,7 @@ def prefill_arm(args):
     scale = lambda n: ((torch.rand(n, generator=g, device=device) + 0.5) * 0.01).to(dtype)
     xs = {H: torch.randn(T, H, generator=g, device=device).to(dtype), I: torch.randn(T, I, generator=g, device=device).to(dtype)}
     calls, flops, scratch_bytes = [], 0.0, 0
-    for _ in range(args.layers if args.layers != LAYERS else 4):
+    for _ in range(layers):
         for (N, M) in shapes:
             R = rank_for_bits(N, M, 1.0)
             t = dict(v=rnd_bits(R, N), u=rnd_bits(M, R), a=scale(N), b=scale(R), c=scale(M),
@@ -545,47 +591,55 @@ def prefill_arm(args):
             _lib.check(L.nq_gemm_fwd(xs[N].data_ptr(), t["a"].data_ptr(), t["v"].data_ptr(), t["b"].data_ptr(),
                                      t["u"].data_ptr(), t["c"].data_ptr(), t["y"].data_ptr(), scratch.data_ptr(),
                                      scratch.numel(), T, N, R, M, _lib.NQ_BF16, st), "nq_gemm_fwd")
-    for _ in range(max(args.warmup, 3)):
+    for _ in range(max(warmup, 3)):
         run()
     torch.cuda.synchronize(device)
-    sampler = ClockSampler(device.index)
-    sampler.start()
-    time.sleep(0.3)
+    sampler = None
+    if min_seconds > 0:
+        sampler = ClockSampler(device.index)
+        sampler.start()
+        time.sleep(0.3)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.profiler.start()
+    if profile:
+        torch.cuda.profiler.start()
     e0.record()
-    for _ in range(args.steps):
+    for _ in range(steps):
         run()
     e1.record()
     torch.cuda.synchronize(device)
-    torch.cuda.profiler.stop()
-    ms = e0.elapsed_time(e1) / args.steps
-    t_end = time.perf_counter() + max(0.0, 1.0 - ms * args.steps * 1e-3)
-    while time.perf_counter() < t_end:
+    if profile:
+        torch.cuda.profiler.stop()
+    ms = e0.elapsed_time(e1) / steps
+    t_end = time.perf_counter() + max(0.0, min_seconds - ms * steps * 1e-3)
+    while time.perf_counter() < t_end:   # keeps the clock record meaningful for short runs
         run()
         torch.cuda.synchronize(device)
-    clocks = sampler.stop()
+    clocks = sampler.stop() if sampler else None
     if L.nq_scratch_status(scratch.data_ptr(), st) != 0:
         raise SystemExit("bench.py: a device-side wait timed out inside the GEMM kernel")
-    peaks = {}
-    try:
-        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-    except (OSError, ValueError):
-        pass
-    peak = float(peaks.get("bf16_tflops_sustained", 1400.0))
-    tf = flops / (ms * 1e-3) / 1e12
+    return flops / (ms * 1e-3) / 1e12, ms, 2 * len(calls), clocks
+
+
+def prefill_arm(args):
+    """`--mode prefill`: the tcgen05 GEMM path at `--tokens` tokens per GEMM."""
+    import torch
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(device)
+    T = args.tokens
+    layers = args.layers if args.layers != LAYERS else 4
+    tf, ms, launches, clocks = measure_prefill(T, layers, args.steps, args.warmup, device, profile=True, min_seconds=1.0)
+    peak, peak_src = tensor_peak()
     print(json.dumps({
         "mode": "prefill", "metric": "prefill TFLOP/s (quantised linears, 2*T*R*(N+M) flops)", "value": tf,
         "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 (fp32 accumulate)",
         "data": "synthetic",
-        "config": {"workload": f"llama-2-7b-shaped layer GEMMs at 1.0 bpw, {T} tokens per GEMM, {len(calls) // 7} layers",
+        "config": {"workload": f"llama-2-7b-shaped layer GEMMs at 1.0 bpw, {T} tokens per GEMM, {layers} layers",
                    "tokens": T},
         "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak,
-                     "traffic": None, "kernel": "gemm_stage_kernel",
-                     "peak_source": "measured (MEASURED_PEAKS.json bf16_tflops_sustained)" if peaks else "fallback 1400"},
-        "tokens_per_s": T * (len(calls) // 7) / (ms * 1e-3) / (len(calls) // 7),
-        "gpu_launches": 2 * len(calls) * args.steps, "clocks": clocks}), flush=True)
+                     "traffic": None, "kernel": "gemm_stage_kernel", "peak_source": peak_src},
+        "tokens_per_s": T / (ms * 1e-3),   # T tokens through the GEMMs of `layers` layers per step
+        "gpu_launches": launches * args.steps, "clocks": clocks}), flush=True)
 
 
 def main():
@@ -596,6 +650,8 @@ def main():
     ap.add_argument("--batch", type=int, default=1, help="tokens per decode step (1, 4 or 16 in the workload)")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-side-numbers", action="store_true",
+                    help="skip the short batch-4 / batch-16 / prefill measurements added to the default line")
     ap.add_argument("--mode", default="replica", choices=["replica", "tp", "prefill"],
                     help="replica: the decode step (N > 1: independent replicas); tp: 70B-shaped TP decode step; "
                          "prefill: GEMM TFLOP/s on Llama-2-7B-shaped layers")
