@@ -42,14 +42,8 @@ namespace nq {
 
 constexpr int kBM = 128;            // tokens per MMA (MMA M, tensor-memory lanes)
 constexpr int kBK = 64;             // k per pipeline stage: 128 bytes of bf16 = one swizzle row
-#ifndef NQ_GEMM_EXPAND_WARPS
-#define NQ_GEMM_EXPAND_WARPS 8
-#endif
-constexpr int kExpandThreads = 32 * NQ_GEMM_EXPAND_WARPS;   // 256 or 512
 constexpr int kGroupThreads = 256;                          // expand threads that share one k block
-constexpr int kGroups = kExpandThreads / kGroupThreads;     // groups take alternate k blocks
-constexpr int kGemmThreads = 96 + kExpandThreads;   // warp 0 activation TMA, warp 1 MMA, warp 2 sign bits, then expand + epilogue
-static_assert(kExpandThreads == 256 || kExpandThreads == 512, "expand warps: 8 or 16");
+constexpr int kFirstExpandWarp = 4;   // warp 0 activation TMA, warps 1 and 3 MMA, warp 2 sign bits, then expand + epilogue
 constexpr int kTileBytes = kBM * kBK * 2;          // 16 KB: one 128-row operand tile
 constexpr int kPreBytes = 256 * 2;                 // input scales of one 256-column chunk
 constexpr unsigned kWaitLimit = 1u << 21;   // attempts of up to ~2 us each
@@ -78,7 +72,17 @@ struct GemmCfg {
     static constexpr int kOffPost = (kOffMisc + 16 + 15) & ~15;   // output scales of the tile as fp32 (read as float4)
     static_assert(kOffPost % 16 == 0 && kOffBar % 8 == 0 && kOffBits % 16 == 0 && kOffPre % 16 == 0, "shared memory map alignment");
     static constexpr int kSmemBytes = kOffPost + kBN * 4 + 1024;   // + slack for the 1024-byte alignment
-    static constexpr int kTmemCols = MH * kBN;
+    // MMA-issuing threads.  The small tiles are bound by the issuing thread (waits and instruction issue cost
+    // more cycles than their MMAs take), so two threads take alternate k blocks, each into an accumulator of
+    // its own, and the epilogue adds the two.  The 256 x 256 tile is bound by the tensor pipe and fills the
+    // tensor memory with one accumulator set.
+    static constexpr int kIssuers = (MH * NH == 4) ? 1 : 2;
+    // Expand groups of 256 threads on alternate k blocks: the expansion of a k block is a chain of dependent
+    // steps, so the small tiles (short k blocks) need two groups to keep up with two issuers.
+    static constexpr int kGroups = (MH * NH == 4) ? 1 : 2;
+    static constexpr int kExpandThreads = kGroups * kGroupThreads;
+    static constexpr int kThreads = 32 * kFirstExpandWarp + kExpandThreads;
+    static constexpr int kTmemCols = kIssuers * MH * kBN;
 };
 
 struct GemmParams {
@@ -196,19 +200,23 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 __device__ long long g_gemm_trace[16];
 #define GT_NOW() clock64()
 #define GT_ADD(i, v) do { if (blockIdx.x == 0 && blockIdx.y == 0) gt[i] += (v); } while (0)
+#define GT_DECL() long long gt[4] = {0, 0, 0, 0}
+#define GT_T(name) const long long name = GT_NOW()
 #else
-#define GT_NOW() 0ll
 #define GT_ADD(i, v) ((void)0)
+#define GT_DECL() ((void)0)
+#define GT_T(name) ((void)0)
 #endif
 
 // ---------------------------------------------------------------------------
 // the kernel: one 128 x 128 output tile per CTA
 // ---------------------------------------------------------------------------
 template <int MH, int NH>
-__global__ void __launch_bounds__(kGemmThreads) gemm_stage_kernel(const __grid_constant__ GemmParams P) {
+__global__ void __launch_bounds__(GemmCfg<MH, NH>::kThreads) gemm_stage_kernel(const __grid_constant__ GemmParams P) {
     using C = GemmCfg<MH, NH>;
     constexpr int kGemmStages = C::kStages, kBN = C::kBN, kBitsSlotBytes = C::kBitsSlotBytes;
     constexpr int kBitsSlots = C::kBitsSlots, kSlotShift = (kBitsSlots == 4) ? 2 : 1;
+    constexpr int kExpandThreads = C::kExpandThreads, kGroups = C::kGroups, kGemmThreads = C::kThreads;
     constexpr int kOffA = C::kOffA, kOffW = C::kOffW, kOffBits = C::kOffBits, kOffPre = C::kOffPre;
     constexpr int kOffBar = C::kOffBar, kOffMisc = C::kOffMisc, kOffPost = C::kOffPost;
     extern __shared__ unsigned char smem_raw[];
@@ -251,7 +259,7 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_stage_kernel(const __grid_c
             mbar_init(bar_bits_full(b), 1);
             mbar_init(bar_bits_empty(b), kExpandThreads);
         }
-        mbar_init(bar_accum, 1);
+        mbar_init(bar_accum, C::kIssuers);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -312,22 +320,24 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_stage_kernel(const __grid_c
                               (uint32_t)pre_bytes, bar_bits_full(b));
             }
         }
-    } else if (warp == 1) {
-        // ------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
+    } else if (warp == 1 || warp == 3) {
+        // ------------------------------------------------------------ MMA issuers
+        const int mw = warp == 1 ? 0 : 1;
+        if (lane == 0 && mw < C::kIssuers) {
+            const uint32_t acc_base = tmem_base + (uint32_t)(mw * MH * kBN);
             const uint32_t fmt = P.is_bf16 ? 1u : 0u;
             const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(kBN >> 3) << 17) |
                                    ((uint32_t)(kBM >> 4) << 24);
             bool ok = true;
-            long long gt[4] = {0, 0, 0, 0};
-            for (int kb = 0; kb < nkb && ok; ++kb) {
+            GT_DECL();
+            for (int kb = mw; kb < nkb && ok; kb += C::kIssuers) {
                 const int s = kb % kGemmStages;
                 const uint32_t ph = (kb / kGemmStages) & 1;
-                const long long t0 = GT_NOW();
+                GT_T(t0);
                 ok = mbar_wait(bar_ready(s), ph, abort_flag, P.status);
-                const long long tm = GT_NOW();
+                GT_T(tm);
                 if (!ok) break;
-                const long long t1 = GT_NOW();
+                GT_T(t1);
                 if (kb >= kGemmStages) { GT_ADD(0, tm - t0); GT_ADD(2, t1 - tm); GT_ADD(3, 1); }
                 tc_fence_after();
                 // descriptors of the stage; inside the 128-byte swizzle row the k offset (32 bytes per MMA) is
@@ -338,36 +348,37 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_stage_kernel(const __grid_c
                 for (int mh = 0; mh < MH; ++mh)
 #pragma unroll
                     for (int k4 = 0; k4 < kBK / 16; ++k4)
-                        umma_f16(tmem_base + (uint32_t)(mh * kBN), a_desc + (uint64_t)((mh * kTileBytes + k4 * 32) >> 4),
-                                 w_desc + (uint64_t)((k4 * 32) >> 4), idesc, (kb | k4) != 0 ? 1u : 0u);
+                        umma_f16(acc_base + (uint32_t)(mh * kBN), a_desc + (uint64_t)((mh * kTileBytes + k4 * 32) >> 4),
+                                 w_desc + (uint64_t)((k4 * 32) >> 4), idesc, (kb != mw || k4 != 0) ? 1u : 0u);
                 umma_commit(bar_free(s));   // the stage's buffers are free once these MMAs have read them
                 if (kb >= kGemmStages) GT_ADD(1, GT_NOW() - t1);
             }
 #ifdef NQ_GEMM_TRACE
-            if (blockIdx.x == 0 && blockIdx.y == 0) { g_gemm_trace[4] = gt[0]; g_gemm_trace[5] = gt[1]; g_gemm_trace[6] = gt[2]; g_gemm_trace[7] = gt[3]; }
+            if (blockIdx.x == 0 && blockIdx.y == 0 && mw == 0) { g_gemm_trace[4] = gt[0]; g_gemm_trace[5] = gt[1]; g_gemm_trace[6] = gt[2]; g_gemm_trace[7] = gt[3]; }
 #endif
+            // arrives when this thread's MMAs are complete (at once if it had no k block)
             if (ok) umma_commit(bar_accum);
         }
     } else {
         // ------------------------------------------------------------ expand warps
         // The expansion of one k block is a chain of dependent steps (wait, shared-memory reads, a few ALU
         // operations, stores, proxy fence, arrive) whose latency, not its instruction count, bounds a
-        // group's rate; with 16 expand warps two groups of eight work on alternate k blocks.
-        const int tu = threadIdx.x - 96;
+        // group's rate; the small tiles run two groups of eight warps on alternate k blocks.
+        const int tu = threadIdx.x - 32 * kFirstExpandWarp;
         const int grp = tu / kGroupThreads, tl = tu % kGroupThreads;
         const uint32_t one2 = P.is_bf16 ? 0x3F803F80u : 0x3C003C00u;
         bool ok = true;
-        long long gt[4] = {0, 0, 0, 0};
+        GT_DECL();
         int c_seen = -1;
         for (int kb = grp; kb < nkb && ok; kb += kGroups) {
             const int s = kb % kGemmStages;
             const uint32_t ph = (kb / kGemmStages) & 1;
             const int c = kb >> 2, b = c & (kBitsSlots - 1), sub = kb & 3;
-            const long long t0 = GT_NOW();
+            GT_T(t0);
             if (c != c_seen) { ok = mbar_wait(bar_bits_full(b), (c >> kSlotShift) & 1, abort_flag, P.status); c_seen = c; }
             ok = ok && mbar_wait(bar_free(s), ph ^ 1, abort_flag, P.status);
             if (!ok) break;
-            const long long t1 = GT_NOW();
+            GT_T(t1);
             GT_ADD(0, t1 - t0);
             const uint4* bits = reinterpret_cast<const uint4*>(smem + kOffBits + b * kBitsSlotBytes);
             const uint2* pre2 = reinterpret_cast<const uint2*>(smem + kOffPre + b * kPreBytes + sub * (kBK * 2));
@@ -402,7 +413,7 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_stage_kernel(const __grid_c
                     }
                 }
             }
-            const long long t2 = GT_NOW();
+            GT_T(t2);
             GT_ADD(1, t2 - t1);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the MMA
             mbar_arrive(bar_ready(s));
@@ -423,7 +434,7 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_stage_kernel(const __grid_c
         if (ok) {
             tc_fence_after();
             const int lq = warp & 3;                 // tensor-memory lane quarter this warp may read
-            const int sub_w = (warp - 3) >> 2;       // index among the warps of that quarter
+            const int sub_w = (warp - kFirstExpandWarp) >> 2;   // index among the warps of that quarter
             const float lim = P.saturate ? (P.is_bf16 ? 3.3895313892515355e+38f : 64504.0f) : 3.4e38f;
             const float4* post4 = reinterpret_cast<const float4*>(smem + kOffPost);
 #pragma unroll 1
@@ -432,6 +443,12 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_stage_kernel(const __grid_c
                 const int row = m0 + kBM * mh + 32 * lq + lane;     // token
                 uint32_t r[32];
                 tmem_ld32(tmem_base + ((uint32_t)(32 * lq) << 16) + (uint32_t)(mh * kBN + c0), r);
+                if (C::kIssuers == 2 && nkb > 1) {   // the second issuer's accumulator
+                    uint32_t r2[32];
+                    tmem_ld32(tmem_base + ((uint32_t)(32 * lq) << 16) + (uint32_t)(MH * kBN + mh * kBN + c0), r2);
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) + __uint_as_float(r2[e]));
+                }
                 if (row >= P.T || n0 + c0 >= P.Nout) continue;
                 if (P.splits > 1) {   // partial sums of this k range: a warp writes 32 consecutive tokens per column
                     float* slab = P.slabs + ((size_t)blockIdx.z * P.Nout + n0 + c0) * P.t_pad + row;
@@ -473,12 +490,12 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_stage_kernel(const __grid_c
             }
         }
     }
-    if (P.splits > 1 && warp >= 3) {
+    if (P.splits > 1 && warp >= kFirstExpandWarp) {
         // Split-K tail.  Every expand thread passes both barriers whatever happened before, so an expired wait
         // elsewhere cannot leave threads behind.  The CTA that finds the other splits' arrivals at the tile's
         // counter adds the slabs up in split order (the result does not depend on arrival order).
         volatile int* last_flag = reinterpret_cast<volatile int*>(smem + kOffMisc + 8);
-        const int tu = threadIdx.x - 96;
+        const int tu = threadIdx.x - 32 * kFirstExpandWarp;
         __threadfence();
         asm volatile("bar.sync 1, %0;" ::"n"(kExpandThreads) : "memory");
         if (tu == 0) {
@@ -616,7 +633,7 @@ static StagePlan plan_stage(int T, int K, int Nout, bool allow_split) {
         const long long tiles = (long long)((T + kBM * c[0] - 1) / (kBM * c[0])) * ((Nout + 128 * c[1] - 1) / (128 * c[1]));
         const long long waves = (tiles + sms - 1) / sms;
         // measured cycles of the MMA thread per 64-column step (wait + issue, tensor pipe busy)
-        const long long per_step = c[0] * c[1] == 4 ? 970 : (c[0] == 2 ? 740 : (c[1] == 2 ? 830 : 510));
+        const long long per_step = c[0] * c[1] == 4 ? 990 : (c[0] == 2 ? 580 : (c[1] == 2 ? 830 : 485));
         const long long cost = waves * (steps * per_step + 6000 + 2000LL * c[0] * c[1]);
         if (best < 0 || cost < best) { best = cost; pl.mh = c[0]; pl.nh = c[1]; }
     }
@@ -697,10 +714,11 @@ static int launch_stage(const void* a, long long lda, const void* tiles, const v
     }
     const void* fn;
     size_t smem_bytes;
-    if (mh == 1 && nh == 1) { fn = (const void*)gemm_stage_kernel<1, 1>; smem_bytes = GemmCfg<1, 1>::kSmemBytes; }
-    else if (mh == 1) { fn = (const void*)gemm_stage_kernel<1, 2>; smem_bytes = GemmCfg<1, 2>::kSmemBytes; }
-    else if (nh == 1) { fn = (const void*)gemm_stage_kernel<2, 1>; smem_bytes = GemmCfg<2, 1>::kSmemBytes; }
-    else { fn = (const void*)gemm_stage_kernel<2, 2>; smem_bytes = GemmCfg<2, 2>::kSmemBytes; }
+    int threads;
+    if (mh == 1 && nh == 1) { fn = (const void*)gemm_stage_kernel<1, 1>; smem_bytes = GemmCfg<1, 1>::kSmemBytes; threads = GemmCfg<1, 1>::kThreads; }
+    else if (mh == 1) { fn = (const void*)gemm_stage_kernel<1, 2>; smem_bytes = GemmCfg<1, 2>::kSmemBytes; threads = GemmCfg<1, 2>::kThreads; }
+    else if (nh == 1) { fn = (const void*)gemm_stage_kernel<2, 1>; smem_bytes = GemmCfg<2, 1>::kSmemBytes; threads = GemmCfg<2, 1>::kThreads; }
+    else { fn = (const void*)gemm_stage_kernel<2, 2>; smem_bytes = GemmCfg<2, 2>::kSmemBytes; threads = GemmCfg<2, 2>::kThreads; }
     // Programmatic stream serialization lets this grid start while the previous kernel of the stream drains
     // (see the kernel's griddepcontrol instructions).  If the driver refuses the attribute once, plain
     // launches are used from then on.
@@ -708,7 +726,7 @@ static int launch_stage(const void* a, long long lda, const void* tiles, const v
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3((Nout + 128 * nh - 1) / (128 * nh), m_tiles, pl.splits);
-    cfg.blockDim = dim3(kGemmThreads);
+    cfg.blockDim = dim3(threads);
     cfg.dynamicSmemBytes = smem_bytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr;
