@@ -449,7 +449,7 @@ def tp_layer_linears():
 
 def tp_arm(args):
     """One decode step of the 70B-shaped linears with every U sharded over the ranks: per launch
-    group the local GEMV, then one NCCL all-gather per linear of its [T, M/G] shard.  Strong scaling."""
+    group the local GEMV, then one NCCL all-gather of the group's [T, sum(M/G)] shards.  Strong scaling."""
     import torch
     import torch.distributed as dist
     from nanoquant_b200 import _lib
@@ -469,30 +469,57 @@ def tp_arm(args):
     x = {"h": torch.randn(T, TP_HIDDEN, generator=g, device=device).to(dtype),
          "i": torch.randn(T, TP_INTER, generator=g, device=device).to(dtype)}
     keep, steps, nbytes, scratch_bytes = [], [], 0, 0
+    per_linear = T > L.nq_gemv_max_tokens()   # more tokens than a decode launch takes: GEMM per linear
     for _ in range(layers):
         groups = {}
-        for (name, N, R, M, src, grp) in tp_layer_linears():
-            m = M // world
-            t = dict(v=rnd_bits(R, N), u=rnd_bits(m, R), s_in=scale(N), s_mid=scale(R), s_out=scale(m),
-                     y=torch.empty(T, m, device=device, dtype=dtype), full=torch.empty(world * T, m, device=device, dtype=dtype))
-            keep.append(t)
-            d = _lib.LinearDesc(x[src].data_ptr(), t["s_in"].data_ptr(), t["v"].data_ptr(), t["s_mid"].data_ptr(),
-                                t["u"].data_ptr(), t["s_out"].data_ptr(), t["y"].data_ptr(), N, R, m, N, m)
-            groups.setdefault(grp, []).append((d, t))
-            nbytes += R * N // 8 + R * m // 8 + 2 * (N + R + m) + 2 * T * (N + m)
+        for spec in tp_layer_linears():
+            groups.setdefault(spec[5], []).append(spec)
         for grp in sorted(groups):
-            arr = (_lib.LinearDesc * len(groups[grp]))(*[d for d, _ in groups[grp]])
-            scratch_bytes = max(scratch_bytes, L.nq_gemv_group_scratch_bytes(arr, len(arr), T))
-            steps.append((arr, [t for _, t in groups[grp]]))
+            # The shards of a launch group (q/k/v, gate/up) are written side by side into one [T, sum(M/G)]
+            # buffer, so one all-gather per group brings every rank's block: the gathered layout is
+            # [rank][T][q_r | k_r | v_r].
+            width = sum(M // world for (_, _, _, M, _, _) in groups[grp])
+            ybuf = torch.empty(T, width, device=device, dtype=dtype)
+            full = torch.empty(world * T, width, device=device, dtype=dtype)
+            descs, singles, col = [], [], 0
+            for (name, N, R, M, src, _) in groups[grp]:
+                m = M // world
+                t = dict(v=rnd_bits(R, N), u=rnd_bits(m, R), s_in=scale(N), s_mid=scale(R), s_out=scale(m))
+                keep.append(t)
+                if per_linear:
+                    t["y"] = torch.empty(T, m, device=device, dtype=dtype)
+                    t["full"] = torch.empty(world * T, m, device=device, dtype=dtype)
+                    singles.append((x[src].data_ptr(), t, N, R, m))
+                    scratch_bytes = max(scratch_bytes, L.nq_linear_scratch_bytes(T, N, R, m))
+                else:
+                    yptr = ybuf.data_ptr() + col * ybuf.element_size()
+                    descs.append(_lib.LinearDesc(x[src].data_ptr(), t["s_in"].data_ptr(), t["v"].data_ptr(),
+                                                 t["s_mid"].data_ptr(), t["u"].data_ptr(), t["s_out"].data_ptr(),
+                                                 yptr, N, R, m, N, width))
+                col += m
+                nbytes += R * N // 8 + R * m // 8 + 2 * (N + R + m) + 2 * T * (N + m)
+            arr = None
+            if not per_linear:
+                arr = (_lib.LinearDesc * len(descs))(*descs)
+                scratch_bytes = max(scratch_bytes, L.nq_gemv_group_scratch_bytes(arr, len(arr), T))
+            steps.append((arr, singles, ybuf, full))
     scratch = torch.zeros(scratch_bytes, dtype=torch.uint8, device=device)
+    launches_per_step = sum(2 * len(sg) if per_linear else 1 for (_, sg, _, _) in steps)
 
     def run():
         st = torch.cuda.current_stream(device).cuda_stream
-        for arr, ts in steps:
-            _lib.check(L.nq_gemv_group_fwd(arr, len(arr), T, _lib.NQ_BF16, scratch.data_ptr(), scratch.numel(), st), "gemv")
-            if world > 1:
-                for t in ts:
-                    dist.all_gather_into_tensor(t["full"], t["y"])
+        for arr, singles, ybuf, full in steps:
+            if per_linear:
+                for (xp, t, N, R, m) in singles:
+                    _lib.check(L.nq_linear_fwd(xp, t["s_in"].data_ptr(), t["v"].data_ptr(), t["s_mid"].data_ptr(),
+                                               t["u"].data_ptr(), t["s_out"].data_ptr(), t["y"].data_ptr(),
+                                               scratch.data_ptr(), scratch.numel(), T, N, R, m, _lib.NQ_BF16, st), "linear")
+                    if world > 1:
+                        dist.all_gather_into_tensor(t["full"], t["y"])
+            else:
+                _lib.check(L.nq_gemv_group_fwd(arr, len(arr), T, _lib.NQ_BF16, scratch.data_ptr(), scratch.numel(), st), "gemv")
+                if world > 1:
+                    dist.all_gather_into_tensor(full, ybuf)
 
     # One GPU: the step is replayed as a CUDA graph.  Several GPUs: the launches and the NCCL calls are
     # issued eagerly in stream order.  (The GEMV kernel holds a device-wide barrier and needs all its
@@ -547,11 +574,11 @@ def tp_arm(args):
             "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "s8 mma / s32 accumulate; bf16 in/out", "data": "synthetic",
             "config": {"workload": f"llama-3-70b-shaped decoder linears at {BPW} bpw, decode batch {T}, U split by output "
-                                   f"rows over {world} GPUs + NCCL all-gather per linear",
+                                   f"rows over {world} GPUs + one NCCL all-gather per launch group",
                        "layers_timed": layers, "layers": TP_LAYERS, "parallelism": f"tp{world}"},
             "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s per GPU", "frac": per_gpu / peak,
                          "traffic": None},
-            "gpu_launches": len(steps) * args.steps}), flush=True)
+            "gpu_launches": launches_per_step * args.steps}), flush=True)
     if world > 1:
         dist.destroy_process_group()
 

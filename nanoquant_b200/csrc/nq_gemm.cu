@@ -43,7 +43,6 @@ namespace nq {
 constexpr int kBM = 128;            // tokens per MMA (MMA M, tensor-memory lanes)
 constexpr int kBK = 64;             // k per pipeline stage: 128 bytes of bf16 = one swizzle row
 constexpr int kGroupThreads = 256;                          // expand threads that share one k block
-constexpr int kFirstExpandWarp = 4;   // warp 0 activation TMA, warps 1 and 3 MMA, warp 2 sign bits, then expand + epilogue
 constexpr int kTileBytes = kBM * kBK * 2;          // 16 KB: one 128-row operand tile
 constexpr int kPreBytes = 256 * 2;                 // input scales of one 256-column chunk
 constexpr unsigned kWaitLimit = 1u << 21;   // attempts of up to ~2 us each
@@ -81,6 +80,8 @@ struct GemmCfg {
     // steps, so the small tiles (short k blocks) need two groups to keep up with two issuers.
     static constexpr int kGroups = (MH * NH == 4) ? 1 : 2;
     static constexpr int kExpandThreads = kGroups * kGroupThreads;
+    // warp 0 activation TMA, warp 1 MMA, warp 2 sign bits, warp 3 second MMA issuer (if any), then expand + epilogue
+    static constexpr int kFirstExpandWarp = 2 + kIssuers;
     static constexpr int kThreads = 32 * kFirstExpandWarp + kExpandThreads;
     static constexpr int kTmemCols = kIssuers * MH * kBN;
 };
@@ -217,6 +218,7 @@ __global__ void __launch_bounds__(GemmCfg<MH, NH>::kThreads) gemm_stage_kernel(c
     constexpr int kGemmStages = C::kStages, kBN = C::kBN, kBitsSlotBytes = C::kBitsSlotBytes;
     constexpr int kBitsSlots = C::kBitsSlots, kSlotShift = (kBitsSlots == 4) ? 2 : 1;
     constexpr int kExpandThreads = C::kExpandThreads, kGroups = C::kGroups, kGemmThreads = C::kThreads;
+    constexpr int kFirstExpandWarp = C::kFirstExpandWarp;
     constexpr int kOffA = C::kOffA, kOffW = C::kOffW, kOffBits = C::kOffBits, kOffPre = C::kOffPre;
     constexpr int kOffBar = C::kOffBar, kOffMisc = C::kOffMisc, kOffPost = C::kOffPost;
     extern __shared__ unsigned char smem_raw[];
@@ -320,7 +322,7 @@ __global__ void __launch_bounds__(GemmCfg<MH, NH>::kThreads) gemm_stage_kernel(c
                               (uint32_t)pre_bytes, bar_bits_full(b));
             }
         }
-    } else if (warp == 1 || warp == 3) {
+    } else if (warp == 1 || (C::kIssuers == 2 && warp == 3)) {
         // ------------------------------------------------------------ MMA issuers
         const int mw = warp == 1 ? 0 : 1;
         if (lane == 0 && mw < C::kIssuers) {

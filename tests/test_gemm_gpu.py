@@ -120,6 +120,39 @@ def test_c_abi_gemm_and_gemv_agree_at_the_dispatch_boundary():
     assert oc.rel_err(exact_np(outs[0]), exact_np(outs[1])) <= 2 * TOL[torch.float16]
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(1032, 264, 1001, 7), (4096, 1608, 4099, 23), (520, 8, 33, 64)])
+def test_c_abi_linear_few_tokens_ragged_split(shape, dtype):
+    # 5..64 tokens: nq_linear_fwd takes the GEMM with the k dimension split over CTAs.  Ragged rank, output
+    # width (odd: element stores) and token count; the scratch is shared with a decode call in between, which
+    # must leave the tile counters in the header alone; the result is the same bit for bit on every call.
+    from nanoquant_b200 import _lib
+    from nanoquant_b200.kernel import utils as ku
+    Lb = _lib.lib()
+    N, R, M, T = shape
+    L = make_layer(N, R, M, T, dtype, seed=sum(shape))
+    vt = ku.pack_tiles(half2_bits(L["V"]), (R, N), "half2")
+    ut = ku.pack_tiles(half2_bits(L["U"]), (M, R), "half2")
+    st = torch.cuda.current_stream().cuda_stream
+    dt = _lib.NQ_F16 if dtype == torch.float16 else _lib.NQ_BF16
+    nbytes = max(Lb.nq_linear_scratch_bytes(T, N, R, M), Lb.nq_linear_scratch_bytes(1, N, R, M))
+    scratch = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+    args = lambda x, y, t: (x.data_ptr(), L["s_pre"].data_ptr(), vt.data_ptr(), L["s_mid"].data_ptr(), ut.data_ptr(),
+                            L["s_post"].data_ptr(), y.data_ptr(), scratch.data_ptr(), nbytes, t, N, R, M, dt, st)
+    ys = []
+    for rep in range(3):
+        y = torch.empty(T, M, dtype=dtype, device="cuda")
+        _lib.check(Lb.nq_linear_fwd(*args(L["x"], y, T)), "nq_linear_fwd")
+        ys.append(y)
+        if rep == 0:   # a one-token decode call on the same scratch between two GEMM calls
+            y1 = torch.empty(1, M, dtype=dtype, device="cuda")
+            _lib.check(Lb.nq_linear_fwd(*args(L["x"][:1].contiguous(), y1, 1)), "nq_linear_fwd")
+            assert oc.rel_err(exact_np(y1), L["y64"][:1]) <= 2 * TOL[dtype]
+    assert Lb.nq_scratch_status(scratch.data_ptr(), st) == 0
+    assert oc.rel_err(exact_np(ys[0]), L["y64"]) <= TOL[dtype]
+    assert torch.equal(ys[0], ys[1]) and torch.equal(ys[1], ys[2])
+
+
 def test_gemm_linearity_full_size(ops):
     # size-independent property at a full-size shape: the op is linear in x.  Doubling x doubles every
     # fp32 partial sum exactly; only intermediate values that fall into the fp16 subnormal range may
