@@ -191,6 +191,11 @@ def workload_config(T):
 # --------------------------------------------------------------------------------------------
 # GPU arm
 # --------------------------------------------------------------------------------------------
+# dram__bytes_read.sum + dram__bytes_write.sum over the algorithmic bytes of the captured decode launches
+# (o, gate+up, down groups: 17.50 MB against 16.82 MB; no writes reach DRAM)
+DRAM_TRAFFIC_RATIO = 1.04
+
+
 class Step:
     """Device-resident weights of the decoder layers and the launch list of one decode step."""
 
@@ -408,7 +413,11 @@ def gpu_arm(args):
         "config": dict(workload_config(T), layers_timed=args.layers,
                        parallelism=("single gpu" if world == 1 else f"{world} independent replicas")),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "kernel": step.kernel_name,
+                     "traffic": (step.bytes / step.kernels_per_step * DRAM_TRAFFIC_RATIO if not step.per_linear else None),
+                     "traffic_source": ("ncu dram__bytes_read+write of three captured launches = 1.04 x their algorithmic "
+                                        "bytes (profiles/gemv_group_kernel_qwen3_8b_decode.md), scaled to the average launch"
+                                        if not step.per_linear else None),
+                     "kernel": step.kernel_name,
                      "bytes_per_launch": step.bytes / step.kernels_per_step, "us_per_launch": launch_us,
                      "peak_source": peak_src},
         "e2e": {"value": world * T / (e2e_ms * 1e-3 / args.steps), "unit": "tokens/s",

@@ -5,22 +5,22 @@
 //
 // Each stage is one launch of the same kernel: Out[T, Nout] = (A[T, K] . W[Nout, K]^T) * post,
 // where W = +-pre[k] comes from packed sign bits.  One CTA computes a (128 or 256)-token x
-// 128-row output tile, so that one expanded weight tile feeds up to two MMAs:
+// (128 or 256)-row output tile (or its share of K, see split-K below):
 //
 //   warp 0      TMA producer: the activation tile [128|256 tokens x 64 k] through a tensor map
-//               (cp.async.bulk.tensor, 128-byte swizzle), the packed sign bits of the
-//               128 weight rows (1-D bulk copies of the GEMV tile layout, one 256-column
-//               chunk = 4 KB at a time) with the 256 input scales of the chunk.
-//   warp 2      the packed sign bits of the tile's weight rows and the input scales, one 256-column
-//               chunk per step, ahead of the expand warps.
-//   warps 3-10  expand the bits to +-pre[k] in bf16/fp16 directly in the K-major
-//               128-byte-swizzled layout the MMA reads (the product x * (+-s_in) is then
-//               exact inside the MMA; pre-scaling x would round it), fence.proxy.async,
-//               signal "weights ready"; afterwards the same warps run the epilogue.
-//   warp 1      one thread issues tcgen05.mma (M = 128 tokens, N = 128 rows, K = 16,
-//               kind::f16, fp32 accumulator in tensor memory) and commits the stage's
-//               buffers back to the producer with tcgen05.commit.
-//   epilogue    tcgen05.ld of the accumulator (lane = token, column = output row),
+//               (cp.async.bulk.tensor, 128-byte swizzle), one per k block.
+//   warp 2      the packed sign bits of the tile's weight rows (1-D bulk copies of the GEMV tile
+//               layout) and the input scales, one 256-column chunk per step, ahead of the expand warps.
+//               (One loading thread for both was measured 10 % slower, an idle warp 5 % slower.)
+//   warp 1      one thread issues tcgen05.mma (M = 128 tokens, N = 128|256 rows, K = 16, kind::f16,
+//               fp32 accumulator in tensor memory) and commits the stage's buffers back with
+//               tcgen05.commit.  The tiles smaller than 256 x 256 have a second issuer (warp 3) with
+//               an accumulator of its own on the odd k blocks.
+//   then 8|16   expand warps turn the bits into +-pre[k] bf16/fp16 directly in the K-major
+//               128-byte-swizzled layout the MMA reads (the product x * (+-s_in) is then exact
+//               inside the MMA; pre-scaling x would round it), fence.proxy.async, arrive on the
+//               stage's "ready" barrier; afterwards the same warps run the epilogue.
+//   epilogue    tcgen05.ld of the accumulator(s) (lane = token, column = output row),
 //               * post[n], saturate, convert, 16-byte stores.
 //
 // The packed operand is the same tile layout the decode GEMV streams (nq_rows_to_tiles),
