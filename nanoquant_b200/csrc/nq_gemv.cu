@@ -666,13 +666,9 @@ __device__ __forceinline__ bool run_all(const Phase* phases, const GemvParams& P
         cp_async_wait<0>();
         __syncthreads();
         NQ_TRACE(6);
-        // start the next job's weight stream before this job's epilogue and before any barrier
         const int my_items = st.my_items;
-        const int s_next = next_step(s + 1);
         const int first_tile_of_job = st.first;
         const uint16_t* my_post = post_s + st.slot * (32 * P.max_items);
-        if (s_next < 2 * njobs)
-            stream_begin(st, job_of(s_next), phases[s_next >= njobs], ring, warp, lane, post_s, P.max_items);
         // finalise: thread -> (token slot, row slot); tokens beyond the slot count and rows beyond the 128 row
         // slots are covered by the strides.  The three column sums of a token are the byte terms of
         // 128 * sum_{bit=1}(X); result = sum(X) - 2 * sum_{bit=1}(X) = sum(X) - terms / 64 (terms is a multiple of 128).
@@ -700,6 +696,11 @@ __device__ __forceinline__ bool run_all(const Phase* phases, const GemvParams& P
                 }
             }
         }
+        // Start the next job's weight stream after this job's results are on their way (their stores then
+        // overlap the address arithmetic below) and before any barrier, whose wait the loads overlap.
+        const int s_next = next_step(s + 1);
+        if (s_next < 2 * njobs)
+            stream_begin(st, job_of(s_next), phases[s_next >= njobs], ring, warp, lane, post_s, P.max_items);
         __syncthreads();  // xq / s1 are reused by the next job
         NQ_TRACE(7);
         s = s_next;

@@ -63,6 +63,36 @@ def test_gemv_more_than_four_tokens(op, T):
     assert oc.rel_err(exact_np(run(op, L)), L["y64"]) <= TOL[torch.float16]
 
 
+@pytest.mark.parametrize("T", [5, 9])
+def test_c_abi_gemv_more_tokens_than_one_launch(T):
+    # nq_gemv_fwd itself (not the dispatcher) with more tokens than one launch takes: several launches of
+    # up to four tokens on the same scratch
+    from nanoquant_b200 import _lib
+    from nanoquant_b200.kernel import utils as ku
+    Lb = _lib.lib()
+    N, R, M = 1000, 136, 300      # unaligned input rows (N % 8 != 0 is fine for the GEMV), ragged rank and width
+    L = make_layer(N, R, M, T, torch.float16, seed=T)
+    vt = ku.pack_tiles(half2_bits(L["V"]), (R, N), "half2")
+    ut = ku.pack_tiles(half2_bits(L["U"]), (M, R), "half2")
+    st = torch.cuda.current_stream().cuda_stream
+    nbytes = Lb.nq_gemv_scratch_bytes(T, N, R, M)
+    scratch = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+    y = torch.empty(T, M, dtype=torch.float16, device="cuda")
+    _lib.check(Lb.nq_gemv_fwd(L["x"].data_ptr(), L["s_pre"].data_ptr(), vt.data_ptr(), L["s_mid"].data_ptr(),
+                              ut.data_ptr(), L["s_post"].data_ptr(), y.data_ptr(), scratch.data_ptr(), nbytes,
+                              T, N, R, M, _lib.NQ_F16, st), "nq_gemv_fwd")
+    assert Lb.nq_scratch_status(scratch.data_ptr(), st) == 0
+    assert oc.rel_err(exact_np(y), L["y64"]) <= TOL[torch.float16]
+
+
+@pytest.mark.parametrize("shape", [(8192, 5056, 3584, 2), (28672, 5056, 1024, 1)])
+def test_gemv_70b_shard_shapes(op, shape):
+    # Llama-3-70B-shaped gate/up and down projections at 0.8 bpw with U split eight ways by output rows
+    N, R, M, T = shape
+    L = make_layer(N, R, M, T, torch.float16, seed=N + M)
+    assert oc.rel_err(exact_np(run(op, L)), L["y64"]) <= TOL[torch.float16]
+
+
 def test_gemv_without_scale_mid_and_1d_input(op):
     L = make_layer(512, 128, 256, 1, torch.float16, seed=2, has_mid=False)
     y2 = run(op, L)
