@@ -41,6 +41,7 @@ sys.path.insert(0, ROOT)
 HIDDEN, INTER, LAYERS, KV = 4096, 12288, 36, 1024
 BPW = 0.8
 WORKLOAD = "qwen3-8b"
+GEMM_MIN_TOKENS = 0   # --gemm-min-tokens: decode batches from this size on use the group GEMM (0: the library's dispatch limit)
 # name -> (hidden, intermediate, layers, kv width, bits per weight); the first one is the headline workload
 WORKLOADS = {"qwen3-8b": (4096, 12288, 36, 1024, 0.8), "llama-3.2-1b": (2048, 8192, 16, 512, 1.0)}
 L2_BYTES = 126e6
@@ -238,9 +239,9 @@ class Step:
                   "i": torch.randn(T, INTER, generator=g, device=device).to(dtype)}
         self.keep, self.launches, self.bytes = [], [], 0
         scratch_bytes = 0
-        # more tokens than one decode launch takes: every linear goes through nq_linear_fwd (split-K GEMM)
-        self.per_linear = T > self.L.nq_gemv_max_tokens()
-        self.singles = []
+        # more tokens than one decode launch takes: the groups go through nq_gemm_group_fwd (split-K GEMM)
+        self.per_linear = T >= (GEMM_MIN_TOKENS or self.L.nq_gemv_max_tokens() + 1)
+        self.n_linears = 0
         for _ in range(layers):
             groups = {}
             for (name, N, R, M, src, grp) in layer_linears():
@@ -252,27 +253,25 @@ class Step:
                                     t["y"].data_ptr(), N, R, M, N, M)
                 groups.setdefault(grp, []).append(d)
                 self.bytes += algorithmic_bytes(N, R, M, T)
-                if self.per_linear:
-                    self.singles.append((self.x[src].data_ptr(), t, N, R, M))
-                    scratch_bytes = max(scratch_bytes, self.L.nq_linear_scratch_bytes(T, N, R, M))
+                self.n_linears += 1
             for grp in sorted(groups):
                 arr = (_lib.LinearDesc * len(groups[grp]))(*groups[grp])
-                scratch_bytes = max(scratch_bytes, self.L.nq_gemv_group_scratch_bytes(arr, len(arr), T))
+                size_fn = self.L.nq_gemm_group_scratch_bytes if self.per_linear else self.L.nq_gemv_group_scratch_bytes
+                scratch_bytes = max(scratch_bytes, size_fn(arr, len(arr), T))
                 self.launches.append(arr)
         self.last_y = self.keep[-1]["y"]
         self.scratch = torch.zeros(scratch_bytes, dtype=torch.uint8, device=device)
-        self.kernels_per_step = 2 * len(self.singles) if self.per_linear else len(self.launches)
+        self.kernels_per_step = (2 if self.per_linear else 1) * len(self.launches)
         self.kernel_name = "gemm_stage_kernel (split-K)" if self.per_linear else "gemv_group_kernel"
         self.graph = None
 
     def run(self):
         st = self.torch.cuda.current_stream(self.device).cuda_stream
         if self.per_linear:
-            for (xp, t, N, R, M) in self.singles:
-                rc = self.L.nq_linear_fwd(xp, t["s_in"].data_ptr(), t["v"].data_ptr(), t["s_mid"].data_ptr(),
-                                          t["u"].data_ptr(), t["s_out"].data_ptr(), t["y"].data_ptr(),
-                                          self.scratch.data_ptr(), self.scratch.numel(), self.T, N, R, M, self.dt_id, st)
-                self.lib.check(rc, "nq_linear_fwd")
+            for arr in self.launches:
+                rc = self.L.nq_gemm_group_fwd(arr, len(arr), self.T, self.dt_id, self.scratch.data_ptr(),
+                                              self.scratch.numel(), st)
+                self.lib.check(rc, "nq_gemm_group_fwd")
             return
         for arr in self.launches:
             rc = self.L.nq_gemv_group_fwd(arr, len(arr), self.T, self.dt_id, self.scratch.data_ptr(),
@@ -531,7 +530,9 @@ def tp_arm(args):
     x = {"h": torch.randn(T, TP_HIDDEN, generator=g, device=device).to(dtype),
          "i": torch.randn(T, TP_INTER, generator=g, device=device).to(dtype)}
     keep, steps, nbytes, scratch_bytes = [], [], 0, 0
-    per_linear = T > L.nq_gemv_max_tokens()   # more tokens than a decode launch takes: GEMM per linear
+    use_gemm = T > L.nq_gemv_max_tokens()   # more tokens than a decode launch takes: the group GEMM (two launches)
+    group_fwd = L.nq_gemm_group_fwd if use_gemm else L.nq_gemv_group_fwd
+    group_bytes = L.nq_gemm_group_scratch_bytes if use_gemm else L.nq_gemv_group_scratch_bytes
     for _ in range(layers):
         groups = {}
         for spec in tp_layer_linears():
@@ -543,45 +544,29 @@ def tp_arm(args):
             width = sum(M // world for (_, _, _, M, _, _) in groups[grp])
             ybuf = torch.empty(T, width, device=device, dtype=dtype)
             full = torch.empty(world * T, width, device=device, dtype=dtype)
-            descs, singles, col = [], [], 0
+            descs, col = [], 0
             for (name, N, R, M, src, _) in groups[grp]:
                 m = M // world
                 t = dict(v=rnd_bits(R, N), u=rnd_bits(m, R), s_in=scale(N), s_mid=scale(R), s_out=scale(m))
                 keep.append(t)
-                if per_linear:
-                    t["y"] = torch.empty(T, m, device=device, dtype=dtype)
-                    t["full"] = torch.empty(world * T, m, device=device, dtype=dtype)
-                    singles.append((x[src].data_ptr(), t, N, R, m))
-                    scratch_bytes = max(scratch_bytes, L.nq_linear_scratch_bytes(T, N, R, m))
-                else:
-                    yptr = ybuf.data_ptr() + col * ybuf.element_size()
-                    descs.append(_lib.LinearDesc(x[src].data_ptr(), t["s_in"].data_ptr(), t["v"].data_ptr(),
-                                                 t["s_mid"].data_ptr(), t["u"].data_ptr(), t["s_out"].data_ptr(),
-                                                 yptr, N, R, m, N, width))
+                yptr = ybuf.data_ptr() + col * ybuf.element_size()
+                descs.append(_lib.LinearDesc(x[src].data_ptr(), t["s_in"].data_ptr(), t["v"].data_ptr(),
+                                             t["s_mid"].data_ptr(), t["u"].data_ptr(), t["s_out"].data_ptr(),
+                                             yptr, N, R, m, N, width))
                 col += m
                 nbytes += R * N // 8 + R * m // 8 + 2 * (N + R + m) + 2 * T * (N + m)
-            arr = None
-            if not per_linear:
-                arr = (_lib.LinearDesc * len(descs))(*descs)
-                scratch_bytes = max(scratch_bytes, L.nq_gemv_group_scratch_bytes(arr, len(arr), T))
-            steps.append((arr, singles, ybuf, full))
+            arr = (_lib.LinearDesc * len(descs))(*descs)
+            scratch_bytes = max(scratch_bytes, group_bytes(arr, len(arr), T))
+            steps.append((arr, ybuf, full))
     scratch = torch.zeros(scratch_bytes, dtype=torch.uint8, device=device)
-    launches_per_step = sum(2 * len(sg) if per_linear else 1 for (_, sg, _, _) in steps)
+    launches_per_step = (2 if use_gemm else 1) * len(steps)
 
     def run():
         st = torch.cuda.current_stream(device).cuda_stream
-        for arr, singles, ybuf, full in steps:
-            if per_linear:
-                for (xp, t, N, R, m) in singles:
-                    _lib.check(L.nq_linear_fwd(xp, t["s_in"].data_ptr(), t["v"].data_ptr(), t["s_mid"].data_ptr(),
-                                               t["u"].data_ptr(), t["s_out"].data_ptr(), t["y"].data_ptr(),
-                                               scratch.data_ptr(), scratch.numel(), T, N, R, m, _lib.NQ_BF16, st), "linear")
-                    if world > 1:
-                        dist.all_gather_into_tensor(t["full"], t["y"])
-            else:
-                _lib.check(L.nq_gemv_group_fwd(arr, len(arr), T, _lib.NQ_BF16, scratch.data_ptr(), scratch.numel(), st), "gemv")
-                if world > 1:
-                    dist.all_gather_into_tensor(full, ybuf)
+        for arr, ybuf, full in steps:
+            _lib.check(group_fwd(arr, len(arr), T, _lib.NQ_BF16, scratch.data_ptr(), scratch.numel(), st), "group_fwd")
+            if world > 1:
+                dist.all_gather_into_tensor(full, ybuf)
 
     # One GPU: the step is replayed as a CUDA graph.  Several GPUs: the launches and the NCCL calls are
     # issued eagerly in stream order.  (The GEMV kernel holds a device-wide barrier and needs all its
@@ -634,7 +619,8 @@ def tp_arm(args):
             "mode": "tp", "metric": "decode tok/s (quantised linears of one decode step)", "value": T / step_s,
             "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "s8 mma / s32 accumulate; bf16 in/out", "data": "synthetic",
+            "dtype": ("bf16 tcgen05 mma / f32 accumulate; bf16 in/out" if use_gemm else "s8 mma / s32 accumulate; bf16 in/out"),
+            "data": "synthetic",
             "config": {"workload": f"llama-3-70b-shaped decoder linears at {BPW} bpw, decode batch {T}, U split by output "
                                    f"rows over {world} GPUs + one NCCL all-gather per launch group",
                        "layers_timed": layers, "layers": TP_LAYERS, "parallelism": f"tp{world}"},
@@ -740,6 +726,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="qwen3-8b", choices=sorted(WORKLOADS),
                     help="decoder shape of the decode step (qwen3-8b is the headline workload)")
+    ap.add_argument("--gemm-min-tokens", type=int, default=0,
+                    help="decode batches of at least this many tokens run the group GEMM instead of the GEMV (0: library default)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-side-numbers", action="store_true",
                     help="skip the short batch-4 / batch-16 / prefill measurements added to the default line")
@@ -750,6 +738,8 @@ def main():
     ap.add_argument("--layers", type=int, default=LAYERS, help="decoder layers resident (fewer only for profiling)")
     ap.add_argument("--tp-layers", type=int, default=TP_LAYERS, help="layers actually timed in --mode tp")
     args = ap.parse_args()
+    global GEMM_MIN_TOKENS
+    GEMM_MIN_TOKENS = args.gemm_min_tokens
     set_workload(args.workload)
     if args.layers == WORKLOADS["qwen3-8b"][2]:   # the default of --layers means "all layers of the workload"
         args.layers = LAYERS

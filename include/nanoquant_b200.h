@@ -215,6 +215,15 @@ int nq_gemm_fwd(const void* x, const void* s_in, const void* v_tiles, const void
                 void* scratch, size_t scratch_bytes,
                 int T, int N, int R, int M, int dtype, nq_stream_t stream);
 
+/* The same for up to four linears that share the token count (q/k/v, gate/up; the
+ * descriptors of nq_gemv_group_fwd, with ldx / ldy honoured): one launch per
+ * stage for the whole group, which matters for few tokens, where a single linear
+ * leaves most SMs idle.  No counterpart in the reference (its callers run one
+ * linear per call).  Scratch: nq_gemm_group_scratch_bytes(), zeroed once. */
+size_t nq_gemm_group_scratch_bytes(const nq_linear_desc* linears_host, int n_linears, int T);
+int nq_gemm_group_fwd(const nq_linear_desc* linears_host, int n_linears, int T, int dtype,
+                      void* scratch, size_t scratch_bytes, nq_stream_t stream);
+
 /* One stage: y[T, Nout] = s_out * (W . (s_in * x[T, K])) with W [Nout, K] in the
  * tile layout; s_in and s_out may be NULL.  `status_word` points at a zeroed
  * 16-byte device area (a scratch header works) whose third word receives a

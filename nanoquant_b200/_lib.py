@@ -53,6 +53,8 @@ SIGNATURES = {
     "nq_gemv_static_max_rank": (c_size_t, []),
     "nq_gemm_scratch_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "nq_gemm_fwd": (c_int, [c_void_p] * 8 + [c_size_t, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "nq_gemm_group_scratch_bytes": (c_size_t, [ctypes.POINTER(LinearDesc), c_int, c_int]),
+    "nq_gemm_group_fwd": (c_int, [ctypes.POINTER(LinearDesc), c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "nq_onebit_gemm_fwd": (c_int, [c_void_p] * 6 + [c_int, c_int, c_int, c_int, c_void_p]),
     "nq_gemv_max_tokens": (c_int, []),
     "nq_linear_scratch_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),

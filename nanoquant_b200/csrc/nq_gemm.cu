@@ -86,24 +86,34 @@ struct GemmCfg {
     static constexpr int kTmemCols = kIssuers * MH * kBN;
 };
 
-struct GemmParams {
+// One linear's stage inside a launch.  A launch runs the same stage of up to four linears that share the
+// token count (q/k/v, gate/up): their output tiles are laid side by side along grid.x.
+struct alignas(64) GemmJob {
     CUtensorMap map_a;     // activations [T, K], box 64 x (128 * MH), 128-byte swizzle
     const uint4* tiles;    // packed weights, GEMV tile layout [row_groups][chunks][32]
     const void* pre;       // [K] input scales (I/O dtype) or nullptr (weights are +-1)
     const void* post;      // [Nout] output scales (I/O dtype) or nullptr
     void* out;             // [T, ld_out] I/O dtype
     long long ld_out;
-    unsigned* status;      // device status word (0 = ok)
-    int T, K, Nout;
+    // split-K (few tokens, few output tiles): `splits` CTAs along grid.z share an output tile, each over
+    // `chunks_per` 256-column chunks; partial sums go to fp32 slabs [split][Nout][t_pad] and the CTA that
+    // arrives last at the tile's counter adds them up in split order and writes the output.
+    float* slabs;
+    unsigned* counters;    // one per output tile of this job, zero between launches
+    int K, Nout;
     int chunks, row_groups;
+    int splits, chunks_per;
+    int tile0;             // first grid.x index of this job's tiles
+};
+constexpr int kMaxGemmJobs = 4;
+
+struct GemmParams {
+    GemmJob job[kMaxGemmJobs];
+    int njobs;
+    unsigned* status;      // device status word (0 = ok)
+    int T, t_pad;          // tokens; slab row length (tokens, multiple of 4)
     int is_bf16;
     int saturate;          // apply the reference's output saturation bounds
-    // split-K (few tokens, few output tiles): grid.z CTAs share an output tile, each over `chunks_per`
-    // 256-column chunks; partial sums go to fp32 slabs [split][Nout][t_pad] and the CTA that arrives last
-    // at the tile's counter adds them up in split order and writes the output.
-    int splits, chunks_per, t_pad;
-    float* slabs;
-    unsigned* counters;    // one per output tile, zero between launches
 };
 
 // ---------------------------------------------------------------------------
@@ -226,13 +236,18 @@ __global__ void __launch_bounds__(GemmCfg<MH, NH>::kThreads) gemm_stage_kernel(c
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     const uint32_t sbase = smem_u32(smem);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * kBN;   // first weight row of the tile
+    int ji = 0;
+    while (ji + 1 < P.njobs && (int)blockIdx.x >= P.job[ji + 1].tile0) ++ji;
+    const GemmJob& J = P.job[ji];
+    if ((int)blockIdx.z >= J.splits) return;   // grid.z is the largest split count of the launch
+    const int tile = (int)blockIdx.x - J.tile0;
+    const int n0 = tile * kBN;   // first weight row of the tile
     const int m0 = blockIdx.y * (kBM * MH);   // first token of the tile
     // k range of this CTA (all of K unless the launch is split): whole 256-column chunks
-    const int c_begin = (int)blockIdx.z * P.chunks_per;
-    const int c_end = min(P.chunks, c_begin + P.chunks_per);
+    const int c_begin = (int)blockIdx.z * J.chunks_per;
+    const int c_end = min(J.chunks, c_begin + J.chunks_per);
     const int kb_begin = 4 * c_begin;
-    const int nkb = min((P.K + kBK - 1) / kBK, 4 * c_end) - kb_begin;   // k blocks of this CTA
+    const int nkb = min((J.K + kBK - 1) / kBK, 4 * c_end) - kb_begin;   // k blocks of this CTA
 
     // One barrier per stage and direction: "ready" completes when the activation tile has landed (the
     // producer's expect-tx arrival plus the TMA's bytes) AND the expand group has arrived for the weight
@@ -270,9 +285,9 @@ __global__ void __launch_bounds__(GemmCfg<MH, NH>::kThreads) gemm_stage_kernel(c
         reinterpret_cast<uint32_t*>(smem + kOffPre)[i] = 0;
     for (int i = threadIdx.x; i < kBN; i += kGemmThreads) {   // output scales of this tile, once, as fp32
         float f = 1.f;
-        if (P.post && n0 + i < P.Nout)
-            f = P.is_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(P.post)[n0 + i])
-                          : __half2float(static_cast<const __half*>(P.post)[n0 + i]);
+        if (J.post && n0 + i < J.Nout)
+            f = P.is_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(J.post)[n0 + i])
+                          : __half2float(static_cast<const __half*>(J.post)[n0 + i]);
         reinterpret_cast<float*>(smem + kOffPost)[i] = f;
     }
     if (warp == 1) {  // tensor-memory allocation: 128 fp32 columns per accumulator, by one whole warp
@@ -285,7 +300,7 @@ __global__ void __launch_bounds__(GemmCfg<MH, NH>::kThreads) gemm_stage_kernel(c
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    int nrg = P.row_groups - (n0 >> 4);          // row groups of this tile that exist
+    int nrg = J.row_groups - (n0 >> 4);          // row groups of this tile that exist
     nrg = nrg > kBN / 16 ? kBN / 16 : nrg;
 
     if (warp == 0) {
@@ -297,7 +312,7 @@ __global__ void __launch_bounds__(GemmCfg<MH, NH>::kThreads) gemm_stage_kernel(c
                 const uint32_t ph = (kb / kGemmStages) & 1;
                 if (!mbar_wait(bar_free(s), ph ^ 1, abort_flag, P.status)) break;
                 mbar_expect_tx(bar_ready(s), (uint32_t)(MH * kTileBytes));
-                tma_load_2d(sbase + kOffA + s * (C::kABytes), &P.map_a, (kb_begin + kb) * kBK, m0, bar_ready(s));
+                tma_load_2d(sbase + kOffA + s * (C::kABytes), &J.map_a, (kb_begin + kb) * kBK, m0, bar_ready(s));
             }
         }
     } else if (warp == 2) {
@@ -309,16 +324,16 @@ __global__ void __launch_bounds__(GemmCfg<MH, NH>::kThreads) gemm_stage_kernel(c
                 const int b = cl & (kBitsSlots - 1), c = c_begin + cl;
                 if (!mbar_wait(bar_bits_empty(b), ((cl >> kSlotShift) & 1) ^ 1, abort_flag, P.status)) break;
                 int pre_bytes = 0;
-                if (P.pre) {
-                    const int left = P.K - c * 256;
+                if (J.pre) {
+                    const int left = J.K - c * 256;
                     pre_bytes = (left < 256 ? left : 256) * 2;
                 }
                 mbar_expect_tx(bar_bits_full(b), (uint32_t)nrg * 512u + (uint32_t)pre_bytes);
                 for (int rg = 0; rg < nrg; ++rg)
                     bulk_load(sbase + kOffBits + b * kBitsSlotBytes + rg * 512,
-                              P.tiles + ((size_t)((n0 >> 4) + rg) * P.chunks + c) * 32, 512u, bar_bits_full(b));
+                              J.tiles + ((size_t)((n0 >> 4) + rg) * J.chunks + c) * 32, 512u, bar_bits_full(b));
                 if (pre_bytes)
-                    bulk_load(sbase + kOffPre + b * kPreBytes, static_cast<const char*>(P.pre) + (size_t)c * 512,
+                    bulk_load(sbase + kOffPre + b * kPreBytes, static_cast<const char*>(J.pre) + (size_t)c * 512,
                               (uint32_t)pre_bytes, bar_bits_full(b));
             }
         }
@@ -393,7 +408,7 @@ __global__ void __launch_bounds__(GemmCfg<MH, NH>::kThreads) gemm_stage_kernel(c
             uint2 pp[4];                                      // input scales of columns 32*jj + 16*h + 4q .. +3
 #pragma unroll
             for (int c4 = 0; c4 < 4; ++c4) {
-                if (P.pre) pp[c4] = pre2[(32 * (c4 >> 1) + 16 * (c4 & 1) + 4 * q) >> 2];
+                if (J.pre) pp[c4] = pre2[(32 * (c4 >> 1) + 16 * (c4 & 1) + 4 * q) >> 2];
                 else pp[c4] = make_uint2(one2, one2);
             }
 #pragma unroll
@@ -451,12 +466,12 @@ __global__ void __launch_bounds__(GemmCfg<MH, NH>::kThreads) gemm_stage_kernel(c
 #pragma unroll
                     for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) + __uint_as_float(r2[e]));
                 }
-                if (row >= P.T || n0 + c0 >= P.Nout) continue;
-                if (P.splits > 1) {   // partial sums of this k range: a warp writes 32 consecutive tokens per column
-                    float* slab = P.slabs + ((size_t)blockIdx.z * P.Nout + n0 + c0) * P.t_pad + row;
+                if (row >= P.T || n0 + c0 >= J.Nout) continue;
+                if (J.splits > 1) {   // partial sums of this k range: a warp writes 32 consecutive tokens per column
+                    float* slab = J.slabs + ((size_t)blockIdx.z * J.Nout + n0 + c0) * P.t_pad + row;
 #pragma unroll
                     for (int e = 0; e < 32; ++e)
-                        if (n0 + c0 + e < P.Nout) slab[(size_t)e * P.t_pad] = __uint_as_float(r[e]);
+                        if (n0 + c0 + e < J.Nout) slab[(size_t)e * P.t_pad] = __uint_as_float(r[e]);
                     continue;
                 }
                 uint32_t packed[16];
@@ -477,8 +492,8 @@ __global__ void __launch_bounds__(GemmCfg<MH, NH>::kThreads) gemm_stage_kernel(c
                         packed[2 * e4 + 1] = *reinterpret_cast<const uint32_t*>(&b2);
                     }
                 }
-                unsigned char* dst = static_cast<unsigned char*>(P.out) + ((size_t)row * P.ld_out + n0 + c0) * 2;
-                if (n0 + c0 + 32 <= P.Nout && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+                unsigned char* dst = static_cast<unsigned char*>(J.out) + ((size_t)row * J.ld_out + n0 + c0) * 2;
+                if (n0 + c0 + 32 <= J.Nout && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
 #pragma unroll
                     for (int v4 = 0; v4 < 4; ++v4)
                         reinterpret_cast<uint4*>(dst)[v4] =
@@ -486,13 +501,13 @@ __global__ void __launch_bounds__(GemmCfg<MH, NH>::kThreads) gemm_stage_kernel(c
                 } else {   // ragged edge or unaligned row: element stores, statically indexed
 #pragma unroll
                     for (int e = 0; e < 32; ++e)
-                        if (n0 + c0 + e < P.Nout)
+                        if (n0 + c0 + e < J.Nout)
                             reinterpret_cast<uint16_t*>(dst)[e] = (uint16_t)(packed[e >> 1] >> (16 * (e & 1)));
                 }
             }
         }
     }
-    if (P.splits > 1 && warp >= kFirstExpandWarp) {
+    if (J.splits > 1 && warp >= kFirstExpandWarp) {
         // Split-K tail.  Every expand thread passes both barriers whatever happened before, so an expired wait
         // elsewhere cannot leave threads behind.  The CTA that finds the other splits' arrivals at the tile's
         // counter adds the slabs up in split order (the result does not depend on arrival order).
@@ -503,9 +518,9 @@ __global__ void __launch_bounds__(GemmCfg<MH, NH>::kThreads) gemm_stage_kernel(c
         if (tu == 0) {
             int last = 0;
             if (!*abort_flag) {
-                const unsigned old = atomicAdd(P.counters + blockIdx.x, 1u);
-                last = old == (unsigned)(P.splits - 1);
-                if (last) P.counters[blockIdx.x] = 0u;   // ready for the next launch
+                const unsigned old = atomicAdd(J.counters + tile, 1u);
+                last = old == (unsigned)(J.splits - 1);
+                if (last) J.counters[tile] = 0u;   // ready for the next launch
             }
             *last_flag = last;
         }
@@ -513,7 +528,7 @@ __global__ void __launch_bounds__(GemmCfg<MH, NH>::kThreads) gemm_stage_kernel(c
         if (*last_flag) {
             __threadfence();
             const int tp4 = P.t_pad >> 2;
-            const int ncols = min(kBN, P.Nout - n0);
+            const int ncols = min(kBN, J.Nout - n0);
             const float lim = P.saturate ? (P.is_bf16 ? 3.3895313892515355e+38f : 64504.0f) : 3.4e38f;
             const float* post_s = reinterpret_cast<const float*>(smem + kOffPost);
             // Items: (column, group of four tokens).  Two items and eight splits per round keep 16 independent
@@ -527,17 +542,17 @@ __global__ void __launch_bounds__(GemmCfg<MH, NH>::kThreads) gemm_stage_kernel(c
                 for (int w = 0; w < 2; ++w) {
                     const int it = min(it0 + w * kExpandThreads, nitems - 1);   // clamped: a duplicate is not stored
                     const int col = it / tp4, r4 = it - col * tp4;
-                    src[w] = P.slabs + ((size_t)n0 + col) * P.t_pad + 4 * r4;
+                    src[w] = J.slabs + ((size_t)n0 + col) * P.t_pad + 4 * r4;
                     acc[w] = make_float4(0.f, 0.f, 0.f, 0.f);
                 }
-                const size_t zstride = (size_t)P.Nout * P.t_pad;
-                for (int z0 = 0; z0 < P.splits; z0 += kZ) {
+                const size_t zstride = (size_t)J.Nout * P.t_pad;
+                for (int z0 = 0; z0 < J.splits; z0 += kZ) {
                     float4 v[2][kZ];
 #pragma unroll
                     for (int u = 0; u < kZ; ++u)
 #pragma unroll
                         for (int w = 0; w < 2; ++w)
-                            v[w][u] = z0 + u < P.splits
+                            v[w][u] = z0 + u < J.splits
                                           ? __ldcg(reinterpret_cast<const float4*>(src[w] + (size_t)(z0 + u) * zstride))
                                           : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
@@ -559,9 +574,9 @@ __global__ void __launch_bounds__(GemmCfg<MH, NH>::kThreads) gemm_stage_kernel(c
                         const int row = 4 * r4 + j;
                         if (row < P.T) {
                             const float v1 = fminf(fmaxf(o[j] * sc, -lim), lim);
-                            const size_t at = (size_t)row * P.ld_out + n0 + col;
-                            if (P.is_bf16) static_cast<__nv_bfloat16*>(P.out)[at] = __float2bfloat16(v1);
-                            else static_cast<__half*>(P.out)[at] = __float2half(v1);
+                            const size_t at = (size_t)row * J.ld_out + n0 + col;
+                            if (P.is_bf16) static_cast<__nv_bfloat16*>(J.out)[at] = __float2bfloat16(v1);
+                            else static_cast<__half*>(J.out)[at] = __float2half(v1);
                         }
                     }
                 }
@@ -602,13 +617,30 @@ static EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-// Tile shape and k split of one stage.
-struct StagePlan {
-    int mh, nh;            // tile: 128*mh tokens x 128*nh weight rows
-    int splits;            // CTAs per output tile along K (1 = no split)
-    int chunks_per;        // 256-column chunks per split
-    int t_pad;             // slab row length (tokens, multiple of 4)
-    int tiles_n;           // output tiles along Nout
+// One linear's stage as the host sees it.
+struct StageJob {
+    const void* a;          // activations [T, K], row stride lda elements
+    long long lda;
+    const void* tiles;
+    const void* pre;
+    const void* post;
+    void* out;
+    long long ld_out;
+    int K, Nout;
+};
+
+// Tile shape of a launch and the k split of each of its jobs.
+struct GroupPlan {
+    int mh, nh;                       // tile: 128*mh tokens x 128*nh weight rows
+    int t_pad;                        // slab row length (tokens, multiple of 4)
+    int tiles_total;                  // grid.x
+    int max_splits;                   // grid.z
+    int tile0[kMaxGemmJobs];          // first grid.x index of each job
+    int splits[kMaxGemmJobs];         // CTAs per output tile along K (1 = no split)
+    int chunks_per[kMaxGemmJobs];     // 256-column chunks per split
+    int counter0[kMaxGemmJobs];       // first tile counter of the job (index into the counter words)
+    size_t slab0[kMaxGemmJobs];       // first slab float of the job
+    size_t slab_floats;               // slab floats of the launch
 };
 constexpr size_t kMaxSlabBytes = (size_t)16 << 20;
 // The tile counters live in words 8..63 of the 256-byte scratch header, which no other kernel writes
@@ -618,88 +650,117 @@ constexpr int kMaxSplitTokens = 64;   // beyond that the serial slab reduction o
 
 // Tile shape (128*mh tokens x 128*nh weight rows) by a small cost model: a CTA needs a measured number of
 // cycles per 64-column step (bounded by the tensor pipe for the 256 x 256 tile, by the per-step waits and
-// MMA issue of the single issuing thread for the smaller ones); the grid runs in ceil(tiles/SMs) waves, each
-// with a fixed prologue/epilogue cost.  With at most 64 tokens and few output tiles the k dimension is
-// split over the idle SMs (whole 256-column chunks per CTA), as far as the slab budget allows.
-static StagePlan plan_stage(int T, int K, int Nout, bool allow_split) {
-    StagePlan pl;
+// MMA issue of the issuing threads for the smaller ones); the grid runs in ceil(tiles/SMs) waves, each
+// with a fixed prologue/epilogue cost.  With at most 64 tokens and few output tiles the k dimension of every
+// job is split over the idle SMs (whole 256-column chunks per CTA), as far as counters and slab budget allow.
+static GroupPlan plan_group(int T, int n, const int* K, const int* Nout, bool allow_split) {
+    GroupPlan pl;
+    memset(&pl, 0, sizeof(pl));
     pl.mh = 1; pl.nh = 1;
     static const int cand[4][2] = {{1, 1}, {2, 1}, {1, 2}, {2, 2}};
     // development aid: NQ_GEMM_FORCE_CFG=<mh><nh> (e.g. 12) pins the tile shape
     static const int forced = [] { const char* e = getenv("NQ_GEMM_FORCE_CFG"); return e ? atoi(e) : 0; }();
-    const long long sms = sm_count(), steps = (K + kBK - 1) / kBK;
+    const long long sms = sm_count();
+    long long steps = 0;
+    for (int j = 0; j < n; ++j) steps = steps > (K[j] + kBK - 1) / kBK ? steps : (K[j] + kBK - 1) / kBK;
     long long best = -1;
     for (const auto& c : cand) {
         if (forced && forced != 10 * c[0] + c[1]) continue;
         if (c[0] == 2 && T <= kBM && !forced) continue;
-        const long long tiles = (long long)((T + kBM * c[0] - 1) / (kBM * c[0])) * ((Nout + 128 * c[1] - 1) / (128 * c[1]));
+        long long tiles = 0;
+        for (int j = 0; j < n; ++j)
+            tiles += (long long)((T + kBM * c[0] - 1) / (kBM * c[0])) * ((Nout[j] + 128 * c[1] - 1) / (128 * c[1]));
         const long long waves = (tiles + sms - 1) / sms;
         // measured cycles of the MMA thread per 64-column step (wait + issue, tensor pipe busy)
         const long long per_step = c[0] * c[1] == 4 ? 990 : (c[0] == 2 ? 580 : (c[1] == 2 ? 830 : 485));
         const long long cost = waves * (steps * per_step + 6000 + 2000LL * c[0] * c[1]);
         if (best < 0 || cost < best) { best = cost; pl.mh = c[0]; pl.nh = c[1]; }
     }
-    pl.tiles_n = (Nout + 128 * pl.nh - 1) / (128 * pl.nh);
-    pl.splits = 1;
-    pl.chunks_per = (K + 255) / 256;
     pl.t_pad = (T + 3) / 4 * 4;
-    if (allow_split && T <= kMaxSplitTokens && pl.tiles_n <= kMaxSplitTiles) {
-        const int chunks = (K + 255) / 256;
-        long long want = sms / pl.tiles_n;
-        const long long by_mem = (long long)(kMaxSlabBytes / ((size_t)pl.t_pad * (size_t)Nout * sizeof(float)));
-        want = want < by_mem ? want : by_mem;
-        want = want < chunks ? want : chunks;
-        if (want >= 2) {
-            pl.chunks_per = (int)((chunks + want - 1) / want);
-            pl.splits = (chunks + pl.chunks_per - 1) / pl.chunks_per;
+    pl.max_splits = 1;
+    int tiles_n[kMaxGemmJobs];
+    for (int j = 0; j < n; ++j) {
+        tiles_n[j] = (Nout[j] + 128 * pl.nh - 1) / (128 * pl.nh);
+        pl.tile0[j] = pl.tiles_total;
+        pl.tiles_total += tiles_n[j];
+        pl.splits[j] = 1;
+        pl.chunks_per[j] = (K[j] + 255) / 256;
+    }
+    if (allow_split && T <= kMaxSplitTokens) {
+        long long want_all = sms / pl.tiles_total;   // CTAs per tile that the idle SMs allow
+        int counters_used = 0;
+        size_t slab_budget = kMaxSlabBytes / sizeof(float);
+        for (int j = 0; j < n && want_all >= 2; ++j) {
+            const int chunks = (K[j] + 255) / 256;
+            const size_t per_split = (size_t)pl.t_pad * (size_t)Nout[j];
+            long long want = want_all;
+            const long long by_mem = (long long)((slab_budget - pl.slab_floats) / per_split);
+            want = want < by_mem ? want : by_mem;
+            want = want < chunks ? want : chunks;
+            if (want < 2 || counters_used + tiles_n[j] > kMaxSplitTiles) continue;
+            pl.chunks_per[j] = (int)((chunks + want - 1) / want);
+            pl.splits[j] = (chunks + pl.chunks_per[j] - 1) / pl.chunks_per[j];
+            pl.counter0[j] = counters_used;
+            counters_used += tiles_n[j];
+            pl.slab0[j] = pl.slab_floats;
+            pl.slab_floats += (size_t)pl.splits[j] * per_split;
+            pl.max_splits = pl.max_splits > pl.splits[j] ? pl.max_splits : pl.splits[j];
         }
     }
     return pl;
 }
-// Slab bytes behind the intermediate in the GEMM scratch.
-static size_t slab_bytes(const StagePlan& pl, int Nout) {
-    return pl.splits > 1 ? (size_t)pl.splits * (size_t)Nout * (size_t)pl.t_pad * sizeof(float) : 0;
-}
 
-// One stage: out[T, Nout] = (a[T, K] . W^T) * post, W from `tiles` and `pre`.  `counters` (zero between
-// launches) and `slabs` may be nullptr: no k split.
-static int launch_stage(const void* a, long long lda, const void* tiles, const void* pre, const void* post,
-                        void* out, long long ld_out, int T, int K, int Nout, int dtype, int saturate,
-                        unsigned* status, unsigned* counters, float* slabs, cudaStream_t stream) {
-    if (!aligned16(a) || (lda % 8) != 0 || (K % 8) != 0) return NQ_ERR_ALIGN;   // TMA: 16-byte base and stride
-    if (pre && !aligned16(pre)) return NQ_ERR_ALIGN;
+// One stage of up to four linears: out_j[T, Nout_j] = (a_j[T, K_j] . W_j^T) * post_j.  `counters` (zero
+// between launches) and `slabs` may be nullptr: no k split.
+static int launch_stage(const StageJob* jobs, int n, int T, int dtype, int saturate, unsigned* status,
+                        unsigned* counters, float* slabs, cudaStream_t stream) {
+    if (n < 1 || n > kMaxGemmJobs) return NQ_ERR_UNSUPPORTED;
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return NQ_ERR_UNSUPPORTED;
-    GemmParams P;
-    memset(&P, 0, sizeof(P));
-    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)T};
-    const cuuint64_t strides[1] = {(cuuint64_t)lda * 2};
-    const StagePlan pl = plan_stage(T, K, Nout, counters != nullptr && slabs != nullptr);
+    int Ks[kMaxGemmJobs], Ns[kMaxGemmJobs];
+    for (int j = 0; j < n; ++j) {
+        const StageJob& S = jobs[j];
+        if (!aligned16(S.a) || (S.lda % 8) != 0 || (S.K % 8) != 0) return NQ_ERR_ALIGN;   // TMA: 16-byte base and stride
+        if (S.pre && !aligned16(S.pre)) return NQ_ERR_ALIGN;
+        Ks[j] = S.K; Ns[j] = S.Nout;
+    }
+    const GroupPlan pl = plan_group(T, n, Ks, Ns, counters != nullptr && slabs != nullptr);
     const int mh = pl.mh, nh = pl.nh;
     const int m_tiles = (T + kBM * mh - 1) / (kBM * mh);
-    const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)(kBM * mh)};
-    const cuuint32_t estr[2] = {1, 1};
-    const CUresult r = enc(&P.map_a, dtype == NQ_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
-                           2, const_cast<void*>(a), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return NQ_ERR_UNSUPPORTED;
-    P.tiles = static_cast<const uint4*>(tiles);
-    P.pre = pre;
-    P.post = post;
-    P.out = out;
-    P.ld_out = ld_out;
+    GemmParams P;
+    memset(&P, 0, sizeof(P));
+    P.njobs = n;
     P.status = status;
-    P.T = T; P.K = K; P.Nout = Nout;
-    P.chunks = (K + 255) / 256;
-    P.row_groups = (Nout + 15) / 16;
+    P.T = T;
+    P.t_pad = pl.t_pad;
     P.is_bf16 = dtype == NQ_BF16;
     P.saturate = saturate;
-    P.splits = pl.splits;
-    P.chunks_per = pl.chunks_per;
-    P.t_pad = pl.t_pad;
-    P.counters = counters;
-    P.slabs = slabs;
+    for (int j = 0; j < n; ++j) {
+        const StageJob& S = jobs[j];
+        GemmJob& J = P.job[j];
+        const cuuint64_t dims[2] = {(cuuint64_t)S.K, (cuuint64_t)T};
+        const cuuint64_t strides[1] = {(cuuint64_t)S.lda * 2};
+        const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)(kBM * mh)};
+        const cuuint32_t estr[2] = {1, 1};
+        const CUresult r = enc(&J.map_a, dtype == NQ_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                               2, const_cast<void*>(S.a), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return NQ_ERR_UNSUPPORTED;
+        J.tiles = static_cast<const uint4*>(S.tiles);
+        J.pre = S.pre;
+        J.post = S.post;
+        J.out = S.out;
+        J.ld_out = S.ld_out;
+        J.K = S.K; J.Nout = S.Nout;
+        J.chunks = (S.K + 255) / 256;
+        J.row_groups = (S.Nout + 15) / 16;
+        J.splits = pl.splits[j];
+        J.chunks_per = pl.chunks_per[j];
+        J.tile0 = pl.tile0[j];
+        J.counters = counters ? counters + pl.counter0[j] : nullptr;
+        J.slabs = slabs ? slabs + pl.slab0[j] : nullptr;
+    }
     static bool attr_set[64];
     int dev = 0;
     NQ_CUDA_TRY(cudaGetDevice(&dev));
@@ -727,7 +788,7 @@ static int launch_stage(const void* a, long long lda, const void* tiles, const v
     static bool pdl_ok = true;
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
-    cfg.gridDim = dim3((Nout + 128 * nh - 1) / (128 * nh), m_tiles, pl.splits);
+    cfg.gridDim = dim3(pl.tiles_total, m_tiles, pl.max_splits);
     cfg.blockDim = dim3(threads);
     cfg.dynamicSmemBytes = smem_bytes;
     cfg.stream = stream;
@@ -754,11 +815,34 @@ using namespace nq;
 
 extern "C" {
 
+// Scratch of a GEMM group: header (status word, tile counters), the intermediates t_j[T, R_j] (I/O dtype,
+// 256-byte aligned each), split-K slabs (shared by the two stages).
+static size_t gemm_group_layout(const nq_linear_desc* d, int n, int T, size_t* t_off, size_t* slab_off) {
+    size_t off = 256;
+    int K1[kMaxGemmJobs], N1[kMaxGemmJobs], K2[kMaxGemmJobs], N2[kMaxGemmJobs];
+    for (int j = 0; j < n; ++j) {
+        if (t_off) t_off[j] = off;
+        off += ((size_t)T * (size_t)d[j].R * 2 + 255) / 256 * 256;
+        K1[j] = d[j].N; N1[j] = d[j].R; K2[j] = d[j].R; N2[j] = d[j].M;
+    }
+    if (slab_off) *slab_off = off;
+    const size_t a = plan_group(T, n, K1, N1, true).slab_floats, b = plan_group(T, n, K2, N2, true).slab_floats;
+    return off + (a > b ? a : b) * sizeof(float);
+}
+
+size_t nq_gemm_group_scratch_bytes(const nq_linear_desc* d, int n_linears, int T) {
+    if (!d || n_linears <= 0 || n_linears > kMaxGemmJobs || T <= 0) return 0;
+    for (int j = 0; j < n_linears; ++j)
+        if (d[j].N <= 0 || d[j].R <= 0 || d[j].M <= 0) return 0;
+    return gemm_group_layout(d, n_linears, T, nullptr, nullptr);
+}
+
 size_t nq_gemm_scratch_bytes(int T, int N, int R, int M) {
     if (T <= 0 || N <= 0 || R <= 0 || M <= 0) return 0;
-    // header (status word, tile counters), intermediate t[T, R] (I/O dtype), split-K slabs (shared by the two stages)
-    const size_t a = slab_bytes(plan_stage(T, N, R, true), R), b = slab_bytes(plan_stage(T, R, M, true), M);
-    return 256 + ((size_t)T * (size_t)R * 2 + 255) / 256 * 256 + (a > b ? a : b);
+    nq_linear_desc d;
+    memset(&d, 0, sizeof(d));
+    d.N = N; d.R = R; d.M = M;
+    return gemm_group_layout(&d, 1, T, nullptr, nullptr);
 }
 
 int nq_onebit_gemm_fwd(const void* x, const void* tiles, const void* s_in, const void* s_out, void* y,
@@ -767,8 +851,42 @@ int nq_onebit_gemm_fwd(const void* x, const void* tiles, const void* s_in, const
     if (T <= 0 || K <= 0 || Nout <= 0) return NQ_ERR_SHAPE;
     if (dtype != NQ_F16 && dtype != NQ_BF16) return NQ_ERR_DTYPE;
     if (!aligned16(tiles)) return NQ_ERR_ALIGN;
-    return launch_stage(x, K, tiles, s_in, s_out, y, Nout, T, K, Nout, dtype, 1,
-                        static_cast<unsigned*>(status_word) + 2, nullptr, nullptr, as_stream(stream));
+    const StageJob job = {x, K, tiles, s_in, s_out, y, Nout, K, Nout};
+    return launch_stage(&job, 1, T, dtype, 1, static_cast<unsigned*>(status_word) + 2, nullptr, nullptr,
+                        as_stream(stream));
+}
+
+int nq_gemm_group_fwd(const nq_linear_desc* d, int n_linears, int T, int dtype, void* scratch,
+                      size_t scratch_bytes, nq_stream_t stream) {
+    if (!d || !scratch) return NQ_ERR_NULL;
+    if (n_linears <= 0 || n_linears > kMaxGemmJobs) return NQ_ERR_UNSUPPORTED;
+    if (T <= 0) return NQ_ERR_SHAPE;
+    if (dtype != NQ_F16 && dtype != NQ_BF16) return NQ_ERR_DTYPE;
+    if (!aligned16(scratch)) return NQ_ERR_ALIGN;
+    for (int j = 0; j < n_linears; ++j) {
+        const nq_linear_desc& L = d[j];
+        if (!L.x || !L.s_in || !L.v_tiles || !L.u_tiles || !L.s_out || !L.y) return NQ_ERR_NULL;
+        if (L.N <= 0 || L.R <= 0 || L.M <= 0 || L.ldx < L.N || L.ldy < L.M) return NQ_ERR_SHAPE;
+        if (L.N % 8 || L.R % 8) return NQ_ERR_SHAPE;
+        if (!aligned16(L.v_tiles) || !aligned16(L.u_tiles)) return NQ_ERR_ALIGN;
+    }
+    size_t t_off[kMaxGemmJobs], slab_off = 0;
+    if (scratch_bytes < gemm_group_layout(d, n_linears, T, t_off, &slab_off)) return NQ_ERR_SCRATCH;
+    unsigned* status = static_cast<unsigned*>(scratch) + 2;   // same word as the GEMV header's status
+    // Both stages use the same counters and slab space: a stage touches them only after the kernel before it
+    // has completed (its stores come behind the dependency wait).
+    unsigned* counters = static_cast<unsigned*>(scratch) + kCounterWord0;
+    float* slabs = reinterpret_cast<float*>(static_cast<char*>(scratch) + slab_off);
+    StageJob s1[kMaxGemmJobs], s2[kMaxGemmJobs];
+    for (int j = 0; j < n_linears; ++j) {
+        const nq_linear_desc& L = d[j];
+        void* t = static_cast<char*>(scratch) + t_off[j];
+        s1[j] = {L.x, L.ldx, L.v_tiles, L.s_in, L.s_mid, t, L.R, L.N, L.R};
+        s2[j] = {t, L.R, L.u_tiles, nullptr, L.s_out, L.y, L.ldy, L.R, L.M};
+    }
+    const int st = launch_stage(s1, n_linears, T, dtype, 0, status, counters, slabs, as_stream(stream));
+    if (st != NQ_OK) return st;
+    return launch_stage(s2, n_linears, T, dtype, 1, status, counters, slabs, as_stream(stream));
 }
 
 int nq_gemm_fwd(const void* x, const void* s_in, const void* v_tiles, const void* s_mid, const void* u_tiles,
@@ -776,19 +894,10 @@ int nq_gemm_fwd(const void* x, const void* s_in, const void* v_tiles, const void
                 int dtype, nq_stream_t stream) {
     if (!x || !s_in || !v_tiles || !u_tiles || !s_out || !y || !scratch) return NQ_ERR_NULL;
     if (T <= 0 || N <= 0 || R <= 0 || M <= 0) return NQ_ERR_SHAPE;
-    if (dtype != NQ_F16 && dtype != NQ_BF16) return NQ_ERR_DTYPE;
-    if (N % 8 || R % 8) return NQ_ERR_SHAPE;
-    if (!aligned16(scratch) || !aligned16(v_tiles) || !aligned16(u_tiles)) return NQ_ERR_ALIGN;
-    if (scratch_bytes < nq_gemm_scratch_bytes(T, N, R, M)) return NQ_ERR_SCRATCH;
-    unsigned* status = static_cast<unsigned*>(scratch) + 2;   // same word as the GEMV header's status
-    void* t = static_cast<char*>(scratch) + 256;
-    // Both stages use the same counters and slab space: a stage touches them only after the kernel before it
-    // has completed (its stores come behind the dependency wait).
-    unsigned* counters = static_cast<unsigned*>(scratch) + kCounterWord0;
-    float* slabs = reinterpret_cast<float*>(static_cast<char*>(t) + ((size_t)T * (size_t)R * 2 + 255) / 256 * 256);
-    int st = launch_stage(x, N, v_tiles, s_in, s_mid, t, R, T, N, R, dtype, 0, status, counters, slabs, as_stream(stream));
-    if (st != NQ_OK) return st;
-    return launch_stage(t, R, u_tiles, nullptr, s_out, y, M, T, R, M, dtype, 1, status, counters, slabs, as_stream(stream));
+    nq_linear_desc d;
+    d.x = x; d.s_in = s_in; d.v_tiles = v_tiles; d.s_mid = s_mid; d.u_tiles = u_tiles; d.s_out = s_out;
+    d.y = y; d.N = N; d.R = R; d.M = M; d.ldx = N; d.ldy = M;
+    return nq_gemm_group_fwd(&d, 1, T, dtype, scratch, scratch_bytes, stream);
 }
 
 #ifdef NQ_GEMM_TRACE

@@ -153,6 +153,50 @@ def test_c_abi_linear_few_tokens_ragged_split(shape, dtype):
     assert torch.equal(ys[0], ys[1]) and torch.equal(ys[1], ys[2])
 
 
+@pytest.mark.parametrize("T", [6, 16, 300])
+def test_c_abi_gemm_group_matches_single_linears(T):
+    # q/k/v-like group (shared input, different ranks and widths) in one launch per stage against the oracle and
+    # against the per-linear entry point; outputs written side by side into one buffer (ldy > M)
+    from nanoquant_b200 import _lib
+    from nanoquant_b200.kernel import utils as ku
+    Lb = _lib.lib()
+    N = 1024
+    shapes = [(N, 264, 1024), (N, 96, 256), (N, 96, 384)]
+    layers = [make_layer(n, r, m, T, torch.bfloat16, seed=10 + i) for i, (n, r, m) in enumerate(shapes)]
+    x = layers[0]["x"]
+    for L in layers[1:]:   # the same activations for the whole group: recompute the oracle on them
+        L["x"] = x
+        L["y64"] = oc.forward_fp64(exact_np(x), L["V"], L["U"], exact_np(L["s_pre"]), exact_np(L["s_mid"]), exact_np(L["s_post"]))
+    width = sum(m for (_, _, m) in shapes)
+    ybuf = torch.zeros(T, width, dtype=torch.bfloat16, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    keep, descs, col = [], [], 0
+    for L, (n, r, m) in zip(layers, shapes):
+        vt = ku.pack_tiles(half2_bits(L["V"]), (r, n), "half2")
+        ut = ku.pack_tiles(half2_bits(L["U"]), (m, r), "half2")
+        keep += [vt, ut]
+        descs.append(_lib.LinearDesc(x.data_ptr(), L["s_pre"].data_ptr(), vt.data_ptr(), L["s_mid"].data_ptr(), ut.data_ptr(),
+                                     L["s_post"].data_ptr(), ybuf.data_ptr() + 2 * col, n, r, m, n, width))
+        col += m
+    arr = (_lib.LinearDesc * len(descs))(*descs)
+    nbytes = Lb.nq_gemm_group_scratch_bytes(arr, len(descs), T)
+    scratch = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+    for _ in range(2):
+        _lib.check(Lb.nq_gemm_group_fwd(arr, len(descs), T, _lib.NQ_BF16, scratch.data_ptr(), nbytes, st), "group")
+    assert Lb.nq_scratch_status(scratch.data_ptr(), st) == 0
+    col = 0
+    for L, (n, r, m), d in zip(layers, shapes, descs):
+        y = ybuf[:, col:col + m]
+        assert oc.rel_err(exact_np(y), L["y64"]) <= TOL[torch.bfloat16]
+        y1 = torch.empty(T, m, dtype=torch.bfloat16, device="cuda")
+        nb1 = Lb.nq_gemm_scratch_bytes(T, n, r, m)
+        s1 = torch.zeros(nb1, dtype=torch.uint8, device="cuda")
+        _lib.check(Lb.nq_gemm_fwd(x.data_ptr(), d.s_in, d.v_tiles, d.s_mid, d.u_tiles, d.s_out, y1.data_ptr(),
+                                  s1.data_ptr(), nb1, T, n, r, m, _lib.NQ_BF16, st), "single")
+        assert oc.rel_err(exact_np(y), exact_np(y1)) <= 2.0 ** -7   # same products, possibly another k split
+        col += m
+
+
 def test_gemm_linearity_full_size(ops):
     # size-independent property at a full-size shape: the op is linear in x.  Doubling x doubles every
     # fp32 partial sum exactly; only intermediate values that fall into the fp16 subnormal range may
