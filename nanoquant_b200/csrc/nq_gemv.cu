@@ -28,9 +28,16 @@
 // Phases: phase 1 computes t[T,R] (fp32, in scratch), a device-wide barrier
 // follows, phase 2 computes y.  Several linears that share the two phases (q/k/v,
 // gate/up) are processed in one launch.  The weight stream of the next job is
-// started before the current job's epilogue and before the barrier, so the barrier
-// wait overlaps with HBM traffic.  The barrier spin is bounded: on expiry a status
-// word is set and every CTA returns.
+// started before the barrier, so the barrier wait overlaps with HBM traffic.  The
+// barrier is one arrival counter (see grid_barrier); its spin is bounded: on expiry
+// a status word is set and every CTA returns.  The kernel is launched cooperative
+// (all CTAs resident) and with programmatic stream serialization: everything that
+// does not depend on the previous kernel (descriptor copy, first weight loads, an L2
+// prefetch of the input scales) runs before griddepcontrol.wait.
+//
+// For 8B-class layers the kernel is a chain of dependent latencies (memory round
+// trips, CTA barriers, one device-wide barrier), not a bandwidth problem; the code
+// between the main loops is therefore kept short and free of divisions.
 //
 // replaces: src/nanoquant/kernel/cuda/gemv_kernel.cu:43-301 of the reference
 // (two kernels per linear, fp16/bf16 accumulation, sign-flip adds).
