@@ -345,7 +345,7 @@ def side_numbers(device, dtype):
                                    "kernel": step.kernel_name, "hbm_frac": step.bytes / (ms * 1e-3) / 1e9 / hbm_peak()[0]}
         del step
         torch.cuda.empty_cache()
-    tf, ms, _, _ = measure_prefill(2048, 4, 3, 3, device)
+    tf, ms, _, _, _ = measure_prefill(2048, 4, 3, 3, device)
     out["prefill_2048_tokens"] = {"value": tf, "unit": "TFLOP/s", "ms_per_step": ms,
                                   "frac_of_sustained_bf16_peak": tf / tensor_peak()[0]}
     return out
@@ -634,7 +634,7 @@ def tp_arm(args):
 # --------------------------------------------------------------------------------------------
 # prefill arm (--mode prefill): Llama-2-7B-shaped layer GEMMs at 1.0 bpw, T tokens per GEMM
 # --------------------------------------------------------------------------------------------
-def measure_prefill(T, layers, steps, warmup, device, profile=False, min_seconds=0.0):
+def measure_prefill(T, layers, steps, warmup, device, profile=False, min_seconds=0.0, e2e=False):
     """TFLOP/s of nq_gemm_fwd on the 7 linears of `layers` Llama-2-7B-shaped layers (hidden 4096, intermediate
     11008, ranks from the rank formula at 1.0 bpw), T tokens per GEMM.  Returns (TFLOP/s, ms per step, launches
     per step, clock record or None)."""
@@ -690,9 +690,33 @@ def measure_prefill(T, layers, steps, warmup, device, profile=False, min_seconds
         run()
         torch.cuda.synchronize(device)
     clocks = sampler.stop() if sampler else None
+    e2e_info = None
+    if e2e:   # the same step with the activations copied from pinned host memory and the last output read back
+        hx = {k: v.cpu().pin_memory() for k, v in xs.items()}
+        last_y = calls[-1][0]["y"]
+        hy = torch.empty_like(last_y, device="cpu").pin_memory()
+
+        def e2e_step():
+            for k in hx:
+                xs[k].copy_(hx[k], non_blocking=True)
+            run()
+            hy.copy_(last_y, non_blocking=True)
+            torch.cuda.current_stream(device).synchronize()
+        for _ in range(2):
+            e2e_step()
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        f0.record()
+        for _ in range(steps):
+            e2e_step()
+        f1.record()
+        torch.cuda.synchronize(device)
+        e2e_ms = f0.elapsed_time(f1) / steps
+        e2e_info = {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                    "h2d_bytes_per_step": sum(v.numel() * v.element_size() for v in hx.values()),
+                    "d2h_bytes_per_step": hy.numel() * hy.element_size()}
     if L.nq_scratch_status(scratch.data_ptr(), st) != 0:
         raise SystemExit("bench.py: a device-side wait timed out inside the GEMM kernel")
-    return flops / (ms * 1e-3) / 1e12, ms, 2 * len(calls), clocks
+    return flops / (ms * 1e-3) / 1e12, ms, 2 * len(calls), clocks, e2e_info
 
 
 def prefill_arm(args):
@@ -702,7 +726,8 @@ def prefill_arm(args):
     torch.cuda.set_device(device)
     T = args.tokens
     layers = args.layers if args.layers != LAYERS else 4
-    tf, ms, launches, clocks = measure_prefill(T, layers, args.steps, args.warmup, device, profile=True, min_seconds=1.0)
+    tf, ms, launches, clocks, e2e = measure_prefill(T, layers, args.steps, args.warmup, device, profile=True,
+                                                    min_seconds=1.0, e2e=True)
     peak, peak_src = tensor_peak()
     print(json.dumps({
         "mode": "prefill", "metric": "prefill TFLOP/s (quantised linears, 2*T*R*(N+M) flops)", "value": tf,
@@ -713,6 +738,7 @@ def prefill_arm(args):
                    "tokens": T},
         "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak,
                      "traffic": None, "kernel": "gemm_stage_kernel", "peak_source": peak_src},
+        "e2e": e2e,
         "tokens_per_s": T / (ms * 1e-3),   # T tokens through the GEMMs of `layers` layers per step
         "gpu_launches": launches * args.steps, "clocks": clocks}), flush=True)
 
