@@ -144,11 +144,13 @@ size_t nq_gemv_group_scratch_bytes(const nq_linear_desc* linears_host, int n_lin
 /* The decode GEMV.  Accumulation is exact integer arithmetic on a 16-bit
  * fixed-point image of (s_in * x) and of the rank-R intermediate (per-token
  * scale), results are converted once per output in fp32.  `scratch` holds a
- * 256-byte header (device-wide barrier state + status word) followed by the
- * fp32 intermediate; it must be 16-byte aligned, at least
- * nq_gemv_scratch_bytes() long and ZEROED ONCE by the caller after allocation
- * (the kernel leaves the header reusable).  Calls that share a scratch buffer
- * must be ordered on one stream.  T > 4 is processed as several launches.
+ * 256-byte header (a free-running launch counter + status word) followed by
+ * the fp32 intermediate, each element stored with the tag of the launch that
+ * wrote it (8 bytes per element); it must be 16-byte aligned, at least
+ * nq_gemv_scratch_bytes() long and ZEROED ONCE, AS A WHOLE, by the caller after
+ * allocation (never the header alone: the tags of the elements refer to the
+ * counter).  Calls that share a scratch buffer must be ordered on one stream.
+ * T > 4 is processed as several launches.
  * fp16 outputs saturate at +-64504, bf16 at +-3.3895e38 like the reference.
  * replaces: nanoquant_dyn_forward, src/nanoquant/kernel/cuda/gemv_kernel.cu:308-429
  * (schema src/nanoquant/kernel/pybind.cpp:85-90) */
@@ -170,14 +172,16 @@ int nq_gemv_group_fwd(const nq_linear_desc* linears_host, int n_linears, int T, 
  * beyond inputs and outputs: code running where allocation is forbidden or already frozen
  * (inside a serving loop whose memory plan is fixed, a plugin host that owns the allocator,
  * a capture-only phase).  It has NO counterpart in the reference.  The intermediate and the
- * barrier words live in a fixed array inside the library image (about 128 KB, present on
+ * launch counter live in a fixed array inside the library image (about 256 KB, present on
  * every GPU that loads the library until the process exits); nothing is allocated or freed,
  * here or in any library it calls.  Limits: rank R <= nq_gemv_static_max_rank() (8192),
  * otherwise NQ_ERR_TOO_LARGE; T > 4 runs as several launches like nq_gemv_fwd.
  * The first call on a device looks the array's device address up (cudaGetSymbolAddress);
- * make that first call outside any stream capture.  Every call clears the barrier / status
- * words on `stream` first and then reuses the same array, so two calls that can overlap on
- * the GPU (different streams, or threads, without ordering) race on it: order them. */
+ * make that first call outside any stream capture.  Nothing has to start at zero between
+ * calls (the array is zero when the library is loaded; every launch tags its intermediate
+ * with a fresh value of the counter), but every call reuses the same array, so two calls
+ * that can overlap on the GPU (different streams, or threads, without ordering) race on
+ * it: order them. */
 int nq_gemv_fwd_static(const void* x, const void* s_in, const void* v_tiles, const void* s_mid,
                        const void* u_tiles, const void* s_out, void* y,
                        int T, int N, int R, int M, int dtype, nq_stream_t stream);

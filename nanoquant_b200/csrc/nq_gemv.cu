@@ -69,7 +69,8 @@ constexpr size_t kRingBytes = (size_t)kGemvWarps * kStages * 1024;
 constexpr unsigned kSpinLimit = 4000000u;
 constexpr size_t kHeaderBytes = 256;
 
-enum : int { KIND_F16 = 0, KIND_BF16 = 1, KIND_F32 = 2 };
+// KIND_T: the rank-R intermediate between the phases, one 8-byte {fp32 value, launch tag} pair per element
+enum : int { KIND_F16 = 0, KIND_BF16 = 1, KIND_T = 2 };
 
 #ifdef NQ_GEMV_TRACE  // development aid: per-CTA (id, timestamp) records of the phase steps
 __device__ unsigned long long g_trace[148 * 64];
@@ -113,7 +114,7 @@ struct Phase {
 
 struct GemvParams {
     Phase phase[2];
-    unsigned* header;     // [0] barrier arrival counter, [1] unused, [2] status
+    unsigned* header;     // [0..1] 64-bit arrival counter (launch tags), [2] status
     int T;
     int scale_kind;       // dtype of the scale vectors (KIND_F16 / KIND_BF16)
     int xq_stride;        // bytes between the int8 vectors in shared memory
@@ -123,7 +124,7 @@ struct GemvParams {
 __device__ __forceinline__ float load_as_float(const void* p, long long i, int kind) {
     if (kind == KIND_F16) return __half2float(static_cast<const __half*>(p)[i]);
     if (kind == KIND_BF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
-    return __ldcg(static_cast<const float*>(p) + i);  // written by other CTAs of this launch: bypass L1
+    return 0.f;   // the tagged intermediate goes through load1_tagged / load8_tagged
 }
 
 __device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -133,51 +134,83 @@ __device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, ui
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// Bounded device-wide barrier on one arrival counter.  Returns false when the wait expired (a status
-// word is set and the caller returns).  Every launch advances the counter by exactly kBarrierSpan (a power
-// of two): CTA 0 adds kBarrierSpan - (nblocks - 1), every other CTA adds 1, so the bits above the span
-// count launches, they change at the moment the last CTA arrives, and 32-bit wrap-around is harmless.
-// Arrival is a release reduction without a return value and the waiters poll the counter itself: the last
-// arrival reaches them in one hop.  `base` is the launch count thread 0 read (barrier_base) after the
-// previous launch on this counter completed and before its own arrival; fewer than a span's worth of
-// arrivals can precede that read, so the upper bits are still those of the launch start.  Reading it
-// early keeps a memory round trip off the critical path.  One thread per CTA arrives and polls; the CTA
-// barrier before and after extends the ordering to every thread of the CTA.
-constexpr unsigned kBarrierSpan = 1u << 16;
-__device__ __forceinline__ unsigned barrier_base(const unsigned* header) {
-    unsigned c;
-    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(c) : "l"(header) : "memory");
-    return c & ~(kBarrierSpan - 1);
+// Hand-over of the rank-R intermediate between the phases WITHOUT a device-wide barrier: the data carries
+// its own flag.  Phase 1 stores every element of t as an 8-byte {fp32 value, tag} pair with one 64-bit
+// store; phase 2 loads the pairs it needs and repeats the load until every tag equals the tag of this
+// launch.  The first poll after the last producer store has landed already returns the data, which takes
+// an arrive / poll / reload sequence (three memory round trips) off the critical path.
+//
+// The tag is the launch count of the scratch buffer, read from a 64-bit arrival counter: every launch
+// advances it by exactly kTagSpan (CTA 0 adds kTagSpan - (nblocks - 1), every other CTA adds 1, with a
+// reduction nobody waits for), so the bits above the span are the same for every CTA of a launch whenever
+// it reads them (fewer than a span's worth of arrivals can precede the read) and differ from those of every
+// recent launch.  The tag is 0x7FF in its upper 12 bits (a NaN pattern as fp32 and in both halves as fp16 /
+// bf16 pairs, which no other kernel that shares the scratch ever stores, and never the 0 of a zeroed scratch)
+// and the launch count modulo 2^20 below; an element is rewritten by every launch whose rank exceeds its
+// index, so a stale tag can only match after 2^20 launches in a row with smaller ranks on the same scratch.
+// The wait is bounded: on expiry a status word is set and the thread goes on with what it has (the host
+// reports the status).
+constexpr unsigned kTagSpan = 1024u;   // > CTAs per launch
+struct TagCtx {
+    unsigned tag;        // tag of this launch
+    unsigned* status;    // device status word
+};
+__device__ __forceinline__ unsigned launch_tag(const unsigned long long* counter) {
+    unsigned long long c;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(c) : "l"(counter) : "memory");
+    return 0x7FF00000u | ((unsigned)(c / kTagSpan) & 0xFFFFFu);
 }
-__device__ bool grid_barrier(unsigned* header, unsigned nblocks, unsigned base) {
-    __shared__ int ok;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        ok = 1;
-        const unsigned w = blockIdx.x == 0 ? kBarrierSpan - (nblocks - 1) : 1u;
-        asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(header), "r"(w) : "memory");
-        unsigned spins = 0, cur;
-        while (true) {
-            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(cur) : "l"(header) : "memory");
-            if ((cur & ~(kBarrierSpan - 1)) != base) break;
-            if (++spins > kSpinLimit) {
-                atomicExch(header + 2, (unsigned)(-NQ_ERR_TIMEOUT));
-                ok = 0;
-                break;
-            }
+// This CTA's arrival at the counter.  Issued by one thread, once per launch, after a CTA barrier that every
+// thread passes behind its own launch_tag() read: the arrival that completes the span would otherwise show
+// the next launch's tag to a thread of the same CTA that reads late.
+__device__ __forceinline__ void launch_arrive(unsigned long long* counter, unsigned nblocks) {
+    const unsigned long long w = blockIdx.x == 0 ? (unsigned long long)(kTagSpan - (nblocks - 1)) : 1ull;
+    asm volatile("red.relaxed.gpu.global.add.u64 [%0], %1;" ::"l"(counter), "l"(w) : "memory");
+}
+// Eight tagged elements (64 bytes) as floats, polled until all eight carry this launch's tag.
+__device__ __forceinline__ void load8_tagged(const void* base, long long i, float (&v)[8], const TagCtx& tc) {
+    const uint4* p = reinterpret_cast<const uint4*>(static_cast<const uint2*>(base) + i);
+    uint4 q[4];
+    for (unsigned spins = 0;; ++spins) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+            asm volatile("ld.relaxed.gpu.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(q[k].x), "=r"(q[k].y), "=r"(q[k].z), "=r"(q[k].w) : "l"(p + k) : "memory");
+        bool ok = true;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) ok = ok && q[k].y == tc.tag && q[k].w == tc.tag;
+        if (ok) break;
+        if (spins > kSpinLimit) {
+            atomicExch(tc.status, (unsigned)(-NQ_ERR_TIMEOUT));
+            break;
         }
     }
-    __syncthreads();
-    return ok != 0;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) { v[2 * k] = __uint_as_float(q[k].x); v[2 * k + 1] = __uint_as_float(q[k].z); }
+}
+__device__ __forceinline__ float load1_tagged(const void* base, long long i, const TagCtx& tc) {
+    const uint2* p = static_cast<const uint2*>(base) + i;
+    uint2 q;
+    for (unsigned spins = 0;; ++spins) {
+        asm volatile("ld.relaxed.gpu.global.v2.u32 {%0,%1}, [%2];" : "=r"(q.x), "=r"(q.y) : "l"(p) : "memory");
+        if (q.y == tc.tag) break;
+        if (spins > kSpinLimit) {
+            atomicExch(tc.status, (unsigned)(-NQ_ERR_TIMEOUT));
+            break;
+        }
+    }
+    return __uint_as_float(q.x);
+}
+__device__ __forceinline__ void store_tagged(void* base, long long i, float val, unsigned tag) {
+    asm volatile("st.relaxed.gpu.global.v2.u32 [%0], {%1,%2};"
+                 ::"l"(static_cast<uint2*>(base) + i), "r"(__float_as_uint(val)), "r"(tag) : "memory");
 }
 
 // Eight consecutive elements of a vector as floats (one or two 128-bit loads).
 template <int KIND>
-__device__ __forceinline__ void load8(const void* base, long long i, float (&v)[8]) {
-    if (KIND == KIND_F32) {
-        const float4 a = __ldcg(reinterpret_cast<const float4*>(static_cast<const float*>(base) + i));
-        const float4 b = __ldcg(reinterpret_cast<const float4*>(static_cast<const float*>(base) + i) + 1);
-        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+__device__ __forceinline__ void load8(const void* base, long long i, float (&v)[8], const TagCtx& tc) {
+    if (KIND == KIND_T) {
+        load8_tagged(base, i, v, tc);
     } else {
         const uint4 u = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(base) + i);
         const uint32_t w[4] = {u.x, u.y, u.z, u.w};
@@ -199,18 +232,19 @@ __device__ __forceinline__ void load8(const void* base, long long i, float (&v)[
 template <int KIND>
 struct Raw8 { uint4 a, b; };   // b: second half of an fp32 block
 template <int KIND>
-__device__ __forceinline__ void load_raw(const void* base, long long i, Raw8<KIND>& r) {
-    if (KIND == KIND_F32) {
-        const uint4* p = reinterpret_cast<const uint4*>(static_cast<const float*>(base) + i);
-        r.a = __ldcg(p);
-        r.b = __ldcg(p + 1);
+__device__ __forceinline__ void load_raw(const void* base, long long i, Raw8<KIND>& r, const TagCtx& tc) {
+    if (KIND == KIND_T) {   // tagged pairs are polled until valid; the block keeps the eight values
+        float v[8];
+        load8_tagged(base, i, v, tc);
+        r.a = make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]), __float_as_uint(v[2]), __float_as_uint(v[3]));
+        r.b = make_uint4(__float_as_uint(v[4]), __float_as_uint(v[5]), __float_as_uint(v[6]), __float_as_uint(v[7]));
     } else {
         r.a = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(base) + i);
     }
 }
 template <int KIND>
 __device__ __forceinline__ void to_float8(const Raw8<KIND>& r, float (&v)[8]) {
-    if (KIND == KIND_F32) {
+    if (KIND == KIND_T) {
         v[0] = __uint_as_float(r.a.x); v[1] = __uint_as_float(r.a.y); v[2] = __uint_as_float(r.a.z); v[3] = __uint_as_float(r.a.w);
         v[4] = __uint_as_float(r.b.x); v[5] = __uint_as_float(r.b.y); v[6] = __uint_as_float(r.b.z); v[7] = __uint_as_float(r.b.w);
     } else {
@@ -295,10 +329,10 @@ __device__ __forceinline__ void store_terms(const uint32_t (&Y)[8], int8_t* r0, 
 // Vector path: rows of `in` / `pre` 16-byte aligned, K % 8 == 0; eight columns per thread and step.
 template <int IN_KIND>
 __device__ __noinline__ void quantise_vec(const Job& jb, int T, int8_t* xq, int stride, float* red,
-                                          int* sumx, float* delta) {
+                                          int* sumx, float* delta, const TagCtx& tc) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int K = jb.K, Kpad = jb.chunks * 256;
-    constexpr bool kHasPre = (IN_KIND != KIND_F32);
+    constexpr bool kHasPre = (IN_KIND != KIND_T);
     constexpr int kBatch = 4;                       // blocks whose loads are issued before the first use:
     constexpr int kStep = kGemvThreads * 8;         // one memory round trip per batch instead of one per block
     // pass 1: per-token max |in * pre|
@@ -314,8 +348,8 @@ __device__ __noinline__ void quantise_vec(const Job& jb, int T, int8_t* xq, int 
                 x[u].a = x[u].b = make_uint4(0u, 0u, 0u, 0u);     // a zero block does not move the maximum
                 sc[u].a = sc[u].b = make_uint4(0u, 0u, 0u, 0u);
                 if (k8 < K) {
-                    load_raw<IN_KIND>(jb.in, t * jb.ld_in + k8, x[u]);
-                    if (kHasPre) load_raw<IN_KIND>(jb.pre, k8, sc[u]);
+                    load_raw<IN_KIND>(jb.in, t * jb.ld_in + k8, x[u], tc);
+                    if (kHasPre) load_raw<IN_KIND>(jb.pre, k8, sc[u], tc);
                 }
             }
 #pragma unroll
@@ -347,8 +381,8 @@ __device__ __noinline__ void quantise_vec(const Job& jb, int T, int8_t* xq, int 
                 x[u].a = x[u].b = make_uint4(0u, 0u, 0u, 0u);     // columns K..Kpad quantise to zero
                 sc[u].a = sc[u].b = make_uint4(0u, 0u, 0u, 0u);
                 if (k8 < K) {
-                    load_raw<IN_KIND>(jb.in, t * jb.ld_in + k8, x[u]);
-                    if (kHasPre) load_raw<IN_KIND>(jb.pre, k8, sc[u]);
+                    load_raw<IN_KIND>(jb.in, t * jb.ld_in + k8, x[u], tc);
+                    if (kHasPre) load_raw<IN_KIND>(jb.pre, k8, sc[u], tc);
                 }
             }
 #pragma unroll
@@ -381,20 +415,20 @@ __device__ __noinline__ void quantise_vec(const Job& jb, int T, int8_t* xq, int 
 // the phase pays a single memory round trip for its input.  Kpad / 8 is a multiple of 32: a warp serves one token.
 template <int IN_KIND>
 __device__ __noinline__ void quantise_one(const Job& jb, int T, int8_t* xq, int stride, float* red,
-                                          int* sumx, float* delta) {
+                                          int* sumx, float* delta, const TagCtx& tc) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int K = jb.K, nv8 = jb.chunks * 32;
-    constexpr bool kHasPre = (IN_KIND != KIND_F32);
+    constexpr bool kHasPre = (IN_KIND != KIND_T);
     const int t = tid / nv8, k8 = (tid - t * nv8) * 8;
     const bool active = t < T;
     float p[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) p[e] = 0.f;
     if (active && k8 < K) {
-        load8<IN_KIND>(jb.in, t * jb.ld_in + k8, p);
+        load8<IN_KIND>(jb.in, t * jb.ld_in + k8, p, tc);
         if (kHasPre) {
             float s[8];
-            load8<IN_KIND>(jb.pre, k8, s);
+            load8<IN_KIND>(jb.pre, k8, s, tc);
 #pragma unroll
             for (int e = 0; e < 8; ++e) p[e] *= s[e];
         }
@@ -430,7 +464,7 @@ __device__ __noinline__ void quantise_one(const Job& jb, int T, int8_t* xq, int 
 
 // Scalar path for unaligned or ragged inputs (any K, any alignment).
 __device__ __noinline__ void quantise_scalar(const Job& jb, int T, int scale_kind, int8_t* xq, int stride,
-                                             float* red, int* sumx, float* delta) {
+                                             float* red, int* sumx, float* delta, const TagCtx& tc) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int K = jb.K, Kpad = jb.chunks * 256;
 #pragma unroll 1
@@ -438,7 +472,7 @@ __device__ __noinline__ void quantise_scalar(const Job& jb, int T, int scale_kin
         float m = 0.f;
         for (int k = tid; k < K; k += kGemvThreads) {
             const float s = jb.pre ? load_as_float(jb.pre, k, scale_kind) : 1.f;
-            m = fmaxf(m, fabsf(load_as_float(jb.in, t * jb.ld_in + k, jb.in_kind) * s));
+            m = fmaxf(m, fabsf((jb.in_kind == KIND_T ? load1_tagged(jb.in, t * jb.ld_in + k, tc) : load_as_float(jb.in, t * jb.ld_in + k, jb.in_kind)) * s));
         }
         m = warp_max_abs(m);
         if (lane == 0) red[t * kGemvWarps + warp] = m;
@@ -453,7 +487,7 @@ __device__ __noinline__ void quantise_scalar(const Job& jb, int T, int scale_kin
             int X = 0;
             if (k < K) {
                 const float s = jb.pre ? load_as_float(jb.pre, k, scale_kind) : 1.f;
-                X = __float2int_rn(load_as_float(jb.in, t * jb.ld_in + k, jb.in_kind) * s * inv);
+                X = __float2int_rn((jb.in_kind == KIND_T ? load1_tagged(jb.in, t * jb.ld_in + k, tc) : load_as_float(jb.in, t * jb.ld_in + k, jb.in_kind)) * s * inv);
             }
             acc += X;
             const int y = class_shift(X, (k >> 5) & 7);
@@ -469,16 +503,16 @@ __device__ __noinline__ void quantise_scalar(const Job& jb, int T, int scale_kin
 }
 
 __device__ __forceinline__ void quantise_input(const Job& jb, int T, int scale_kind, int8_t* xq, int stride,
-                                               float* red, int* sumx, float* delta) {
-    if (!jb.vec) quantise_scalar(jb, T, scale_kind, xq, stride, red, sumx, delta);
+                                               float* red, int* sumx, float* delta, const TagCtx& tc) {
+    if (!jb.vec) quantise_scalar(jb, T, scale_kind, xq, stride, red, sumx, delta, tc);
     else if (T * jb.chunks * 32 <= kGemvThreads) {
-        if (jb.in_kind == KIND_F32) quantise_one<KIND_F32>(jb, T, xq, stride, red, sumx, delta);
-        else if (jb.in_kind == KIND_F16) quantise_one<KIND_F16>(jb, T, xq, stride, red, sumx, delta);
-        else quantise_one<KIND_BF16>(jb, T, xq, stride, red, sumx, delta);
+        if (jb.in_kind == KIND_T) quantise_one<KIND_T>(jb, T, xq, stride, red, sumx, delta, tc);
+        else if (jb.in_kind == KIND_F16) quantise_one<KIND_F16>(jb, T, xq, stride, red, sumx, delta, tc);
+        else quantise_one<KIND_BF16>(jb, T, xq, stride, red, sumx, delta, tc);
     }
-    else if (jb.in_kind == KIND_F32) quantise_vec<KIND_F32>(jb, T, xq, stride, red, sumx, delta);
-    else if (jb.in_kind == KIND_F16) quantise_vec<KIND_F16>(jb, T, xq, stride, red, sumx, delta);
-    else quantise_vec<KIND_BF16>(jb, T, xq, stride, red, sumx, delta);
+    else if (jb.in_kind == KIND_T) quantise_vec<KIND_T>(jb, T, xq, stride, red, sumx, delta, tc);
+    else if (jb.in_kind == KIND_F16) quantise_vec<KIND_F16>(jb, T, xq, stride, red, sumx, delta, tc);
+    else quantise_vec<KIND_BF16>(jb, T, xq, stride, red, sumx, delta, tc);
 }
 
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
@@ -600,16 +634,20 @@ __device__ __forceinline__ bool run_all(const Phase* phases, const GemvParams& P
     // with the tail of the previous kernel in the stream; the activations and the scratch (shared with
     // that kernel) are only touched after it has completed.  No-ops without the launch attribute.
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const unsigned bar_base = tid == 0 ? barrier_base(P.header) : 0u;
+    // tag of this launch for the intermediate's {value, tag} pairs (and this CTA's arrival, which nobody waits for)
+    TagCtx tc;
+    tc.tag = launch_tag(reinterpret_cast<const unsigned long long*>(P.header));
+    tc.status = P.header + 2;
+    bool arrived = false;
     NQ_TRACE(1);
 #pragma unroll 1
     while (true) {
-        if (!barrier_done && s >= njobs) {    // everything of phase 1 is written: publish, then read t
+        if (!barrier_done && s >= njobs) {    // this CTA's share of phase 1 is on its way
             NQ_TRACE(8);
-            if (!grid_barrier(P.header, gridDim.x, bar_base)) return false;
             barrier_done = true;
-            // Every CTA of this grid is resident now, so CTAs of the next kernel that start early cannot
-            // keep one of ours from being scheduled: let the next kernel begin its prologue.
+            // No device-wide barrier: phase 2 polls the tagged intermediate itself (load8_tagged).  All CTAs of
+            // this cooperative grid are resident, so CTAs of the next kernel that start early cannot keep one of
+            // ours from being scheduled: let the next kernel begin its prologue.
             asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
             NQ_TRACE(9);
         }
@@ -617,7 +655,11 @@ __device__ __forceinline__ bool run_all(const Phase* phases, const GemvParams& P
         const Job& jb = job_of(s);
         const int chunks = jb.chunks;
         for (int i = tid; i < st.my_items * (32 * kCols); i += kGemvThreads) s1[i] = 0;
-        quantise_input(jb, P.T, P.scale_kind, xq, P.xq_stride, red, sumx, delta);
+        quantise_input(jb, P.T, P.scale_kind, xq, P.xq_stride, red, sumx, delta, tc);
+        if (!arrived) {   // behind the CTA barriers of the quantiser
+            if (tid == 0) launch_arrive(reinterpret_cast<unsigned long long*>(P.header), gridDim.x);
+            arrived = true;
+        }
         NQ_TRACE(5);
 
         // MMA column n = 8*cg + g reads int8 vector n (= 3*tok + term); unused columns re-read a valid one
@@ -690,8 +732,8 @@ __device__ __forceinline__ bool run_all(const Phase* phases, const GemvParams& P
                     float val = (float)(sx - (terms >> 6)) * dl;
                     if (jb.post) val *= jb.post_vec ? load_as_float(my_post, idx, P.scale_kind)
                                                     : load_as_float(jb.post, row, P.scale_kind);
-                    if (jb.out_kind == KIND_F32) {
-                        static_cast<float*>(jb.out)[tok * jb.ld_out + row] = val;
+                    if (jb.out_kind == KIND_T) {
+                        store_tagged(jb.out, tok * jb.ld_out + row, val, tc.tag);
                     } else if (jb.out_kind == KIND_F16) {
                         // same saturation bounds as the reference epilogue
                         val = fminf(fmaxf(val, -64504.0f), 64504.0f);
@@ -711,6 +753,10 @@ __device__ __forceinline__ bool run_all(const Phase* phases, const GemvParams& P
         __syncthreads();  // xq / s1 are reused by the next job
         NQ_TRACE(7);
         s = s_next;
+    }
+    if (!arrived) {   // a CTA without row tiles in either phase still counts towards the launch
+        __syncthreads();
+        if (tid == 0) launch_arrive(reinterpret_cast<unsigned long long*>(P.header), gridDim.x);
     }
     return true;
 }
@@ -761,9 +807,9 @@ static int dynamic_smem_limit(int dev, int* out) {
 // GEMV without caller-provided scratch
 // ---------------------------------------------------------------------------
 // Scratch of nq_gemv_fwd_static: lives in the library image on every GPU that loads it, until
-// the process exits.  256-byte header + fp32 intermediate for up to 4 tokens x rank 8192.
+// the process exits.  256-byte header + tagged fp32 intermediate (8 bytes per element) for up to 4 tokens x rank 8192.
 constexpr int kStaticMaxRank = 8192;
-constexpr size_t kStaticScratchBytes = kHeaderBytes + (size_t)kMaxTok * kStaticMaxRank * sizeof(float);
+constexpr size_t kStaticScratchBytes = kHeaderBytes + (size_t)kMaxTok * kStaticMaxRank * sizeof(uint2);
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 // Device address of g_static_scratch on the current device.  In host code the symbol name is
@@ -792,7 +838,7 @@ extern "C" {
 
 size_t nq_gemv_scratch_bytes(int T, int N, int R, int M) {
     if (T <= 0 || N <= 0 || R <= 0 || M <= 0) return 0;
-    return kHeaderBytes + round_up((size_t)kMaxTok * (size_t)R * sizeof(float), 256);
+    return kHeaderBytes + round_up((size_t)kMaxTok * (size_t)R * sizeof(uint2), 256);
 }
 
 size_t nq_gemv_group_scratch_bytes(const nq_linear_desc* d, int n_linears, int T) {
@@ -800,7 +846,7 @@ size_t nq_gemv_group_scratch_bytes(const nq_linear_desc* d, int n_linears, int T
     size_t b = kHeaderBytes;
     for (int i = 0; i < n_linears; ++i) {
         if (d[i].R <= 0) return 0;
-        b += round_up((size_t)kMaxTok * (size_t)d[i].R * sizeof(float), 256);
+        b += round_up((size_t)kMaxTok * (size_t)d[i].R * sizeof(uint2), 256);
     }
     return b;
 }
@@ -867,8 +913,8 @@ int nq_gemv_group_fwd(const nq_linear_desc* d, int n_linears, int T, int dtype, 
         int tiles_a = 0, tiles_b = 0;   // running tile counts of the two phases
         for (int i = 0; i < n_linears; ++i) {
             const nq_linear_desc& L = d[i];
-            float* tbuf = reinterpret_cast<float*>(static_cast<char*>(scratch) + off);
-            off += round_up((size_t)kMaxTok * (size_t)L.R * sizeof(float), 256);
+            void* tbuf = static_cast<char*>(scratch) + off;   // {fp32, tag} pairs, 8 bytes per element
+            off += round_up((size_t)kMaxTok * (size_t)L.R * sizeof(uint2), 256);
             Job& a = P.phase[0].job[i];
             a.tiles = static_cast<const uint4*>(L.v_tiles);
             a.in = static_cast<const char*>(L.x) + (size_t)t0 * L.ldx * esz;
@@ -882,7 +928,7 @@ int nq_gemv_group_fwd(const nq_linear_desc* d, int n_linears, int T, int dtype, 
             a.chunks = (L.N + 255) / 256;
             a.items = (L.R + 31) / 32;
             a.in_kind = dtype;
-            a.out_kind = KIND_F32;
+            a.out_kind = KIND_T;
             a.vec = (L.N % 8 == 0) && (L.ldx % 8 == 0) && aligned16(a.in) && aligned16(L.s_in);
             a.post_vec = L.s_mid && (L.R % 8 == 0) && aligned16(L.s_mid);
             a.tile_start = tiles_a;
@@ -899,7 +945,7 @@ int nq_gemv_group_fwd(const nq_linear_desc* d, int n_linears, int T, int dtype, 
             b.K = L.R;
             b.chunks = (L.R + 255) / 256;
             b.items = (L.M + 31) / 32;
-            b.in_kind = KIND_F32;
+            b.in_kind = KIND_T;
             b.out_kind = dtype;
             b.vec = (L.R % 8 == 0);  // the intermediate lives in the 256-byte aligned scratch
             b.post_vec = (L.M % 8 == 0) && aligned16(L.s_out);
@@ -960,8 +1006,9 @@ int nq_gemv_fwd_static(const void* x, const void* s_in, const void* v_tiles, con
     void* scratch = nullptr;
     const int st = static_scratch_ptr(&scratch);   // first call on a device: symbol lookup
     if (st != NQ_OK) return st;
-    // the array keeps whatever the previous call left: the barrier / status words must start at zero
-    NQ_CUDA_TRY(cudaMemsetAsync(scratch, 0, 16, as_stream(stream)));
+    // Nothing has to be cleared between calls: the array is zero when the library is loaded, the arrival
+    // counter in its header runs freely (every launch derives a fresh tag from it) and stale intermediate
+    // elements carry older tags.
     return nq_gemv_fwd(x, s_in, v_tiles, s_mid, u_tiles, s_out, y, scratch, kStaticScratchBytes, T, N, R, M, dtype,
                        stream);
 }
