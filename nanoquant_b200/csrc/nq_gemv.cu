@@ -25,15 +25,17 @@
 // near one third of the HBM rate on this part, which is why the integer MMA is
 // used as a wide dot-product unit here.
 //
-// Phases: phase 1 computes t[T,R] (fp32, in scratch), a device-wide barrier
-// follows, phase 2 computes y.  Several linears that share the two phases (q/k/v,
-// gate/up) are processed in one launch.  The weight stream of the next job is
-// started before the barrier, so the barrier wait overlaps with HBM traffic.  The
-// barrier is one arrival counter (see grid_barrier); its spin is bounded: on expiry
-// a status word is set and every CTA returns.  The kernel is launched cooperative
-// (all CTAs resident) and with programmatic stream serialization: everything that
-// does not depend on the previous kernel (descriptor copy, first weight loads, an L2
-// prefetch of the input scales) runs before griddepcontrol.wait.
+// Phases: phase 1 computes t[T,R] (fp32, in scratch), phase 2 computes y.  Several
+// linears that share the two phases (q/k/v, gate/up) are processed in one launch.
+// There is no device-wide barrier between the phases: every element of t is stored
+// together with a tag of the launch and phase 2 polls the elements it needs until
+// they carry this launch's tag (see launch_tag / load8_tagged); the poll is bounded:
+// on expiry a status word is set and the thread goes on.  The weight stream of the
+// next job is started before that wait, so it overlaps with HBM traffic.  The kernel
+// is launched cooperative (all CTAs resident: consumers spin on other CTAs' data) and
+// with programmatic stream serialization: everything that does not depend on the
+// previous kernel (descriptor copy, first weight loads, an L2 prefetch of the input
+// scales) runs before griddepcontrol.wait.
 //
 // For 8B-class layers the kernel is a chain of dependent latencies (memory round
 // trips, CTA barriers, one device-wide barrier), not a bandwidth problem; the code
