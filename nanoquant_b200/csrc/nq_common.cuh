@@ -37,6 +37,49 @@ inline cudaStream_t as_stream(nq_stream_t s) { return reinterpret_cast<cudaStrea
 int sm_count();
 
 // ---------------------------------------------------------------------------
+// launch tags: data that carries its own "ready" flag
+// ---------------------------------------------------------------------------
+// A producer CTA stores every element of an intermediate as an 8-byte {fp32 value, tag} pair with one 64-bit
+// store; a consumer CTA of the same launch loads the pairs it needs and repeats the load until every tag
+// equals the tag of this launch.  The first poll after the last producer store has landed already returns
+// the data, which takes an arrive / poll / reload sequence (three memory round trips) and any device-wide
+// barrier off the critical path.  Consumers spin on other CTAs, so the launch must be cooperative.
+//
+// The tag is the launch count of the scratch buffer, read from a 64-bit arrival counter in its header:
+// every launch advances it by exactly kTagSpan (the first CTA adds kTagSpan - (CTAs - 1), every other CTA
+// adds 1, with a reduction nobody waits for), so the bits above the span are the same for every CTA of a
+// launch whenever it reads them (fewer than a span's worth of arrivals can precede the read) and differ from
+// those of every recent launch.  Reads and arrivals of a launch must come after the previous launch on the
+// scratch has completed (behind griddepcontrol.wait).  The tag is 0x7FF in its upper 12 bits (a NaN pattern
+// as fp32 and in both halves as fp16 / bf16 pairs, which no kernel that shares the scratch ever stores, and
+// never the 0 of a zeroed scratch) and the launch count modulo 2^20 below; an element is rewritten by every
+// launch that uses its address, so a stale tag can only match after 2^20 launches in a row that leave it
+// alone.  Waits are bounded: on expiry a status word is set and the thread goes on with what it has (the
+// host reports the status).
+constexpr unsigned kTagSpan = 1024u;        // > CTAs per tagged launch
+constexpr unsigned kSpinLimit = 4000000u;   // polls before a wait gives up
+struct TagCtx {
+    unsigned tag;        // tag of this launch
+    unsigned* status;    // device status word
+};
+__device__ __forceinline__ unsigned launch_tag(const unsigned long long* counter) {
+    unsigned long long c;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(c) : "l"(counter) : "memory");
+    return 0x7FF00000u | ((unsigned)(c / kTagSpan) & 0xFFFFFu);
+}
+// This CTA's arrival at the counter.  Issued by one thread, once per launch, after a CTA barrier that every
+// thread passes behind its own launch_tag() read: the arrival that completes the span would otherwise show
+// the next launch's tag to a thread of the same CTA that reads late.
+__device__ __forceinline__ void launch_arrive(unsigned long long* counter, bool first_cta, unsigned n_ctas) {
+    const unsigned long long w = first_cta ? (unsigned long long)(kTagSpan - (n_ctas - 1)) : 1ull;
+    asm volatile("red.relaxed.gpu.global.add.u64 [%0], %1;" ::"l"(counter), "l"(w) : "memory");
+}
+__device__ __forceinline__ void store_tagged(void* base, long long i, float val, unsigned tag) {
+    asm volatile("st.relaxed.gpu.global.v2.u32 [%0], {%1,%2};"
+                 ::"l"(static_cast<uint2*>(base) + i), "r"(__float_as_uint(val)), "r"(tag) : "memory");
+}
+
+// ---------------------------------------------------------------------------
 // bit orders of a 32-column word
 //   lsb_first: element k              -> bit k
 //   half2:     element 2j / element 2j+1 -> bit 15-j / bit 31-j

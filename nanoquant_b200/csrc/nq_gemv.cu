@@ -68,7 +68,6 @@ constexpr int kStages = NQ_GEMV_STAGES;          // 1 KB weight slots in flight 
 constexpr size_t kRedBytes = 384;   // per-warp maxima: kMaxTok * kGemvWarps floats (16-byte aligned rows)
 constexpr size_t kFixedBytes = 512;
 constexpr size_t kRingBytes = (size_t)kGemvWarps * kStages * 1024;
-constexpr unsigned kSpinLimit = 4000000u;
 constexpr size_t kHeaderBytes = 256;
 
 // KIND_T: the rank-R intermediate between the phases, one 8-byte {fp32 value, launch tag} pair per element
@@ -136,39 +135,6 @@ __device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, ui
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// Hand-over of the rank-R intermediate between the phases WITHOUT a device-wide barrier: the data carries
-// its own flag.  Phase 1 stores every element of t as an 8-byte {fp32 value, tag} pair with one 64-bit
-// store; phase 2 loads the pairs it needs and repeats the load until every tag equals the tag of this
-// launch.  The first poll after the last producer store has landed already returns the data, which takes
-// an arrive / poll / reload sequence (three memory round trips) off the critical path.
-//
-// The tag is the launch count of the scratch buffer, read from a 64-bit arrival counter: every launch
-// advances it by exactly kTagSpan (CTA 0 adds kTagSpan - (nblocks - 1), every other CTA adds 1, with a
-// reduction nobody waits for), so the bits above the span are the same for every CTA of a launch whenever
-// it reads them (fewer than a span's worth of arrivals can precede the read) and differ from those of every
-// recent launch.  The tag is 0x7FF in its upper 12 bits (a NaN pattern as fp32 and in both halves as fp16 /
-// bf16 pairs, which no other kernel that shares the scratch ever stores, and never the 0 of a zeroed scratch)
-// and the launch count modulo 2^20 below; an element is rewritten by every launch whose rank exceeds its
-// index, so a stale tag can only match after 2^20 launches in a row with smaller ranks on the same scratch.
-// The wait is bounded: on expiry a status word is set and the thread goes on with what it has (the host
-// reports the status).
-constexpr unsigned kTagSpan = 1024u;   // > CTAs per launch
-struct TagCtx {
-    unsigned tag;        // tag of this launch
-    unsigned* status;    // device status word
-};
-__device__ __forceinline__ unsigned launch_tag(const unsigned long long* counter) {
-    unsigned long long c;
-    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(c) : "l"(counter) : "memory");
-    return 0x7FF00000u | ((unsigned)(c / kTagSpan) & 0xFFFFFu);
-}
-// This CTA's arrival at the counter.  Issued by one thread, once per launch, after a CTA barrier that every
-// thread passes behind its own launch_tag() read: the arrival that completes the span would otherwise show
-// the next launch's tag to a thread of the same CTA that reads late.
-__device__ __forceinline__ void launch_arrive(unsigned long long* counter, unsigned nblocks) {
-    const unsigned long long w = blockIdx.x == 0 ? (unsigned long long)(kTagSpan - (nblocks - 1)) : 1ull;
-    asm volatile("red.relaxed.gpu.global.add.u64 [%0], %1;" ::"l"(counter), "l"(w) : "memory");
-}
 // Eight tagged elements (64 bytes) as floats, polled until all eight carry this launch's tag.
 __device__ __forceinline__ void load8_tagged(const void* base, long long i, float (&v)[8], const TagCtx& tc) {
     const uint4* p = reinterpret_cast<const uint4*>(static_cast<const uint2*>(base) + i);
@@ -202,10 +168,6 @@ __device__ __forceinline__ float load1_tagged(const void* base, long long i, con
         }
     }
     return __uint_as_float(q.x);
-}
-__device__ __forceinline__ void store_tagged(void* base, long long i, float val, unsigned tag) {
-    asm volatile("st.relaxed.gpu.global.v2.u32 [%0], {%1,%2};"
-                 ::"l"(static_cast<uint2*>(base) + i), "r"(__float_as_uint(val)), "r"(tag) : "memory");
 }
 
 // Eight consecutive elements of a vector as floats (one or two 128-bit loads).
@@ -659,7 +621,7 @@ __device__ __forceinline__ bool run_all(const Phase* phases, const GemvParams& P
         for (int i = tid; i < st.my_items * (32 * kCols); i += kGemvThreads) s1[i] = 0;
         quantise_input(jb, P.T, P.scale_kind, xq, P.xq_stride, red, sumx, delta, tc);
         if (!arrived) {   // behind the CTA barriers of the quantiser
-            if (tid == 0) launch_arrive(reinterpret_cast<unsigned long long*>(P.header), gridDim.x);
+            if (tid == 0) launch_arrive(reinterpret_cast<unsigned long long*>(P.header), blockIdx.x == 0, gridDim.x);
             arrived = true;
         }
         NQ_TRACE(5);
@@ -758,7 +720,7 @@ __device__ __forceinline__ bool run_all(const Phase* phases, const GemvParams& P
     }
     if (!arrived) {   // a CTA without row tiles in either phase still counts towards the launch
         __syncthreads();
-        if (tid == 0) launch_arrive(reinterpret_cast<unsigned long long*>(P.header), gridDim.x);
+        if (tid == 0) launch_arrive(reinterpret_cast<unsigned long long*>(P.header), blockIdx.x == 0, gridDim.x);
     }
     return true;
 }
