@@ -30,7 +30,8 @@ def test_library_exports_every_declared_symbol():
         assert hasattr(L, name), name
     assert L.nq_abi_version() >= 1
     assert L.nq_strerror(-7).decode().startswith("a bounded")
-    assert L.nq_gemv_scratch_bytes(1, 4096, 1536, 4096) == 256 + 16 * 1536
+    # header + four token slots of tagged fp32 (8 bytes per element)
+    assert L.nq_gemv_scratch_bytes(1, 4096, 1536, 4096) == 256 + 4 * 1536 * 8
     assert L.nq_tiles_bytes(4096, 1536) == 256 * 6 * 512
 
 
