@@ -238,6 +238,30 @@ int nq_onebit_gemm_fwd(const void* x, const void* tiles, const void* s_in, const
                        void* y, void* status_word, int T, int K, int Nout, int dtype,
                        nq_stream_t stream);
 
+/* ------------------------------------------------------------------------ *
+ * Tensor parallelism: all-gather of the output shards over peer memory
+ * ------------------------------------------------------------------------ */
+
+/* All-gather of [T, M/G] output shards as ONE small kernel per call (plain peer stores over NVLink, a
+ * flag word per rank, a bounded wait), so that a tensor-parallel step can be captured in a CUDA graph
+ * together with the GEMV / GEMM launches.  The reference has no distributed code; the portable
+ * alternative is an NCCL all-gather (nanoquant_b200/tp.py uses either).
+ * Every rank owns a buffer of the same layout whose base pointers (peer-accessible, 16-byte aligned,
+ * e.g. from symmetric memory) are passed by every rank in rank order: nq_allgather_flags_bytes() of
+ * flag words, zeroed once, at `flags_offset`, and gathered regions.  The call copies `shard`
+ * (shard_bytes, a multiple of 16) into slot `rank` of the region at `region_offset` in EVERY rank's
+ * buffer, signals the peers and waits until all ranks' shards have arrived in this rank's region;
+ * kernels launched afterwards on `stream` see the gathered [G][shard] data.  `local_state`:
+ * nq_allgather_state_bytes() of local device memory, zeroed once, one per communicator.  All ranks
+ * must issue the same sequence of calls; consecutive calls must use different regions (a rank may be
+ * one call ahead of a peer).  nq_allgather_status() synchronises and reports an expired wait. */
+size_t nq_allgather_state_bytes(void);
+size_t nq_allgather_flags_bytes(int world);
+int nq_allgather_push(const void* shard, size_t shard_bytes, void* const* rank_bases_host,
+                      size_t flags_offset, size_t region_offset, void* local_state,
+                      int world, int rank, nq_stream_t stream);
+int nq_allgather_status(const void* local_state, nq_stream_t stream);
+
 /* Token-count dispatch the reference leaves to the caller's `kernel_type`:
  * the GEMV for T <= nq_gemv_max_tokens(), the GEMM above.  Scratch must satisfy
  * nq_linear_scratch_bytes(). */

@@ -56,6 +56,11 @@ SIGNATURES = {
     "nq_gemm_group_scratch_bytes": (c_size_t, [ctypes.POINTER(LinearDesc), c_int, c_int]),
     "nq_gemm_group_fwd": (c_int, [ctypes.POINTER(LinearDesc), c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "nq_onebit_gemm_fwd": (c_int, [c_void_p] * 6 + [c_int, c_int, c_int, c_int, c_void_p]),
+    "nq_allgather_state_bytes": (c_size_t, []),
+    "nq_allgather_flags_bytes": (c_size_t, [c_int]),
+    "nq_allgather_push": (c_int, [c_void_p, c_size_t, ctypes.POINTER(c_void_p), c_size_t, c_size_t, c_void_p, c_int, c_int,
+                                  c_void_p]),
+    "nq_allgather_status": (c_int, [c_void_p, c_void_p]),
     "nq_gemv_max_tokens": (c_int, []),
     "nq_linear_scratch_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "nq_linear_fwd": (c_int, [c_void_p] * 8 + [c_size_t, c_int, c_int, c_int, c_int, c_int, c_void_p]),

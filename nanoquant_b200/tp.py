@@ -8,7 +8,10 @@ intermediate is computed redundantly on every GPU and the only exchange is one
 all-gather of the ``[T, M/G]`` output shards (NCCL over NVLink, issued on the compute
 stream).  Per-GPU bytes: ``R*N/8 + R*M/(8G)`` + scales + activations.
 
-Nothing here reads another GPU's memory directly and no TMA multicast is involved.
+Two collectives are available: NCCL (``gather_outputs``) and ``PeerGather``, one small kernel per call that
+stores the shard into every rank's symmetric-memory buffer with plain peer stores and waits (bounded) for the
+peers' flags, which can be captured in a CUDA graph together with the GEMV / GEMM launches.  No TMA multicast
+and no multimem is involved anywhere.
 """
 from __future__ import annotations
 
@@ -90,3 +93,60 @@ def tp_linear_forward(x: torch.Tensor, shard: TPLinearShard, group=None,
     else:
         y_local = local_fn(x, shard)
     return gather_outputs(y_local, shard.world, group=group)
+
+
+class PeerGather:
+    """All-gather over peer memory (``nq_allgather_push``) on a symmetric-memory arena.
+
+    ``PeerGather(nbytes, group)`` allocates ``nbytes`` of gather regions (plus the flag words) in symmetric
+    memory on every rank.  ``region(shape, dtype)`` carves a ``[world, *shape]`` region out of the arena;
+    ``gather(shard, region)`` launches the push on the current stream and returns the region, which holds
+    every rank's shard once the kernel has completed (stream order).  Consecutive gathers must use different
+    regions.  Multicast objects are not created (``TORCH_SYMM_MEM_DISABLE_MULTICAST=1`` is set before the
+    rendezvous)."""
+
+    FLAGS_BYTES = 256
+
+    def __init__(self, nbytes: int, group=None, device: Optional[torch.device] = None):
+        import ctypes
+        import os
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm_mem
+        from . import _lib
+        self._lib, self._L, self._ct = _lib, _lib.lib(), ctypes
+        group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        total = self.FLAGS_BYTES + (nbytes + 255) // 256 * 256
+        self.arena = symm_mem.empty(total, dtype=torch.uint8, device=device)
+        self.arena.zero_()
+        self.handle = symm_mem.rendezvous(self.arena, group)
+        bases = [int(p) for p in self.handle.buffer_ptrs]
+        assert bases[self.rank] == self.arena.data_ptr()
+        self._bases = (ctypes.c_void_p * self.world)(*bases)
+        self.state = torch.zeros(self._L.nq_allgather_state_bytes(), dtype=torch.uint8, device=device)
+        self._next = self.FLAGS_BYTES
+        torch.cuda.synchronize(device)
+        dist.barrier(group)     # every rank has zeroed its flags before anybody signals
+
+    def region(self, shape, dtype) -> torch.Tensor:
+        """A ``[world, *shape]`` view of the arena (same offset on every rank: call in the same order everywhere)."""
+        n = self.world * int(torch.Size(shape).numel()) * torch.empty((), dtype=dtype).element_size()
+        if self._next + n > self.arena.numel():
+            raise RuntimeError("PeerGather arena exhausted")
+        view = self.arena[self._next:self._next + n].view(dtype).view(self.world, *shape)
+        self._next += (n + 255) // 256 * 256
+        return view
+
+    def gather(self, shard: torch.Tensor, region: torch.Tensor) -> torch.Tensor:
+        if not shard.is_contiguous() or shard.numel() * shard.element_size() * self.world != region.numel() * region.element_size():
+            raise ValueError("shard must be contiguous and 1/world of the region")
+        off = region.data_ptr() - self.arena.data_ptr()
+        st = self._L.nq_allgather_push(shard.data_ptr(), shard.numel() * shard.element_size(), self._bases, 0, off,
+                                       self.state.data_ptr(), self.world, self.rank,
+                                       torch.cuda.current_stream(shard.device).cuda_stream)
+        self._lib.check(st, "nq_allgather_push")
+        return region
+
+    def status(self) -> int:
+        return self._L.nq_allgather_status(self.state.data_ptr(), torch.cuda.current_stream(self.arena.device).cuda_stream)

@@ -62,3 +62,74 @@ def test_tp_linear_two_gpus():
     for rank, out in results:
         for shape, same_as_single, in_bar in out:
             assert same_as_single and in_bar, (rank, shape)
+
+
+def _peer_worker(rank, world, port, q):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    os.environ["TORCH_SYMM_MEM_DISABLE_MULTICAST"] = "1"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from nanoquant_b200 import tp
+        dev = torch.device("cuda", rank)
+        pg = tp.PeerGather(1 << 20)
+        shapes = [((1, 512), torch.bfloat16), ((3, 2048), torch.float16), ((160, 1024), torch.bfloat16)]
+        regions = [pg.region(sh, dt) for sh, dt in shapes]
+        ok = []
+        g = torch.Generator(device=dev).manual_seed(100 + rank)
+        # eager, twice over every region, then the same sequence replayed from a CUDA graph
+        shards = [torch.randn(sh, generator=g, device=dev).to(dt) for sh, dt in shapes]
+        for rep in range(2):
+            for sh_t, reg in zip(shards, regions):
+                sh_t.add_(1)                      # new data every round
+                got = pg.gather(sh_t, reg)
+                ref = [torch.empty_like(sh_t) for _ in range(world)]
+                dist.all_gather(ref, sh_t)
+                torch.cuda.synchronize()
+                ok.append(bool(torch.equal(got, torch.stack(ref))))
+        s = torch.cuda.Stream(dev)
+        s.wait_stream(torch.cuda.current_stream(dev))
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(s):
+            with torch.cuda.graph(graph, stream=s):
+                for sh_t, reg in zip(shards, regions):
+                    pg.gather(sh_t, reg)
+        torch.cuda.current_stream(dev).wait_stream(s)
+        for rep in range(3):
+            for sh_t in shards:
+                sh_t.mul_(2)
+            graph.replay()
+            torch.cuda.synchronize()
+            for sh_t, reg in zip(shards, regions):
+                ref = [torch.empty_like(sh_t) for _ in range(world)]
+                dist.all_gather(ref, sh_t)
+                torch.cuda.synchronize()
+                ok.append(bool(torch.equal(reg, torch.stack(ref))))
+        ok.append(pg.status() == 0)
+        q.put((rank, ok))
+    except Exception as e:   # report instead of leaving the parent waiting
+        q.put((rank, [f"{type(e).__name__}: {e}"]))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_peer_memory_all_gather_two_gpus():
+    """nq_allgather_push on symmetric memory against NCCL, eagerly and replayed from a CUDA graph."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_peer_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, ok in results:
+        assert all(v is True for v in ok), (rank, ok)
