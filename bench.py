@@ -530,6 +530,15 @@ def tp_arm(args):
     x = {"h": torch.randn(T, TP_HIDDEN, generator=g, device=device).to(dtype),
          "i": torch.randn(T, TP_INTER, generator=g, device=device).to(dtype)}
     keep, steps, nbytes, scratch_bytes = [], [], 0, 0
+    # collective: "peer" = nq_allgather_push on symmetric memory (one kernel per gather, graph-capturable),
+    # "nccl" = all_gather_into_tensor, issued eagerly
+    peer = None
+    if world > 1 and args.tp_collective == "peer":
+        from nanoquant_b200 import tp as nq_tp
+        esz = 2
+        gathered = sum(world * T * sum(M // world for (_, _, _, M, _, g_) in tp_layer_linears() if g_ == grp) * esz + 256
+                       for grp in range(4)) * layers
+        peer = nq_tp.PeerGather(gathered + 4096)
     use_gemm = T > L.nq_gemv_max_tokens()   # more tokens than a decode launch takes: the group GEMM (two launches)
     group_fwd = L.nq_gemm_group_fwd if use_gemm else L.nq_gemv_group_fwd
     group_bytes = L.nq_gemm_group_scratch_bytes if use_gemm else L.nq_gemv_group_scratch_bytes
@@ -543,7 +552,8 @@ def tp_arm(args):
             # [rank][T][q_r | k_r | v_r].
             width = sum(M // world for (_, _, _, M, _, _) in groups[grp])
             ybuf = torch.empty(T, width, device=device, dtype=dtype)
-            full = torch.empty(world * T, width, device=device, dtype=dtype)
+            full = (peer.region((T, width), dtype) if peer is not None
+                    else torch.empty(world * T, width, device=device, dtype=dtype))
             descs, col = [], 0
             for (name, N, R, M, src, _) in groups[grp]:
                 m = M // world
@@ -565,18 +575,21 @@ def tp_arm(args):
         st = torch.cuda.current_stream(device).cuda_stream
         for arr, ybuf, full in steps:
             _lib.check(group_fwd(arr, len(arr), T, _lib.NQ_BF16, scratch.data_ptr(), scratch.numel(), st), "group_fwd")
-            if world > 1:
+            if peer is not None:
+                peer.gather(ybuf, full)
+            elif world > 1:
                 dist.all_gather_into_tensor(full, ybuf)
 
-    # One GPU: the step is replayed as a CUDA graph.  Several GPUs: the launches and the NCCL calls are
-    # issued eagerly in stream order.  (The GEMV kernel holds a device-wide barrier and needs all its
-    # CTAs resident; it must never share the GPU with a collective kernel that is itself waiting for a
-    # peer, so the collectives are kept strictly ordered with it instead of being captured in a graph.)
+    # One GPU, or the peer-memory collective: the step is replayed as a CUDA graph.  With NCCL the launches
+    # and the collectives are issued eagerly in stream order (a first attempt to capture NCCL collectives
+    # together with the cooperative GEMV launches hung; that combination is not used).
     graph = None
     for _ in range(2):
         run()
     torch.cuda.synchronize(device)
-    if world == 1:
+    if world > 1:
+        dist.barrier()
+    if world == 1 or peer is not None:
         s = torch.cuda.Stream(device)
         s.wait_stream(torch.cuda.current_stream(device))
         with torch.cuda.stream(s):
@@ -606,6 +619,8 @@ def tp_arm(args):
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     if L.nq_scratch_status(scratch.data_ptr(), torch.cuda.current_stream(device).cuda_stream) != 0:
         raise SystemExit("bench.py: a device-wide wait timed out inside the GEMV kernel")
+    if peer is not None and peer.status() != 0:
+        raise SystemExit("bench.py: a wait for a peer's shard timed out inside the all-gather kernel")
     if rank == 0:
         step_s = ms.item() * 1e-3 / args.steps * (TP_LAYERS / layers)
         peaks = {}
@@ -622,7 +637,8 @@ def tp_arm(args):
             "dtype": ("bf16 tcgen05 mma / f32 accumulate; bf16 in/out" if use_gemm else "s8 mma / s32 accumulate; bf16 in/out"),
             "data": "synthetic",
             "config": {"workload": f"llama-3-70b-shaped decoder linears at {BPW} bpw, decode batch {T}, U split by output "
-                                   f"rows over {world} GPUs + one NCCL all-gather per launch group",
+                                   f"rows over {world} GPUs + one all-gather per launch group "
+                                   f"({'peer-memory kernel, CUDA graph' if peer is not None else 'NCCL, eager'})",
                        "layers_timed": layers, "layers": TP_LAYERS, "parallelism": f"tp{world}"},
             "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s per GPU", "frac": per_gpu / peak,
                          "traffic": None},
@@ -763,6 +779,8 @@ def main():
     ap.add_argument("--tokens", type=int, default=2048, help="tokens per GEMM in --mode prefill")
     ap.add_argument("--layers", type=int, default=LAYERS, help="decoder layers resident (fewer only for profiling)")
     ap.add_argument("--tp-layers", type=int, default=TP_LAYERS, help="layers actually timed in --mode tp")
+    ap.add_argument("--tp-collective", default="peer", choices=["peer", "nccl"],
+                    help="--mode tp with several GPUs: all-gather by the peer-memory kernel (graph replay) or by NCCL (eager)")
     args = ap.parse_args()
     global GEMM_MIN_TOKENS
     GEMM_MIN_TOKENS = args.gemm_min_tokens
