@@ -82,3 +82,32 @@ def test_zero_tokens_through_the_operators():
     y = torch.ops.binary_kernels.nanoquant_dyn_forward(L["x"][:0], L["s_pre"], half2_bits(L["V"]), L["s_mid"],
                                                        half2_bits(L["U"]), L["s_post"], num_acc_stage1=1, num_acc_stage2=1)
     assert y.shape == (0, 128)
+
+
+def test_peer_all_gather_on_one_gpu(env):
+    """nq_allgather_push with a world of one (the rank's own buffer is the only "peer"): the shard lands in
+    slot 0 of the region, repeated launches advance the epoch, arguments are checked."""
+    import ctypes
+    _lib, L, z, st = env
+    dev = z.device
+    flags = L.nq_allgather_flags_bytes(1)
+    assert flags == 256 and L.nq_allgather_flags_bytes(9) == 0
+    arena = torch.zeros(flags + 3 * 4096, dtype=torch.uint8, device=dev)
+    state = torch.zeros(L.nq_allgather_state_bytes(), dtype=torch.uint8, device=dev)
+    bases = (ctypes.c_void_p * 1)(arena.data_ptr())
+    for rep, nbytes in enumerate((16, 4096, 1040)):
+        shard = torch.randint(0, 255, (nbytes,), dtype=torch.uint8, device=dev)
+        off = flags + rep * 4096
+        assert L.nq_allgather_push(shard.data_ptr(), nbytes, bases, 0, off, state.data_ptr(), 1, 0, st) == _lib.NQ_OK
+        assert L.nq_allgather_status(state.data_ptr(), st) == _lib.NQ_OK
+        assert torch.equal(arena[off:off + nbytes], shard)
+        assert int(arena[:4].view(torch.int32)[0]) == rep + 1           # this rank's flag word holds the epoch
+    shard = torch.zeros(64, dtype=torch.uint8, device=dev)
+    args = lambda **kw: dict(dict(shard=shard.data_ptr(), n=64, bases=bases, fo=0, ro=flags, state=state.data_ptr(), world=1, rank=0), **kw)
+    call = lambda a: L.nq_allgather_push(a["shard"], a["n"], a["bases"], a["fo"], a["ro"], a["state"], a["world"], a["rank"], st)
+    assert call(args(n=40)) == _lib.NQ_ERR_ALIGN          # not a multiple of 16 bytes
+    assert call(args(ro=flags + 8)) == _lib.NQ_ERR_ALIGN
+    assert call(args(world=9)) == _lib.NQ_ERR_SHAPE
+    assert call(args(rank=1)) == _lib.NQ_ERR_SHAPE
+    assert call(args(state=None)) == _lib.NQ_ERR_NULL
+    torch.cuda.synchronize()
