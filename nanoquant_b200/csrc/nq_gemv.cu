@@ -598,6 +598,9 @@ __device__ __forceinline__ bool run_all(const Phase* phases, const GemvParams& P
     // with the tail of the previous kernel in the stream; the activations and the scratch (shared with
     // that kernel) are only touched after it has completed.  No-ops without the launch attribute.
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    // All CTAs of this cooperative grid are resident, so CTAs of the next kernel that start early cannot keep one
+    // of ours from being scheduled: let the next kernel begin its prologue wherever an SM frees up.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     // tag of this launch for the intermediate's {value, tag} pairs (and this CTA's arrival, which nobody waits for)
     TagCtx tc;
     tc.tag = launch_tag(reinterpret_cast<const unsigned long long*>(P.header));
@@ -609,10 +612,7 @@ __device__ __forceinline__ bool run_all(const Phase* phases, const GemvParams& P
         if (!barrier_done && s >= njobs) {    // this CTA's share of phase 1 is on its way
             NQ_TRACE(8);
             barrier_done = true;
-            // No device-wide barrier: phase 2 polls the tagged intermediate itself (load8_tagged).  All CTAs of
-            // this cooperative grid are resident, so CTAs of the next kernel that start early cannot keep one of
-            // ours from being scheduled: let the next kernel begin its prologue.
-            asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+            // No device-wide barrier: phase 2 polls the tagged intermediate itself (load8_tagged).
             NQ_TRACE(9);
         }
         if (s >= 2 * njobs) break;
