@@ -538,7 +538,15 @@ def tp_arm(args):
         esz = 2
         gathered = sum(world * T * sum(M // world for (_, _, _, M, _, g_) in tp_layer_linears() if g_ == grp) * esz + 256
                        for grp in range(4)) * layers
-        peer = nq_tp.PeerGather(gathered + 4096)
+        try:
+            peer = nq_tp.PeerGather(gathered + 4096)
+            ok = torch.ones(1, device=device)
+        except Exception as e:   # no symmetric memory on this system: every rank falls back to NCCL together
+            print(f"bench.py: peer-memory all-gather unavailable ({type(e).__name__}: {e}); using NCCL", file=sys.stderr)
+            peer, ok = None, torch.zeros(1, device=device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if ok.item() == 0:
+            peer = None
     use_gemm = T > L.nq_gemv_max_tokens()   # more tokens than a decode launch takes: the group GEMM (two launches)
     group_fwd = L.nq_gemm_group_fwd if use_gemm else L.nq_gemv_group_fwd
     group_bytes = L.nq_gemm_group_scratch_bytes if use_gemm else L.nq_gemv_group_scratch_bytes
