@@ -426,6 +426,79 @@ __device__ __noinline__ void quantise_one(const Job& jb, int T, int8_t* xq, int 
     __syncthreads();
 }
 
+// The same with NI (2 or 4) blocks per thread: item f = tid + i * threads covers token f / nv8, columns
+// (f % nv8) * 8.  All NI loads of a thread are in flight together (the tagged intermediate is polled item by
+// item, but its later items are valid by then), nothing is loaded twice, and several tokens cost one memory
+// round trip instead of one per token and pass.
+template <int IN_KIND, int NI>
+__device__ __noinline__ void quantise_few(const Job& jb, int T, int8_t* xq, int stride, float* red,
+                                          int* sumx, float* delta, const TagCtx& tc) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int K = jb.K, nv8 = jb.chunks * 32, items = T * nv8;
+    constexpr bool kHasPre = (IN_KIND != KIND_T);
+    float p[NI][8];
+    int tt[NI], kk[NI];
+    Raw8<IN_KIND> x[NI], sc[NI];
+#pragma unroll
+    for (int i = 0; i < NI; ++i) {
+        const int f = tid + i * kGemvThreads;
+        const int t = f / nv8;
+        tt[i] = f < items ? t : -1;
+        kk[i] = (f - t * nv8) * 8;
+        x[i].a = x[i].b = make_uint4(0u, 0u, 0u, 0u);
+        sc[i].a = sc[i].b = make_uint4(0u, 0u, 0u, 0u);
+        if (tt[i] >= 0 && kk[i] < K) {
+            load_raw<IN_KIND>(jb.in, t * jb.ld_in + kk[i], x[i], tc);
+            if (kHasPre) load_raw<IN_KIND>(jb.pre, kk[i], sc[i], tc);
+        }
+    }
+    float wm[kMaxTok];   // this warp's maximum per token (a warp's item belongs to one token)
+#pragma unroll
+    for (int q = 0; q < kMaxTok; ++q) wm[q] = 0.f;
+#pragma unroll
+    for (int i = 0; i < NI; ++i) {
+        float s[8], m = 0.f;
+        to_float8<IN_KIND>(x[i], p[i]);
+        if (kHasPre) {
+            to_float8<IN_KIND>(sc[i], s);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) p[i][e] *= s[e];
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) m = fmaxf(m, fabsf(p[i][e]));
+        m = warp_max_abs(m);
+#pragma unroll
+        for (int q = 0; q < kMaxTok; ++q) wm[q] = tt[i] == q ? fmaxf(wm[q], m) : wm[q];
+    }
+    if (lane < kMaxTok) {
+        float v = wm[0];
+#pragma unroll
+        for (int q = 1; q < kMaxTok; ++q) v = lane == q ? wm[q] : v;
+        red[lane * kGemvWarps + warp] = v;
+    }
+    if (tid < kMaxTok) sumx[tid] = 0;
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < NI; ++i) {
+        if (tt[i] >= 0) {      // warp-uniform
+            const float inv = token_inv(red, tt[i], kk[i] == 0, delta);
+            const int j = (kk[i] >> 5) & 7;
+            uint32_t Y[8];
+            int acc = 0;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const int X = __float2int_rn(p[i][e] * inv);
+                acc += X;
+                Y[e] = (uint32_t)class_shift(X, j);
+            }
+            store_terms(Y, xq + (3 * tt[i]) * stride, stride, kk[i]);
+            acc = __reduce_add_sync(0xffffffffu, acc);
+            if (lane == 0 && acc != 0) atomicAdd(&sumx[tt[i]], acc);
+        }
+    }
+    __syncthreads();
+}
+
 // Scalar path for unaligned or ragged inputs (any K, any alignment).
 __device__ __noinline__ void quantise_scalar(const Job& jb, int T, int scale_kind, int8_t* xq, int stride,
                                              float* red, int* sumx, float* delta, const TagCtx& tc) {
@@ -473,6 +546,16 @@ __device__ __forceinline__ void quantise_input(const Job& jb, int T, int scale_k
         if (jb.in_kind == KIND_T) quantise_one<KIND_T>(jb, T, xq, stride, red, sumx, delta, tc);
         else if (jb.in_kind == KIND_F16) quantise_one<KIND_F16>(jb, T, xq, stride, red, sumx, delta, tc);
         else quantise_one<KIND_BF16>(jb, T, xq, stride, red, sumx, delta, tc);
+    }
+    else if (T * jb.chunks * 32 <= 2 * kGemvThreads) {
+        if (jb.in_kind == KIND_T) quantise_few<KIND_T, 2>(jb, T, xq, stride, red, sumx, delta, tc);
+        else if (jb.in_kind == KIND_F16) quantise_few<KIND_F16, 2>(jb, T, xq, stride, red, sumx, delta, tc);
+        else quantise_few<KIND_BF16, 2>(jb, T, xq, stride, red, sumx, delta, tc);
+    }
+    else if (T > 1 && T * jb.chunks * 32 <= 4 * kGemvThreads) {   // one token of that width: quantise_vec measured faster
+        if (jb.in_kind == KIND_T) quantise_few<KIND_T, 4>(jb, T, xq, stride, red, sumx, delta, tc);
+        else if (jb.in_kind == KIND_F16) quantise_few<KIND_F16, 4>(jb, T, xq, stride, red, sumx, delta, tc);
+        else quantise_few<KIND_BF16, 4>(jb, T, xq, stride, red, sumx, delta, tc);
     }
     else if (jb.in_kind == KIND_T) quantise_vec<KIND_T>(jb, T, xq, stride, red, sumx, delta, tc);
     else if (jb.in_kind == KIND_F16) quantise_vec<KIND_F16>(jb, T, xq, stride, red, sumx, delta, tc);
