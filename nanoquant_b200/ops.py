@@ -115,6 +115,33 @@ def gemv_forward(x: torch.Tensor, s_in: torch.Tensor, v_tiles: torch.Tensor, s_m
     return y
 
 
+def dense_gemv_forward(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``F.linear(x, weight, bias)`` for the few tokens of a decode step through ``nq_dense_gemv_fwd``.
+
+    For the layers the reference leaves as ``nn.Linear`` (``lm_head``, ``utils/load_utils.py:322``): ``weight``
+    ``[V, N]`` fp16/bf16 with a unit inner stride, ``x`` ``[..., N]`` with at most ``nq_dense_gemv_max_tokens()``
+    rows in total; more rows raise (a batched GEMM is the right tool there)."""
+    _check_cuda_cont(x, "x", weight.dtype, str(weight.dtype))
+    if weight.dim() != 2 or weight.stride(1) != 1 or not weight.is_cuda:
+        raise RuntimeError("weight must be a CUDA [V, N] matrix with a unit inner stride")
+    if x.size(-1) != weight.size(1):
+        raise RuntimeError(f"x has {x.size(-1)} columns, weight expects {weight.size(1)}")
+    if bias is not None:
+        _check_cuda_cont(bias, "bias", weight.dtype, str(weight.dtype))
+    V, N = weight.shape
+    x2 = x.reshape(-1, N)
+    T = x2.size(0)
+    y = torch.empty((T, V), dtype=x.dtype, device=x.device)
+    if T > 0:
+        L = _lib.lib()
+        with torch.cuda.device(x.device):
+            st = L.nq_dense_gemv_fwd(x2.data_ptr(), weight.data_ptr(), bias.data_ptr() if bias is not None else None,
+                                     y.data_ptr(), T, N, V, weight.stride(0), V, _dtype_id(x),
+                                     torch.cuda.current_stream(x.device).cuda_stream)
+        _lib.check(st, "nq_dense_gemv_fwd")
+    return y.reshape(*x.shape[:-1], V)
+
+
 def _nanoquant_dyn_forward_cuda(x, scale_g, Ubits, scale_l, Vbits, scale_h,
                                 num_thread_stage1=128, num_thread_stage2=128,
                                 num_row_per_warp_stage1=2, num_row_per_warp_stage2=2,

@@ -186,6 +186,15 @@ def forward_fp64(x, V, U, s_pre, s_mid, s_post, bias=None) -> np.ndarray:
     return y
 
 
+def dense_forward_fp64(x, W, bias=None) -> np.ndarray:
+    """``F.linear(x, W, bias)`` in float64 on the exact stored values: the un-quantised ``lm_head`` the
+    reference's decode loop calls once per token (``utils/load_utils.py:322`` keeps it an ``nn.Linear``)."""
+    y = np.asarray(x, np.float64) @ np.asarray(W, np.float64).T
+    if bias is not None:
+        y = y + np.asarray(bias, np.float64)
+    return y
+
+
 def forward_from_packed(x, Vp, Up, s_pre, s_mid, s_post, N, R, M, method="half2"):
     """:func:`forward_fp64` on packed factors ``Vp [R, N/32]``, ``Up [M, R/32]``."""
     V = unpack_rows(np.asarray(Vp), (R, N), method)
