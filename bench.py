@@ -321,7 +321,42 @@ class StepCycle:
         return max(st.status() for st in self.steps)
 
 
-def side_numbers(device, dtype):
+VOCAB = {"qwen3-8b": 151936, "llama-3.2-1b": 128256}
+
+
+def measure_head(device, dtype, T, step_ms=None, vocab=None, steps=20, profile=False):
+    """The un-quantised ``lm_head`` of the workload's model ([vocab, hidden] in the model dtype, larger than L2)
+    as one ``nq_dense_gemv_fwd`` launch per decode step: time, algorithmic GB/s against the measured HBM peak,
+    and, given the time of the decoder's linears, the decode rate with the head included."""
+    import torch
+    from nanoquant_b200 import ops
+    V = vocab or VOCAB[WORKLOAD]
+    g = torch.Generator(device=device).manual_seed(3)
+    W = (torch.randn((V, HIDDEN), generator=g, device=device, dtype=torch.float32) * 0.02).to(dtype)
+    x = torch.randn((T, HIDDEN), generator=g, device=device, dtype=torch.float32).to(dtype)
+    for _ in range(3):
+        ops.dense_gemv_forward(x, W)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize(device)
+    if profile:
+        torch.cuda.profiler.start()
+    e0.record()
+    for _ in range(steps):
+        ops.dense_gemv_forward(x, W)
+    e1.record()
+    torch.cuda.synchronize(device)
+    if profile:
+        torch.cuda.profiler.stop()
+    ms = e0.elapsed_time(e1) / steps
+    nbytes = 2 * (V * HIDDEN + T * (HIDDEN + V))
+    out = {"value": nbytes / (ms * 1e-3) / 1e9, "unit": "GB/s", "ms": ms, "kernel": "dense_gemv_kernel",
+           "shape": [V, HIDDEN], "hbm_frac": nbytes / (ms * 1e-3) / 1e9 / hbm_peak()[0]}
+    if step_ms is not None:
+        out["decode_tokens_per_s_with_head"] = T / ((step_ms + ms) * 1e-3)
+    return out
+
+
+def side_numbers(device, dtype, step_ms):
     """Short measurements of the workload's other operating points (decode batches 4 and 16, one prefill GEMM
     size), reported beside the headline line; same kernels, same synthetic weights, CUDA events."""
     import torch
@@ -345,6 +380,7 @@ def side_numbers(device, dtype):
                                    "kernel": step.kernel_name, "hbm_frac": step.bytes / (ms * 1e-3) / 1e9 / hbm_peak()[0]}
         del step
         torch.cuda.empty_cache()
+    out["lm_head_gemv"] = measure_head(device, dtype, 1, step_ms)
     tf, ms, _, _, _ = measure_prefill(2048, 4, 3, 3, device)
     out["prefill_2048_tokens"] = {"value": tf, "unit": "TFLOP/s", "ms_per_step": ms,
                                   "frac_of_sustained_bf16_peak": tf / tensor_peak()[0]}
@@ -483,7 +519,7 @@ def gpu_arm(args):
     if world == 1 and T == 1 and args.layers == LAYERS and WORKLOAD == "qwen3-8b" and not args.no_side_numbers:
         del step
         torch.cuda.empty_cache()
-        out["other_operating_points"] = side_numbers(device, dtype)
+        out["other_operating_points"] = side_numbers(device, dtype, step_s * 1e3)
     if not args.no_cpu_baseline:
         cpu = CpuLayer(T)
         t_layer, reps = cpu.timed(budget_s=12.0)
@@ -767,6 +803,28 @@ def prefill_arm(args):
         "gpu_launches": launches * args.steps, "clocks": clocks}), flush=True)
 
 
+def head_arm(args):
+    """`--mode head`: the dense GEMV of the un-quantised `lm_head` alone (`--vocab` rows, `--batch` tokens)."""
+    import torch
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(device)
+    sampler = ClockSampler(device.index or 0)
+    sampler.start()
+    h = measure_head(device, torch.bfloat16, args.batch, vocab=args.vocab or None, steps=args.steps, profile=True)
+    clocks = sampler.stop()
+    peak, peak_src = hbm_peak()
+    print(json.dumps({
+        "mode": "head", "metric": "lm_head GEMV GB/s (algorithmic bytes: weights once + x + y)", "value": h["value"],
+        "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": 3, "ms_per_step": h["ms"],
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 (fp32 accumulate)",
+        "data": "synthetic",
+        "config": {"workload": f"{WORKLOAD} lm_head {h['shape'][0]} x {h['shape'][1]}, {args.batch} token(s)",
+                   "l2": "weights larger than L2" if 2 * h["shape"][0] * h["shape"][1] > 2 * L2_BYTES else "weights may fit L2"},
+        "roofline": {"bound": "hbm", "achieved": h["value"], "peak": peak, "unit": "GB/s", "frac": h["value"] / peak,
+                     "traffic": None, "kernel": "dense_gemv_kernel", "peak_source": peak_src},
+        "gpu_launches": args.steps, "clocks": clocks}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -781,9 +839,10 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-side-numbers", action="store_true",
                     help="skip the short batch-4 / batch-16 / prefill measurements added to the default line")
-    ap.add_argument("--mode", default="replica", choices=["replica", "tp", "prefill"],
+    ap.add_argument("--mode", default="replica", choices=["replica", "tp", "prefill", "head"],
                     help="replica: the decode step (N > 1: independent replicas); tp: 70B-shaped TP decode step; "
                          "prefill: GEMM TFLOP/s on Llama-2-7B-shaped layers")
+    ap.add_argument("--vocab", type=int, default=0, help="rows of the head in --mode head (0: the workload's vocabulary)")
     ap.add_argument("--tokens", type=int, default=2048, help="tokens per GEMM in --mode prefill")
     ap.add_argument("--layers", type=int, default=LAYERS, help="decoder layers resident (fewer only for profiling)")
     ap.add_argument("--tp-layers", type=int, default=TP_LAYERS, help="layers actually timed in --mode tp")
@@ -801,6 +860,8 @@ def main():
         tp_arm(args)
     elif args.mode == "prefill":
         prefill_arm(args)
+    elif args.mode == "head":
+        head_arm(args)
     else:
         gpu_arm(args)
 
