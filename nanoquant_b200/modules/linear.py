@@ -124,6 +124,22 @@ class NanoQuantLinear(nn.Module):
             import binary_kernels  # noqa: F401
             self.kernel_forward = torch.ops.binary_kernels.marlin_nanoquant_forward
 
+    def fold_input_scale(self, weight: torch.Tensor) -> None:
+        """Multiply ``scale_pre`` by a per-input-column weight (fp32 product, stored in the scale's dtype).
+
+        For the RMSNorm that feeds this linear in a decoder layer: ``linear(norm(x) * w)`` becomes
+        ``linear'(norm(x))`` with ``scale_pre' = scale_pre * w``, which removes an elementwise pass and one
+        rounding of the activations.  Valid before ``_prepare_kernel`` and after it for ``kernel_type="gemv"``
+        (the Marlin operands of ``"gemm"`` hold the scale in permuted order, so fold before preparing)."""
+        if not hasattr(self, "scale_pre"):
+            raise RuntimeError("fold_input_scale: call it before _prepare_kernel('gemm')")
+        w = weight.detach().reshape(-1).to(device=self.scale_pre.device, dtype=torch.float32)
+        if w.numel() != self.in_features:
+            raise ValueError(f"fold_input_scale: expected {self.in_features} weights, got {w.numel()}")
+        with torch.no_grad():
+            folded = self.scale_pre.detach().float() * w.view_as(self.scale_pre)
+            self.scale_pre.copy_(folded.to(self.scale_pre.dtype))
+
     def load_packed(self, V_packed, V_shape, U_packed, U_shape, scale_pre, scale_post, scale_mid=None,
                     dtype=torch.bfloat16, device="cuda"):
         """Checkpoint tensors (``lsb_first`` words, reference ``modules/linear.py:288-303``)

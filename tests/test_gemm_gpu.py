@@ -239,6 +239,39 @@ def test_module_kernel_paths():
         assert oc.rel_err(exact_np(y).reshape(-1, M), y64) <= TOL[torch.bfloat16]
 
 
+def test_module_fold_input_scale():
+    """A per-column weight folded into scale_pre (the RMSNorm weight in front of the linear) equals scaling x."""
+    from nanoquant_b200.modules.linear import NanoQuantLinear
+    N, R, M, T = 512, 160, 384, 3
+    d = oc.synth_linear(N, R, M, T, seed=8)
+    tt = lambda a: torch.from_numpy(np.ascontiguousarray(a))
+    g = torch.Generator().manual_seed(1)
+    w = (torch.rand(N, generator=g) + 0.5).to(torch.float16)
+    for kernel_type in ("gemv", "gemm"):
+        m = NanoQuantLinear(N, M, R, has_scale_mid=True).cuda()
+        with torch.no_grad():
+            m.V.copy_(tt(d["V"]).float())
+            m.U.copy_(tt(d["U"]).float())
+            m.scale_pre.copy_(tt(d["s_pre"]).float()[None])
+            m.scale_mid.copy_(tt(d["s_mid"]).float()[None])
+            m.scale_post.copy_(tt(d["s_post"]).float()[None])
+        m.fold_input_scale(w)
+        sp, sm, so = (exact_np(m.scale_pre)[0], exact_np(m.scale_mid)[0], exact_np(m.scale_post)[0])
+        # the folded scale is the product rounded once to the module's dtype
+        want = (tt(d["s_pre"]).to(torch.bfloat16).float() * w.float()).to(torch.bfloat16)
+        assert torch.equal(m.scale_pre.detach().cpu()[0], want)
+        m._prepare_kernel(kernel_type, torch.float16)
+        if kernel_type == "gemm":
+            with pytest.raises(RuntimeError, match="before _prepare_kernel"):
+                m.fold_input_scale(w)
+        x = tt(d["x"]).cuda()
+        y64 = oc.forward_fp64(d["x"], d["V"], d["U"], sp, sm, so)
+        assert oc.rel_err(exact_np(m(x)), y64) <= TOL[torch.float16]
+    with pytest.raises(ValueError):
+        m2 = NanoQuantLinear(N, M, R)
+        m2.fold_input_scale(w[:-1])
+
+
 def test_module_load_packed_checkpoint_tensors():
     from nanoquant_b200.modules.linear import NanoQuantLinear
     N, R, M, T = 512, 160, 384, 2
