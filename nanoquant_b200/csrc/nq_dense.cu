@@ -8,7 +8,7 @@
 // the A fragments of mma.sync.m16n8k16 (16 weight rows x 8 tokens per instruction, fp32 accumulation); the
 // tokens are the MMA's N dimension, so up to 8 of them cost the same instructions as one.
 //
-// Work split.  A unit is 16 consecutive rows of W.  The 16 warps of a CTA split the K dimension of a unit
+// Work split.  A unit is 16 consecutive rows of W.  The 16 (above 8 tokens: 32) warps of a CTA split the K dimension of a unit
 // in batches of 4 k blocks (32 columns each) per warp, keep 8 x 16-byte loads per lane in flight, and add
 // their partial 16 x 8 accumulators through shared memory (double buffered: one CTA barrier per 16 rows =
 // per 128 KB of weights at N = 4096).  CTAs own contiguous, equally sized ranges of units.
@@ -22,8 +22,8 @@
 
 namespace nq {
 
-constexpr int kDenseThreads = 512;
-constexpr int kDenseWarps = kDenseThreads / 32;
+// 16 warps per CTA and two CTAs per SM for up to 8 tokens; 32 warps and one CTA per SM above (16 tokens of a
+// wide row leave shared memory for one CTA only, and the loads in flight per SM stay the same)
 constexpr int kDenseBlocksPerBatch = 4;   // k blocks of 32 columns per warp per batch
 constexpr int kDenseMaxTokens = 16;
 
@@ -76,11 +76,16 @@ __device__ __forceinline__ void store_scalar(void* p, long long i, float v) {
 
 // NB = token blocks of 8 (1: T <= 8, 2: T <= 16).
 template <int NB, bool BF16>
-__global__ void __launch_bounds__(kDenseThreads, 2) dense_gemv_kernel(const DenseParams P) {
+__global__ void __launch_bounds__(512 * NB, 2 / NB) dense_gemv_kernel(const DenseParams P) {
+    constexpr int kDenseWarps = 16 * NB, kDenseThreads = 32 * kDenseWarps;
     extern __shared__ __align__(16) unsigned char smem[];
     unsigned char* xs = smem;                                                  // [T][x_stride]
-    float* part = reinterpret_cast<float*>(smem + (size_t)P.T * P.x_stride);   // [2][warps][NB][4][32]
+    float* part = reinterpret_cast<float*>(smem + (size_t)P.T * P.x_stride);   // [kBuffers][warps][NB][4][32]
     constexpr int kPartPerWarp = NB * 4 * 32;
+    // Shared memory that a CTA holds is taken from the SM's L1, through which the streaming loads in flight pass:
+    // with 16 tokens of a wide row resident, a second partial-sum buffer costs more bandwidth than the extra CTA
+    // barrier of a single one.
+    constexpr int kBuffers = NB == 1 ? 2 : 1;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, q = lane & 3;
 
@@ -88,12 +93,20 @@ __global__ void __launch_bounds__(kDenseThreads, 2) dense_gemv_kernel(const Dens
     // not meet a NaN)
     {
         const int chunks = P.x_stride / 16;          // 16-byte chunks per token, padding included
-        const int valid = P.N / 8;
-        for (int i = tid; i < P.T * chunks; i += kDenseThreads) {
-            const int t = i / chunks, c = i - t * chunks;
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (c < valid) v = *reinterpret_cast<const uint4*>(P.x + ((size_t)t * P.N + (size_t)c * 8) * 2);
-            *reinterpret_cast<uint4*>(xs + (size_t)t * P.x_stride + (size_t)c * 16) = v;
+        const int valid = P.N / 8, total = P.T * chunks;
+        for (int i0 = tid; i0 < total; i0 += 4 * kDenseThreads) {   // four independent loads per round trip
+            uint4 v[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int i = i0 + k * kDenseThreads, t = i / chunks, c = i - t * chunks;
+                v[k] = make_uint4(0, 0, 0, 0);
+                if (i < total && c < valid) v[k] = ldg_stream16(P.x + ((size_t)t * P.N + (size_t)c * 8) * 2);
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int i = i0 + k * kDenseThreads, t = i / chunks, c = i - t * chunks;
+                if (i < total) *reinterpret_cast<uint4*>(xs + (size_t)t * P.x_stride + (size_t)c * 16) = v[k];
+            }
         }
     }
     __syncthreads();
@@ -104,30 +117,37 @@ __global__ void __launch_bounds__(kDenseThreads, 2) dense_gemv_kernel(const Dens
     const unsigned char* x0 = xs + (size_t)(tok0 ? g : 0) * P.x_stride + q * 16;
     const unsigned char* x1 = xs + (size_t)(tok1 ? g + 8 : 0) * P.x_stride + q * 16;
 
-    for (int u = u0; u < u1; ++u) {
+    // One batch of weights per lane: 2 rows x 4 k blocks x 16 bytes.  The batch of the NEXT (unit, batch) step is
+    // requested right after the MMAs have consumed the registers of the current one, i.e. before the CTA barrier
+    // and the reduction that end a unit, so the stream of loads never drains.
+    uint4 wa[kDenseBlocksPerBatch], wb[kDenseBlocksPerBatch];
+    auto load_batch = [&](int u, int b) {
         const int ra = min(u * 16 + g, P.V - 1), rb = min(u * 16 + g + 8, P.V - 1);   // clamped: never stored
-        const char* pa = P.w + (long long)ra * P.ldw_bytes + q * 16;
-        const char* pb = P.w + (long long)rb * P.ldw_bytes + q * 16;
-        float acc[NB][4];
+        const int blk0 = (b * kDenseWarps + warp) * kDenseBlocksPerBatch;
+        const char* pa = P.w + (long long)ra * P.ldw_bytes + q * 16 + (size_t)blk0 * 64;
+        const char* pb = P.w + (long long)rb * P.ldw_bytes + q * 16 + (size_t)blk0 * 64;
 #pragma unroll
-        for (int n = 0; n < NB; ++n)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
-
-        for (int b = 0; b < P.nbat; ++b) {
-            const int blk0 = (b * kDenseWarps + warp) * kDenseBlocksPerBatch;
-            uint4 wa[kDenseBlocksPerBatch], wb[kDenseBlocksPerBatch];
-#pragma unroll
-            for (int j = 0; j < kDenseBlocksPerBatch; ++j) {
-                const int k0 = (blk0 + j) * 32 + q * 8;
-                if (k0 < P.N) {
-                    wa[j] = ldg_stream16(pa + (size_t)(blk0 + j) * 64);
-                    wb[j] = ldg_stream16(pb + (size_t)(blk0 + j) * 64);
-                } else {
-                    wa[j] = make_uint4(0, 0, 0, 0);
-                    wb[j] = make_uint4(0, 0, 0, 0);
-                }
+        for (int j = 0; j < kDenseBlocksPerBatch; ++j) {
+            const int k0 = (blk0 + j) * 32 + q * 8;
+            if (k0 < P.N) {
+                wa[j] = ldg_stream16(pa + j * 64);
+                wb[j] = ldg_stream16(pb + j * 64);
+            } else {
+                wa[j] = make_uint4(0, 0, 0, 0);
+                wb[j] = make_uint4(0, 0, 0, 0);
             }
+        }
+    };
+    float acc[NB][4];
+#pragma unroll
+    for (int n = 0; n < NB; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
+    if (u0 < u1) load_batch(u0, 0);
+
+    for (int u = u0, b = 0; u < u1;) {
+        {
+            const int blk0 = (b * kDenseWarps + warp) * kDenseBlocksPerBatch;
 #pragma unroll
             for (int j = 0; j < kDenseBlocksPerBatch; ++j) {
                 const size_t off = (size_t)(blk0 + j) * 64;
@@ -143,10 +163,18 @@ __global__ void __launch_bounds__(kDenseThreads, 2) dense_gemv_kernel(const Dens
                 }
             }
         }
+        const bool unit_done = b + 1 == P.nbat;
+        const int nu = unit_done ? u + 1 : u, nbt = unit_done ? 0 : b + 1;
+        if (nu < u1) load_batch(nu, nbt);
+        if (!unit_done) {
+            b = nbt;
+            continue;
+        }
 
-        // partial accumulators of the 16 warps -> shared memory (buffer u & 1), then 128 * NB threads add them.
-        // The barrier of unit u + 1 orders this unit's reads before the writes of unit u + 2 to the same buffer.
-        float* mine = part + ((size_t)((u - u0) & 1) * kDenseWarps + warp) * kPartPerWarp;
+        // partial accumulators of the warps -> shared memory, then 128 * NB threads add them.  With two buffers the
+        // barrier of unit u + 1 orders this unit's reads before the writes of unit u + 2 to the same buffer.
+        const int buf = kBuffers == 2 ? ((u - u0) & 1) : 0;
+        float* mine = part + ((size_t)buf * kDenseWarps + warp) * kPartPerWarp;
 #pragma unroll
         for (int n = 0; n < NB; ++n)
 #pragma unroll
@@ -158,7 +186,7 @@ __global__ void __launch_bounds__(kDenseThreads, 2) dense_gemv_kernel(const Dens
             const int nb = n >> 3, nn = n & 7;
             // accumulator register i of lane (g', q') is row g' + 8 * (i / 2), token 2 q' + (i % 2)
             const int reg = (row >> 3) * 2 + (nn & 1), src_lane = (row & 7) * 4 + (nn >> 1);
-            const float* src = part + (size_t)((u - u0) & 1) * kDenseWarps * kPartPerWarp + (nb * 4 + reg) * 32 + src_lane;
+            const float* src = part + (size_t)buf * kDenseWarps * kPartPerWarp + (nb * 4 + reg) * 32 + src_lane;
             float s = 0.f;
 #pragma unroll
             for (int w = 0; w < kDenseWarps; ++w) s += src[w * kPartPerWarp];
@@ -168,11 +196,19 @@ __global__ void __launch_bounds__(kDenseThreads, 2) dense_gemv_kernel(const Dens
                 store_scalar<BF16>(P.y, (long long)n * P.ldy + v, s);
             }
         }
+        if constexpr (kBuffers == 1) __syncthreads();   // the sums are read before the next unit overwrites them
+#pragma unroll
+        for (int n = 0; n < NB; ++n)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
+        u = nu;
+        b = 0;
     }
 }
 
 template <int NB, bool BF16>
 int launch_dense(const DenseParams& P, size_t smem, int optin, cudaStream_t stream) {
+    constexpr int kDenseThreads = 512 * NB;
     static int configured[64] = {0};    // per device: 0 = not yet, else CTAs per SM + 1
     int dev = 0;
     NQ_CUDA_TRY(cudaGetDevice(&dev));
@@ -208,13 +244,16 @@ int nq_dense_gemv_fwd(const void* x, const void* w, const void* bias, void* y, i
     if (!aligned16(x) || !aligned16(w)) return NQ_ERR_ALIGN;
 
     const int nblk = (N + 31) / 32;
-    const int per_batch = kDenseWarps * kDenseBlocksPerBatch;
-    const int nbat = (nblk + per_batch - 1) / per_batch;
+    auto warps_for = [](int t) { return t > 8 ? 32 : 16; };
+    auto nbat_for = [&](int t) {
+        const int per_batch = warps_for(t) * kDenseBlocksPerBatch;
+        return (nblk + per_batch - 1) / per_batch;
+    };
     // token stride: the padded row plus 64 bytes, so that the eight lanes of a quarter warp (two tokens x four
     // 16-byte chunks) hit eight different 16-byte bank groups
-    const int x_stride = nbat * per_batch * 64 + 64;
+    auto stride_for = [&](int t) { return nbat_for(t) * warps_for(t) * kDenseBlocksPerBatch * 64 + 64; };
     auto smem_for = [&](int t) {
-        return (size_t)t * x_stride + (size_t)2 * kDenseWarps * (t > 8 ? 2 : 1) * 4 * 32 * sizeof(float);
+        return (size_t)t * stride_for(t) + (size_t)(t > 8 ? 1 : 2) * warps_for(t) * (t > 8 ? 2 : 1) * 4 * 32 * sizeof(float);
     };
     int dev = 0, optin = 0;
     NQ_CUDA_TRY(cudaGetDevice(&dev));
@@ -238,8 +277,8 @@ int nq_dense_gemv_fwd(const void* x, const void* w, const void* bias, void* y, i
         P.N = N;
         P.V = V;
         P.units = (V + 15) / 16;
-        P.nbat = nbat;
-        P.x_stride = x_stride;
+        P.nbat = nbat_for(P.T);
+        P.x_stride = stride_for(P.T);
         const size_t smem = smem_for(P.T);
         int st;
         if (dtype == NQ_BF16) st = P.T > 8 ? launch_dense<2, true>(P, smem, optin, s) : launch_dense<1, true>(P, smem, optin, s);
