@@ -786,8 +786,7 @@ static int launch_stage(const StageJob* jobs, int n, int T, int dtype, int satur
     // (see the kernel's griddepcontrol instructions).  If the driver refuses the attribute once, plain
     // launches are used from then on.
     static bool pdl_ok = true;
-    cudaLaunchConfig_t cfg;
-    memset(&cfg, 0, sizeof(cfg));
+    cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(pl.tiles_total, m_tiles, pl.max_splits);
     cfg.blockDim = dim3(threads);
     cfg.dynamicSmemBytes = smem_bytes;

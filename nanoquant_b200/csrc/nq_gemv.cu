@@ -38,7 +38,7 @@
 // scales) runs before griddepcontrol.wait.
 //
 // For 8B-class layers the kernel is a chain of dependent latencies (memory round
-// trips, CTA barriers, one device-wide barrier), not a bandwidth problem; the code
+// trips, CTA barriers, the hand-over of t between the phases), not a bandwidth problem; the code
 // between the main loops is therefore kept short and free of divisions.
 //
 // replaces: src/nanoquant/kernel/cuda/gemv_kernel.cu:43-301 of the reference
@@ -612,7 +612,7 @@ __device__ __forceinline__ void stream_issue(PairStream& st, const Job& jb, uint
 
 // Set the cursor up and start the first weight loads of a job.  They do not depend on
 // the job's input vector, so this runs before the input is ready (for a phase-2 job:
-// before the device-wide barrier, which then overlaps with the loads).
+// before the wait for the tagged intermediate, which then overlaps with the loads).
 __device__ __forceinline__ void stream_begin(PairStream& st, const Job& jb, const Phase& ph, uint4* ring, int warp,
                                              int lane, uint16_t* post_s, int max_items) {
     st.my_items = my_tiles(jb, ph, st.first);
@@ -643,8 +643,8 @@ __device__ __forceinline__ bool cta_has_items(const Job& jb, const Phase& ph) {
     return my_tiles(jb, ph, f) > 0;
 }
 
-// The whole launch for one CTA: the jobs of phase 1, the device-wide barrier, the jobs
-// of phase 2.  CG = column groups of 8 MMA columns (3 columns per token).
+// The whole launch for one CTA: the jobs of phase 1, then the jobs of phase 2 (which poll the
+// tagged intermediate).  CG = column groups of 8 MMA columns (3 columns per token).
 template <int CG>
 __device__ __forceinline__ bool run_all(const Phase* phases, const GemvParams& P, unsigned char* smem) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -666,7 +666,6 @@ __device__ __forceinline__ bool run_all(const Phase* phases, const GemvParams& P
         while (s < 2 * njobs && !cta_has_items(job_of(s), phases[s >= njobs])) ++s;
         return s;
     };
-    bool barrier_done = false;
     PairStream st;
     st.slot = 0;
     int s = next_step(0);
@@ -692,12 +691,6 @@ __device__ __forceinline__ bool run_all(const Phase* phases, const GemvParams& P
     NQ_TRACE(1);
 #pragma unroll 1
     while (true) {
-        if (!barrier_done && s >= njobs) {    // this CTA's share of phase 1 is on its way
-            NQ_TRACE(8);
-            barrier_done = true;
-            // No device-wide barrier: phase 2 polls the tagged intermediate itself (load8_tagged).
-            NQ_TRACE(9);
-        }
         if (s >= 2 * njobs) break;
         const Job& jb = job_of(s);
         const int chunks = jb.chunks;
@@ -1007,12 +1000,11 @@ int nq_gemv_group_fwd(const nq_linear_desc* d, int n_linears, int T, int dtype, 
         }
         void* args[] = {&P};
         const void* fn = cg_for(tn) == 1 ? (const void*)gemv_group_kernel<1> : (const void*)gemv_group_kernel<2>;
-        // Cooperative launch (all CTAs co-resident for the device-wide barrier) plus programmatic stream
+        // Cooperative launch (all CTAs co-resident: phase 2 spins on data of other CTAs) plus programmatic stream
         // serialization, so that this kernel's prologue overlaps the previous kernel's tail.  If the driver
         // refuses the combination once, plain cooperative launches are used from then on.
         static bool pdl_ok = true;
-        cudaLaunchConfig_t cfg;
-        memset(&cfg, 0, sizeof(cfg));
+        cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(grid);
         cfg.blockDim = dim3(kGemvThreads);
         cfg.dynamicSmemBytes = smem_for(tn);
