@@ -520,7 +520,7 @@ def gpu_arm(args):
         del step
         torch.cuda.empty_cache()
         out["other_operating_points"] = side_numbers(device, dtype, step_s * 1e3)
-    if not args.no_cpu_baseline:
+    if not args.no_cpu_baseline and world == 1:   # the CPU baseline is reported on rank 0 of a single-GPU run only
         cpu = CpuLayer(T)
         t_layer, reps = cpu.timed(budget_s=12.0)
         out["cpu_baseline"] = {"value": T / (t_layer * LAYERS), "unit": "tokens/s", "cores": cpu.cores,
