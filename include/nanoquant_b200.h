@@ -276,7 +276,8 @@ int nq_linear_fwd(const void* x, const void* s_in, const void* v_tiles, const vo
  * `lm_head`: y[t, v] = sum_k x[t, k] * w[v, k] (+ bias[v]), w [V, N] row-major with `ldw` elements
  * between rows (N % 8 == 0, ldw % 8 == 0, w and x 16-byte aligned), x [T, N] contiguous, y [T, V] with
  * `ldy` elements between tokens, bias nullable, fp32 accumulation, 1 <= T <= nq_dense_gemv_max_tokens()
- * (NQ_ERR_UNSUPPORTED above: use a GEMM).  HBM bound: w is streamed once per call.
+ * (NQ_ERR_UNSUPPORTED above: use a GEMM).  HBM bound: w is streamed once per launch; all tokens of a
+ * launch sit in shared memory, and where 9-16 tokens of a very wide row do not fit they go in two launches.
  * replaces: the nn.Linear `lm_head` call of the HF model forward that the reference's decode loop
  * runs per token (src/nanoquant/kernel/test_decode.py:385-417); lm_head is excluded from quantisation
  * (src/nanoquant/utils/load_utils.py:322). */
