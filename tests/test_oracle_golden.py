@@ -107,3 +107,22 @@ def test_forward_from_packed_roundtrip():
         y2 = oc.forward_from_packed(d["x"], oc.pack_rows(d["V"], method), oc.pack_rows(d["U"], method),
                                     d["s_pre"], d["s_mid"], d["s_post"], 96, 64, 40, method)
         assert np.array_equal(y, y2)
+
+
+def test_dense_forward_is_torch_linear():
+    """The un-quantised head is an ``nn.Linear`` in the reference (``utils/load_utils.py:322``): the oracle's dense
+    forward must be ``torch.nn.functional.linear`` evaluated in float64 on the same bf16 values."""
+    import torch
+
+    g = torch.Generator().manual_seed(7)
+    x = torch.randn((5, 192), generator=g).to(torch.bfloat16)
+    W = (torch.randn((77, 192), generator=g) * 0.05).to(torch.bfloat16)
+    b = torch.randn((77,), generator=g).to(torch.bfloat16)
+    to64 = lambda t: t.float().numpy().astype(np.float64)
+    for bias in (None, b):
+        want = torch.nn.functional.linear(x.double(), W.double(), None if bias is None else bias.double()).numpy()
+        got = oc.dense_forward_fp64(to64(x), to64(W), None if bias is None else to64(bias))
+        assert np.allclose(got, want, rtol=1e-13, atol=1e-15)
+        # and the bf16 module output agrees with it within bf16 rounding
+        y16 = torch.nn.functional.linear(x, W, bias).float().numpy()
+        assert oc.rel_err(y16, got) < 2.0 ** -7
