@@ -803,6 +803,122 @@ def prefill_arm(args):
         "gpu_launches": launches * args.steps, "clocks": clocks}), flush=True)
 
 
+# --------------------------------------------------------------------------------------------
+# single launch group (--mode linear): one linear or one launch group, rotated over copies larger than L2
+# --------------------------------------------------------------------------------------------
+GROUP_SHAPES = {   # name -> [(N, R, M)] of one launch
+    "config1": [(4096, 1536, 4096)],                       # 4096 -> 4096, r = 1536 (0.75 bpw)
+    "qwen3-qkv": [(4096, 1600, 4096), (4096, 608, 1024), (4096, 608, 1024)],
+    "qwen3-o": [(4096, 1600, 4096)],
+    "qwen3-gate-up": [(4096, 2432, 12288)] * 2,
+    "qwen3-down": [(12288, 2432, 4096)],
+    "llama70b-qkv": [(8192, 3232, 8192), (8192, 704, 1024), (8192, 704, 1024)],
+    "llama70b-o": [(8192, 3232, 8192)],
+    "llama70b-gate-up": [(8192, 5056, 28672)] * 2,
+    "llama70b-down": [(28672, 5056, 8192)],
+}
+
+
+def measure_group(shapes, T, dtype, device, steps, resident, profile=False, max_copies=0):
+    """Time of one launch group (us), over `copies` separate weight sets replayed from one CUDA graph (rotated: more
+    than 2 x L2 of packed factors, so every launch streams from HBM) or over one set (L2-resident when it fits)."""
+    import torch
+    from nanoquant_b200 import _lib
+    L = _lib.lib()
+    dt_id = _lib.NQ_BF16 if dtype == torch.bfloat16 else _lib.NQ_F16
+    g = torch.Generator(device=device).manual_seed(0)
+    rnd_bits = lambda rows, cols: torch.randint(-2**31, 2**31 - 1, ((rows + 15) // 16, (cols + 255) // 256, 128),
+                                                generator=g, device=device, dtype=torch.int32)
+    scale = lambda n: ((torch.rand(n, generator=g, device=device) + 0.5) * 0.01).to(dtype)
+    packed = sum(R * (N + M) // 8 for (N, R, M) in shapes)
+    copies = 1 if resident else max(2, int(2 * L2_BYTES // packed) + 1)
+    if max_copies:
+        copies = min(copies, max_copies)
+    use_gemm = T > L.nq_gemv_max_tokens()
+    fwd = L.nq_gemm_group_fwd if use_gemm else L.nq_gemv_group_fwd
+    size_fn = L.nq_gemm_group_scratch_bytes if use_gemm else L.nq_gemv_group_scratch_bytes
+    xs = {N: torch.randn(T, N, generator=g, device=device).to(dtype) for N in {n for (n, _, _) in shapes}}
+    keep, arrs = [], []
+    for _ in range(copies):
+        ds = []
+        for (N, R, M) in shapes:
+            t = dict(v=rnd_bits(R, N), u=rnd_bits(M, R), a=scale(N), b=scale(R), c=scale(M),
+                     y=torch.empty(T, M, device=device, dtype=dtype))
+            keep.append(t)
+            ds.append(_lib.LinearDesc(xs[N].data_ptr(), t["a"].data_ptr(), t["v"].data_ptr(), t["b"].data_ptr(),
+                                      t["u"].data_ptr(), t["c"].data_ptr(), t["y"].data_ptr(), N, R, M, N, M))
+        arrs.append((_lib.LinearDesc * len(ds))(*ds))
+    nbytes = size_fn(arrs[0], len(shapes), T)
+    scratch = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+    reps = 1 if copies > 1 else 8
+
+    def run():
+        st = torch.cuda.current_stream(device).cuda_stream
+        for _ in range(reps):
+            for a in arrs:
+                _lib.check(fwd(a, len(shapes), T, dt_id, scratch.data_ptr(), nbytes, st), "group launch")
+    s = torch.cuda.Stream(device)
+    s.wait_stream(torch.cuda.current_stream(device))
+    with torch.cuda.stream(s):
+        run()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=s):
+            run()
+    torch.cuda.current_stream(device).wait_stream(s)
+    torch.cuda.synchronize(device)
+    for _ in range(3):
+        graph.replay()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize(device)
+    if profile:
+        torch.cuda.profiler.start()
+    e0.record()
+    for _ in range(steps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize(device)
+    if profile:
+        torch.cuda.profiler.stop()
+    if L.nq_scratch_status(scratch.data_ptr(), torch.cuda.current_stream(device).cuda_stream) != 0:
+        raise SystemExit("bench.py: a device-side wait timed out")
+    us = e0.elapsed_time(e1) * 1e3 / (steps * copies * reps)
+    return us, copies, (2 if use_gemm else (T + 3) // 4)
+
+
+def linear_arm(args):
+    """`--mode linear --shape NAME --batch T`: one launch group alone, HBM-streamed (rotated copies) and L2-resident."""
+    import torch
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(device)
+    dtype = torch.float16 if args.dtype == "f16" else torch.bfloat16
+    shapes, T = GROUP_SHAPES[args.shape], args.batch
+    sampler = ClockSampler(device.index or 0)
+    sampler.start()
+    us, copies, launches = measure_group(shapes, T, dtype, device, args.steps, resident=False, profile=True,
+                                         max_copies=args.copies)
+    clocks = sampler.stop()
+    us_l2, _, _ = measure_group(shapes, T, dtype, device, args.steps, resident=True)
+    nbytes = sum(algorithmic_bytes(N, R, M, T) for (N, R, M) in shapes)
+    flops = sum(2.0 * T * R * (N + M) for (N, R, M) in shapes)
+    gemm = T > 4
+    peak, peak_src = (tensor_peak() if gemm else hbm_peak())
+    achieved = flops / us / 1e6 if gemm else nbytes / us / 1e3
+    print(json.dumps({
+        "mode": "linear", "metric": ("launch group TFLOP/s (2*T*R*(N+M))" if gemm else
+                                     "launch group GB/s (algorithmic bytes: packed factors + scales + activations)"),
+        "value": achieved, "unit": "TFLOP/s" if gemm else "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": 3,
+        "us_per_group": us, "us_per_group_l2_resident": us_l2, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": args.dtype, "data": "synthetic",
+        "config": {"workload": f"{args.shape} {shapes}, {T} token(s); {copies} weight sets replayed in turn "
+                               f"({copies * sum(R * (N + M) // 8 for (N, R, M) in shapes) / 1e6:.0f} MB of packed factors)",
+                   "launches_per_group": launches},
+        "roofline": {"bound": "tensor" if gemm else "hbm", "achieved": achieved, "peak": peak,
+                     "unit": "TFLOP/s" if gemm else "GB/s", "frac": achieved / peak, "traffic": None,
+                     "bytes_per_group": nbytes, "peak_source": peak_src,
+                     "l2_resident_achieved": (flops / us_l2 / 1e6 if gemm else nbytes / us_l2 / 1e3)},
+        "gpu_launches": launches * copies * args.steps, "clocks": clocks}), flush=True)
+
+
 def head_arm(args):
     """`--mode head`: the dense GEMV of the un-quantised `lm_head` alone (`--vocab` rows, `--batch` tokens)."""
     import torch
@@ -839,9 +955,12 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-side-numbers", action="store_true",
                     help="skip the short batch-4 / batch-16 / prefill measurements added to the default line")
-    ap.add_argument("--mode", default="replica", choices=["replica", "tp", "prefill", "head"],
+    ap.add_argument("--mode", default="replica", choices=["replica", "tp", "prefill", "head", "linear"],
                     help="replica: the decode step (N > 1: independent replicas); tp: 70B-shaped TP decode step; "
                          "prefill: GEMM TFLOP/s on Llama-2-7B-shaped layers")
+    ap.add_argument("--shape", default="config1", choices=sorted(GROUP_SHAPES), help="launch group of --mode linear")
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "f16"], help="I/O type of --mode linear")
+    ap.add_argument("--copies", type=int, default=0, help="--mode linear: cap on the weight sets (0: enough for 2 x L2)")
     ap.add_argument("--vocab", type=int, default=0, help="rows of the head in --mode head (0: the workload's vocabulary)")
     ap.add_argument("--tokens", type=int, default=2048, help="tokens per GEMM in --mode prefill")
     ap.add_argument("--layers", type=int, default=LAYERS, help="decoder layers resident (fewer only for profiling)")
@@ -862,6 +981,8 @@ def main():
         prefill_arm(args)
     elif args.mode == "head":
         head_arm(args)
+    elif args.mode == "linear":
+        linear_arm(args)
     else:
         gpu_arm(args)
 

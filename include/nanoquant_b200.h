@@ -122,9 +122,14 @@ int nq_tiles_to_rows(const void* tiles, int32_t* packed, int64_t rows, int64_t c
  * Decode GEMV (small T)
  * ------------------------------------------------------------------------ */
 
-/* One quantised linear y[T, M] = s_out * (U . (s_mid * (V . (s_in * x[T, N])))).
+/* One quantised linear y[T, M] = s_out * (U . (s_mid * (V . (s_in * x[T, N])))) + bias + residual.
  * v_tiles / u_tiles are V [R, N] and U [M, R] in the tile layout, s_mid may be
- * NULL; x, y and the scales share one dtype; ldx / ldy are row strides in elements. */
+ * NULL; x, y, the scales, bias and residual share one dtype; ldx / ldy / ldr are row strides in
+ * elements.  bias [M] and residual [T, ldr] may be NULL (zero the struct before filling it); they are
+ * added in fp32 after the output scale and before the saturation, i.e. y = sat(s_out * (...) + bias + residual).
+ * bias matches the add of src/nanoquant/modules/linear.py:148-149, which the reference's kernel branches
+ * (linear.py:121-141) leave out; the residual is the decoder layer's skip connection.
+ * residual may alias y (each output element is read, then written, by one thread). */
 typedef struct {
     const void* x;
     const void* s_in;
@@ -135,6 +140,9 @@ typedef struct {
     void* y;
     int N, R, M;
     int64_t ldx, ldy;
+    const void* bias;
+    const void* residual;
+    int64_t ldr;
 } nq_linear_desc;
 
 /* Bytes of scratch nq_gemv_fwd / nq_gemv_group_fwd need (0 on invalid sizes). */
@@ -189,8 +197,17 @@ size_t nq_gemv_static_max_rank(void);
 
 /* Synchronises `stream` and returns the status word of a scratch buffer:
  * NQ_OK, or NQ_ERR_TIMEOUT when a device-wide wait of an earlier launch gave up
- * (the scratch must then be zeroed again before reuse). */
+ * (the scratch must then be zeroed again before reuse; until then launches on it do
+ * not spin at all and their results are void).  scratch == NULL reports the array of
+ * nq_gemv_fwd_static on the current device. */
 int nq_scratch_status(const void* scratch, nq_stream_t stream);
+
+/* Number of polls a wait for the tagged intermediate may spend before it gives up
+ * (per thread and launch: after its first expiry a thread does not spin again).
+ * 0 restores the default (4e6, seconds).  Host-side setting read at launch time;
+ * returns the previous value.  For failure-path tests and for callers that want a
+ * tighter bound. */
+unsigned nq_gemv_set_wait_limit(unsigned polls);
 
 /* ------------------------------------------------------------------------ *
  * Prefill GEMM (many tokens) on tcgen05 / tensor memory

@@ -27,7 +27,8 @@ class LinearDesc(ctypes.Structure):
     """``nq_linear_desc``."""
     _fields_ = [("x", c_void_p), ("s_in", c_void_p), ("v_tiles", c_void_p), ("s_mid", c_void_p),
                 ("u_tiles", c_void_p), ("s_out", c_void_p), ("y", c_void_p),
-                ("N", c_int), ("R", c_int), ("M", c_int), ("ldx", c_int64), ("ldy", c_int64)]
+                ("N", c_int), ("R", c_int), ("M", c_int), ("ldx", c_int64), ("ldy", c_int64),
+                ("bias", c_void_p), ("residual", c_void_p), ("ldr", c_int64)]
 
 
 # name -> (restype, argtypes); every symbol declared in include/nanoquant_b200.h
@@ -49,6 +50,7 @@ SIGNATURES = {
     "nq_gemv_fwd": (c_int, [c_void_p] * 8 + [c_size_t, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "nq_gemv_group_fwd": (c_int, [ctypes.POINTER(LinearDesc), c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "nq_scratch_status": (c_int, [c_void_p, c_void_p]),
+    "nq_gemv_set_wait_limit": (ctypes.c_uint, [ctypes.c_uint]),
     "nq_gemv_fwd_static": (c_int, [c_void_p] * 7 + [c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "nq_gemv_static_max_rank": (c_size_t, []),
     "nq_gemm_scratch_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),

@@ -57,26 +57,43 @@ int sm_count();
 // alone.  Waits are bounded: on expiry a status word is set and the thread goes on with what it has (the
 // host reports the status).
 constexpr unsigned kTagSpan = 1024u;        // > CTAs per tagged launch
-constexpr unsigned kSpinLimit = 4000000u;   // polls before a wait gives up
+constexpr unsigned kSpinLimit = 4000000u;   // default number of polls before a wait gives up
 struct TagCtx {
     unsigned tag;        // tag of this launch
-    unsigned* status;    // device status word
+    unsigned limit;      // polls a wait of this thread may still spend; 0 after an expiry (sticky: one missing
+                         // producer costs every thread one limit, not one limit per element it waits for)
+    unsigned* status;    // device status word (header word 2)
+    unsigned begun;      // tag and status have been read
 };
-__device__ __forceinline__ unsigned launch_tag(const unsigned long long* counter) {
+// Reads the launch tag and the status word of the scratch header.  Issue it AFTER the first data loads of the
+// kernel: its results are first needed when a tag is compared or stored, so the round trips overlap.  A status
+// left by an earlier expiry on this scratch disables spinning altogether (the data of such a launch is void anyway).
+__device__ __forceinline__ void tag_begin(TagCtx& tc, unsigned* header, unsigned limit) {
     unsigned long long c;
-    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(c) : "l"(counter) : "memory");
-    return 0x7FF00000u | ((unsigned)(c / kTagSpan) & 0xFFFFFu);
+    unsigned st;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(c) : "l"(header) : "memory");
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(st) : "l"(header + 2) : "memory");
+    tc.tag = 0x7FF00000u | ((unsigned)(c / kTagSpan) & 0xFFFFFu);
+    tc.limit = st ? 0u : limit;
+    tc.status = header + 2;
+    tc.begun = 1u;
+}
+__device__ __forceinline__ void tag_wait_expired(TagCtx& tc) {
+    atomicExch(tc.status, (unsigned)(-NQ_ERR_TIMEOUT));
+    tc.limit = 0u;
 }
 // This CTA's arrival at the counter.  Issued by one thread, once per launch, after a CTA barrier that every
-// thread passes behind its own launch_tag() read: the arrival that completes the span would otherwise show
+// thread passes behind its own tag_begin() read: the arrival that completes the span would otherwise show
 // the next launch's tag to a thread of the same CTA that reads late.
 __device__ __forceinline__ void launch_arrive(unsigned long long* counter, bool first_cta, unsigned n_ctas) {
     const unsigned long long w = first_cta ? (unsigned long long)(kTagSpan - (n_ctas - 1)) : 1ull;
     asm volatile("red.relaxed.gpu.global.add.u64 [%0], %1;" ::"l"(counter), "l"(w) : "memory");
 }
+// One 64-bit scalar store: value and tag become visible together (a vector store of two 32-bit words would be two
+// accesses in the memory model).
 __device__ __forceinline__ void store_tagged(void* base, long long i, float val, unsigned tag) {
-    asm volatile("st.relaxed.gpu.global.v2.u32 [%0], {%1,%2};"
-                 ::"l"(static_cast<uint2*>(base) + i), "r"(__float_as_uint(val)), "r"(tag) : "memory");
+    const unsigned long long w = ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(val);
+    asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" ::"l"(static_cast<unsigned long long*>(base) + i), "l"(w) : "memory");
 }
 
 // ---------------------------------------------------------------------------
