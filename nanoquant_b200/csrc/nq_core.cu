@@ -31,7 +31,7 @@ int sm_count() {
 
 extern "C" {
 
-int nq_abi_version(void) { return 1; }
+int nq_abi_version(void) { return 2; }
 
 const char* nq_strerror(int status) {
     switch (status) {

@@ -1,41 +1,45 @@
 // Decode GEMV for the binary low-rank linear, one launch per group of linears.
 //
-//   y = s_out * (U . (s_mid * (V . (s_in * x)))) (+ bias) (+ residual)        T <= 4 tokens per launch
+//   y = s_out * (U . (s_mid * (V . (s_in * x))))          T <= 4 tokens per launch
 //
-// The kernel is bound by the HBM stream of the packed factors and, for the layer sizes of 8B-class
-// decoders, by a chain of dependent latencies (memory round trips of 0.4-0.9 us each, CTA barriers).
+// The kernel is bound by the HBM stream of the packed factors and, for the layer
+// sizes of 8B-class decoders, by latency; both call for as few instructions per
+// weight and per phase as possible.
 //
-//  * The packed sign bits are the A operand of an integer tensor-core MMA (mma.sync m16n8k32
-//    s8*s8->s32) WITHOUT unpacking: in the tile layout (see nq_rows_to_tiles)
-//    `word & (0x01010101 << j)` is an int8x4 register with values {0, 2^j} ({0, -128} for j = 7), so
-//    one LOP3 prepares four weights and the eight masks j = 0..7 consume a whole 32-bit word.  Columns
-//    [32j, 32j+32) of a 256-column chunk form the "class" j.
-//  * The input vector of a phase (s_in*x, or the rank-R intermediate t) is turned, once per CTA, into
-//    17-bit fixed point X with a per-token scale.  A column of class j is stored as X * 2^(7-j)
-//    (negated for j = 7), split into three signed bytes.  The product of the A value 2^j and that
-//    operand is 2^7 * X for every class, so all eight masks accumulate into ONE accumulator per output
-//    row and byte term.  The three byte terms of a token are three of the N = 8 MMA columns.
-//  * sum(+-X) = sum(X) - 2 * sum_{bit=1}(X).  All accumulation is exact int32 / int64, so a result does
-//    not depend on how rows are dealt to warps, CTAs or launches.
+//  * The packed sign bits are the A operand of an integer tensor-core MMA
+//    (mma.sync m16n8k32 s8*s8->s32) WITHOUT unpacking: in the tile layout (see
+//    nq_rows_to_tiles) `word & (0x01010101 << j)` is an int8x4 register with values
+//    {0, 2^j} ({0, -128} for j = 7), so one LOP3 prepares four weights and the eight
+//    masks j = 0..7 consume a whole 32-bit word.  Columns [32j, 32j+32) of a
+//    256-column chunk form the "class" j.
+//  * The input vector of a phase (s_in*x, or the rank-R intermediate t) is turned,
+//    once per CTA, into 17-bit fixed point X with a per-token scale.  A column of
+//    class j is stored as X * 2^(7-j) (negated for j = 7), split into three signed
+//    bytes.  The product of the A value 2^j and that operand is 2^7 * X for every
+//    class, so all eight masks accumulate into ONE accumulator per output row and
+//    byte term.  The three byte terms of a token are three of the N = 8 MMA columns.
+//  * sum(+-X) = sum(X) - 2 * sum_{bit=1}(X).  All accumulation is exact int32 /
+//    int64, so the result does not depend on the order in which warps add up.
 //
-// A SIMT sign-flip-add inner loop issues ~1.5 instructions per weight and tops out near one third of
-// the HBM rate on this part, which is why the integer MMA is used as a wide dot-product unit here.
+// A SIMT sign-flip-add inner loop issues ~1.5 instructions per weight and tops out
+// near one third of the HBM rate on this part, which is why the integer MMA is
+// used as a wide dot-product unit here.
 //
-// Launch structure.  Phase 1 computes t[T,R] (fp32), phase 2 computes y; the linears of a group (q/k/v,
-// gate/up) go through both phases together.  In each phase every linear gets a contiguous range of CTAs
-// in proportion to its packed bytes and a CTA owns a contiguous range of 16-row groups of ONE linear, so
-// it prepares one input vector per phase.  A CTA's (row unit, 256-column chunk) items are cut into one
-// contiguous range per warp and streamed through a per-warp cp.async ring; partial sums meet in shared
-// memory.  There is no device-wide barrier between the phases: every element of t is stored as one
-// 64-bit {value, launch tag} word and phase 2 polls the elements it needs until they carry this launch's
-// tag (nq_common.cuh); the poll is bounded and an expiry is sticky.  The launch is cooperative (consumers
-// spin on data of CTAs that must be resident) with programmatic stream serialization: the descriptor
-// reads, an L2 prefetch of ALL packed bytes this CTA will read in both phases, the first ring loads and
-// the output scales run before griddepcontrol.wait, i.e. under the tail of the previous kernel, and the
-// HBM stream of the factors overlaps the latency chain that follows.
+// Phases: phase 1 computes t[T,R] (fp32, in scratch), phase 2 computes y.  Several
+// linears that share the two phases (q/k/v, gate/up) are processed in one launch.
+// There is no device-wide barrier between the phases: every element of t is stored
+// together with a tag of the launch and phase 2 polls the elements it needs until
+// they carry this launch's tag (see tag_begin / load8_tagged); the poll is bounded:
+// on expiry a status word is set and the thread goes on.  The weight stream of the
+// next job is started before that wait, so it overlaps with HBM traffic.  The kernel
+// is launched cooperative (all CTAs resident: consumers spin on other CTAs' data) and
+// with programmatic stream serialization: everything that does not depend on the
+// previous kernel (descriptor copy, first weight loads, an L2 prefetch of the input
+// scales) runs before griddepcontrol.wait.
 //
-// Everything a loop needs lives in registers: a shared-memory or parameter read behind an `asm volatile`
-// with a memory clobber is re-issued every iteration.
+// For 8B-class layers the kernel is a chain of dependent latencies (memory round
+// trips, CTA barriers, the hand-over of t between the phases), not a bandwidth problem; the code
+// between the main loops is therefore kept short and free of divisions.
 //
 // replaces: src/nanoquant/kernel/cuda/gemv_kernel.cu:43-301 of the reference
 // (two kernels per linear, fp16/bf16 accumulation, sign-flip adds).
@@ -45,95 +49,69 @@
 
 namespace nq {
 
-constexpr int kGemvThreads = 512;
+#ifndef NQ_GEMV_THREADS
+#define NQ_GEMV_THREADS 512
+#endif
+#ifndef NQ_GEMV_STAGES
+#define NQ_GEMV_STAGES 4
+#endif
+#ifndef NQ_GEMV_MIN_CTAS
+#define NQ_GEMV_MIN_CTAS 1
+#endif
+constexpr int kGemvThreads = NQ_GEMV_THREADS;
 constexpr int kGemvWarps = kGemvThreads / 32;
 constexpr int kMaxJobs = 4;         // linears per launch
 constexpr int kMaxTok = 4;          // tokens per launch (3 byte terms each, 8 MMA columns per column group)
 constexpr int kQMax = 64000;        // |X| bound: X * 2^7 splits into three signed bytes
 constexpr int kMaxK = 32768;        // keeps sum(X) and every accumulator inside int32
-#ifndef NQ_GEMV_STAGES
-#define NQ_GEMV_STAGES 4
-#endif
 constexpr int kStages = NQ_GEMV_STAGES;          // 1 KB weight slots in flight per warp
-constexpr size_t kStateBytes = 256;              // per-phase maxima, sums and units
+constexpr size_t kRedBytes = 384;   // per-warp maxima: kMaxTok * kGemvWarps floats (16-byte aligned rows)
+constexpr size_t kFixedBytes = 512;
 constexpr size_t kRingBytes = (size_t)kGemvWarps * kStages * 1024;
 constexpr size_t kHeaderBytes = 256;
 
-// KIND_T: the rank-R intermediate between the phases, one 64-bit {fp32 value, launch tag} word per element
+// KIND_T: the rank-R intermediate between the phases, one 8-byte {fp32 value, launch tag} pair per element
 enum : int { KIND_F16 = 0, KIND_BF16 = 1, KIND_T = 2 };
 
-#ifdef NQ_GEMV_TRACE  // development aid: per-warp (id, globaltimer, clock) records of the phase steps
-__device__ unsigned long long g_trace[148 * 16 * 32 * 2];
-__device__ __forceinline__ void trace_mark(int id) {
-    __shared__ int s_n[16];
-    if ((threadIdx.x & 31) == 0) {
-        const int w = threadIdx.x >> 5;
-        unsigned long long t, c;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        asm volatile("mov.u64 %0, %%clock64;" : "=l"(c));
-        const int n = id == 0 ? 0 : s_n[w];
-        if (n < 32) {
-            unsigned long long* r = g_trace + ((size_t)(blockIdx.x * 16 + w) * 32 + n) * 2;
-            r[0] = (t << 8) | (unsigned)id; r[1] = c;
-            s_n[w] = n + 1;
-            if (n + 1 < 32) r[2] = 0;
-        }
-    }
-}
-#define NQ_TRACE(id) trace_mark(id)
-#else
-#define NQ_TRACE(id) ((void)0)
-#endif
-
-// One linear in one phase.  Lives in the kernel parameters; every CTA reads the descriptor of the job it
-// works on with uniform accesses into registers.
-struct JobDesc {
+struct Job {
     const uint4* tiles;   // [row_groups][chunks][32]
-    const void* in;       // [T, ld_in] fp16/bf16 (phase 1) or tagged fp32 (phase 2)
+    const void* in;       // [T, ld_in]  fp16/bf16 (phase 1) or fp32 (phase 2)
     const void* pre;      // [K] scale in the I/O dtype, or nullptr
     const void* post;     // [rows] scale in the I/O dtype, or nullptr
-    void* out;            // [T, ld_out] tagged fp32 (phase 1) or fp16/bf16 (phase 2)
+    void* out;            // [T, ld_out] fp32 (phase 1) or fp16/bf16 (phase 2)
     const void* bias;     // [rows] in the I/O dtype or nullptr (phase 2)
     const void* resid;    // [T, ld_res] in the I/O dtype or nullptr (phase 2)
     long long ld_in, ld_out, ld_res;
     int rows, K;
     int chunks;           // ceil(K / 256)
-    int cta0, ncta;       // CTAs [cta0, cta0 + ncta) work on this job
-    int rg_q, rg_r;       // 16-row groups per CTA: rg_q, one more for the first rg_r CTAs of the range
+    int items;            // ceil(rows / 32)
     int in_kind, out_kind;
     int vec;              // rows of `in` / `pre` are 16-byte aligned and K % 8 == 0
-    int post_vec;         // `post` (and `bias`) 16-byte aligned and rows % 8 == 0: staged in shared memory
+    int tile_start;       // index of this job's row tile 0 in the phase's flattened tile list
+    int post_vec;         // `post` is 16-byte aligned and rows % 8 == 0: staged in shared memory with 16-byte copies
+};
+
+struct Phase {
+    Job job[kMaxJobs];
+    int njobs;
+    int total_tiles;      // row tiles (32 rows) of all jobs of the phase
+    int tiles_q, tiles_r; // total_tiles = tiles_q * gridDim.x + tiles_r: CTA b owns tiles_q (+1 if b < tiles_r) tiles
 };
 
 struct GemvParams {
-    JobDesc job[2][kMaxJobs];
+    Phase phase[2];
     unsigned* header;     // [0..1] 64-bit arrival counter (launch tags), [2] status
-    int njobs;
+    unsigned spin_limit;  // polls before a wait for the tagged intermediate gives up
     int T;
     int scale_kind;       // dtype of the scale vectors (KIND_F16 / KIND_BF16)
     int xq_stride;        // bytes between the int8 vectors in shared memory
-    int rows_cap[2];      // most rows (16 per row group) a CTA owns in a phase
-    unsigned spin_limit;  // polls before a wait for the tagged intermediate gives up
-};
-
-// The job descriptor fields the device code uses, in registers.
-struct Work {
-    const uint4* tiles;
-    const void* in;
-    const void* pre;
-    const void* post;
-    void* out;
-    const void* bias;
-    const void* resid;
-    long long ld_in, ld_out, ld_res;
-    int rows, K, chunks;
-    int in_kind, out_kind, vec, post_vec;
-    int rg0, cnt;         // this CTA's row groups: first, count (0: no work in this phase)
+    int max_items;        // row tiles a CTA may own per job
 };
 
 __device__ __forceinline__ float load_as_float(const void* p, long long i, int kind) {
     if (kind == KIND_F16) return __half2float(static_cast<const __half*>(p)[i]);
-    return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
+    if (kind == KIND_BF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
+    return 0.f;   // the tagged intermediate goes through load1_tagged / load8_tagged
 }
 
 __device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -143,7 +121,8 @@ __device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, ui
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// Eight tagged elements (64 bytes) as floats, polled until all eight carry this launch's tag.
+// Eight tagged elements (64 bytes) as floats, polled until all eight carry this launch's tag.  Every element is
+// one 64-bit word {value, tag}: a 64-bit access is single-copy atomic, so a matching tag implies its value.
 __device__ __forceinline__ void load8_tagged(const void* base, long long i, float (&v)[8], TagCtx& tc) {
     const unsigned long long* p = static_cast<const unsigned long long*>(base) + i;
     unsigned long long e[8];
@@ -172,24 +151,69 @@ __device__ __forceinline__ float load1_tagged(const void* base, long long i, Tag
     return __uint_as_float((unsigned)e);
 }
 
-// Eight consecutive 16-bit elements as floats.
+// Eight consecutive elements of a vector as floats (one or two 128-bit loads).
 template <int KIND>
-__device__ __forceinline__ void to_float8(const uint4& u, float (&v)[8]) {
-    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+__device__ __forceinline__ void load8(const void* base, long long i, float (&v)[8], TagCtx& tc) {
+    if (KIND == KIND_T) {
+        load8_tagged(base, i, v, tc);
+    } else {
+        const uint4 u = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(base) + i);
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-        if (KIND == KIND_F16) {
-            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[e]));
-            v[2 * e] = f.x; v[2 * e + 1] = f.y;
-        } else {  // bf16 -> fp32 is a 16-bit shift
-            v[2 * e] = __uint_as_float(w[e] << 16);
-            v[2 * e + 1] = __uint_as_float(w[e] & 0xFFFF0000u);
+        for (int e = 0; e < 4; ++e) {
+            if (KIND == KIND_F16) {
+                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[e]));
+                v[2 * e] = f.x; v[2 * e + 1] = f.y;
+            } else {  // bf16 -> fp32 is a 16-bit shift
+                v[2 * e] = __uint_as_float(w[e] << 16);
+                v[2 * e + 1] = __uint_as_float(w[e] & 0xFFFF0000u);
+            }
         }
     }
 }
 
-// Class-shifted operand of column k: X * 2^(7-j), negated for j = 7, j = (k % 256) / 32, as a multiplier.
-__device__ __forceinline__ int class_mult(int j) { return (j == 7) ? -1 : (1 << (7 - j)); }
+// The launch tag is read behind the first input loads of the kernel (see tag_begin).
+__device__ __forceinline__ void tag_ensure(TagCtx& tc) {
+    if (!tc.begun) tag_begin(tc, tc.status - 2, tc.limit);
+}
+
+// The same split in two: the raw 128-bit loads of a block (so that several blocks can be in flight before
+// the first conversion) and the conversion.
+template <int KIND>
+struct Raw8 { uint4 a, b; };   // b: second half of an fp32 block
+template <int KIND>
+__device__ __forceinline__ void load_raw(const void* base, long long i, Raw8<KIND>& r, TagCtx& tc) {
+    if (KIND == KIND_T) {   // tagged pairs are polled until valid; the block keeps the eight values
+        float v[8];
+        load8_tagged(base, i, v, tc);
+        r.a = make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]), __float_as_uint(v[2]), __float_as_uint(v[3]));
+        r.b = make_uint4(__float_as_uint(v[4]), __float_as_uint(v[5]), __float_as_uint(v[6]), __float_as_uint(v[7]));
+    } else {
+        r.a = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(base) + i);
+    }
+}
+template <int KIND>
+__device__ __forceinline__ void to_float8(const Raw8<KIND>& r, float (&v)[8]) {
+    if (KIND == KIND_T) {
+        v[0] = __uint_as_float(r.a.x); v[1] = __uint_as_float(r.a.y); v[2] = __uint_as_float(r.a.z); v[3] = __uint_as_float(r.a.w);
+        v[4] = __uint_as_float(r.b.x); v[5] = __uint_as_float(r.b.y); v[6] = __uint_as_float(r.b.z); v[7] = __uint_as_float(r.b.w);
+    } else {
+        const uint32_t w[4] = {r.a.x, r.a.y, r.a.z, r.a.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            if (KIND == KIND_F16) {
+                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[e]));
+                v[2 * e] = f.x; v[2 * e + 1] = f.y;
+            } else {
+                v[2 * e] = __uint_as_float(w[e] << 16);
+                v[2 * e + 1] = __uint_as_float(w[e] & 0xFFFF0000u);
+            }
+        }
+    }
+}
+
+// Class-shifted operand of column k: X * 2^(7-j), negated for j = 7, j = (k % 256) / 32.
+__device__ __forceinline__ int class_shift(int X, int j) { return (j == 7) ? -X : (X << (7 - j)); }
 
 // Byte offset of column k inside an int8 vector: chunk base + 32*j + 8*q + 4*h + b for
 // k % 256 = 32*j + 16*h + 4*q + b, so that lane (g, q) fetches the two B registers
@@ -199,561 +223,612 @@ __device__ __forceinline__ int xq_pos(int k) {
     return (k & ~255) + (kin & 0xE0) + 2 * (kin & 12) + ((kin & 16) >> 2) + (kin & 3);
 }
 
-// Units per value (0 when the maximum is zero, tiny or not finite: everything quantises to zero).
-__device__ __forceinline__ float scale_from_max(float m, float& unit) {
-    const bool good = (m > 1.0e-30f) && (m < 3.0e38f);
-    unit = good ? m * (1.0f / (float)kQMax) : 0.f;
-    // |p * inv| <= kQMax * (1 + 2^-21): the reciprocal is good to 1 ulp and the products round once each
-    float r;
-    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(m));
-    return good ? (float)kQMax * r : 0.f;
-}
-
-// Z = Y + 0x808080 has the bytes b_t + 128 of the signed byte terms Y = b0 + 256 b1 + 65536 b2
-// (|Y| < 2^23).  Four columns -> the three term words (column-major bytes), sign bit flipped back.
-__device__ __forceinline__ void store_terms4(uint32_t z0, uint32_t z1, uint32_t z2, uint32_t z3, int8_t* dst,
-                                             int stride) {
-    const uint32_t t0 = __byte_perm(z0, z1, 0x5140), t1 = __byte_perm(z0, z1, 0x0062);
-    const uint32_t t2 = __byte_perm(z2, z3, 0x5140), t3 = __byte_perm(z2, z3, 0x0062);
-    *reinterpret_cast<uint32_t*>(dst) = __byte_perm(t0, t2, 0x5410) ^ 0x80808080u;
-    *reinterpret_cast<uint32_t*>(dst + stride) = __byte_perm(t0, t2, 0x7632) ^ 0x80808080u;
-    *reinterpret_cast<uint32_t*>(dst + 2 * stride) = __byte_perm(t1, t3, 0x5410) ^ 0x80808080u;
-}
-
-// Shared state of one phase (separate copies per phase: nothing has to be cleared between the jobs).
-struct PhaseState {
-    unsigned smax[kMaxTok];   // per-token max |input| as float bits (non-negative floats order like integers)
-    int sumx[kMaxTok];        // per-token sum of the fixed-point values
-    float unit[kMaxTok];      // value of one fixed-point unit
-    unsigned pad[4];
-};
-
-// Eight columns of one token: products in, three byte vectors out; returns the sum of the fixed-point values.
-__device__ __forceinline__ int convert8(const float (&p)[8], float inv, int k8, int8_t* row0, int stride) {
-    const int mult = class_mult((k8 >> 5) & 7);
-    uint32_t z[8];
-    int acc = 0;
+// red[t * kGemvWarps + warp] holds the per-warp maxima of token t.  Every thread derives the fixed-point
+// scale of its token from them itself (a few broadcast reads), which saves a serial step and a CTA barrier.
+__device__ __forceinline__ float token_max(const float* red, int t) {
+    const float4* r = reinterpret_cast<const float4*>(red + t * kGemvWarps);
+    float m = 0.f;
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-        const int X = __float2int_rn(p[e] * inv);
-        acc += X;
-        z[e] = (uint32_t)(X * mult + 0x808080);
+    for (int i = 0; i < kGemvWarps / 4; ++i) {
+        const float4 v = r[i];
+        m = fmaxf(m, fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)));
     }
-    int8_t* dst = row0 + xq_pos(k8);
-    store_terms4(z[0], z[1], z[2], z[3], dst, stride);
-    store_terms4(z[4], z[5], z[6], z[7], dst + 8, stride);
-    return acc;
+    return m;
+}
+// Units per value (0 when the maximum is zero or not finite: everything quantises to zero); the thread
+// for which `writer` holds records the value of one unit for the epilogue.
+__device__ __forceinline__ float token_inv(const float* red, int t, bool writer, float* delta) {
+    const float m = token_max(red, t);
+    const bool good = (m > 0.f) && (m < 3.0e38f);
+    // A rounded reciprocal times kQMax instead of a division: every thread computes the same value,
+    // |p * inv| stays within kQMax (1 + 2^-22), and the unit differs from 1 / inv by a relative 2^-22 at most.
+    if (writer) delta[t] = good ? m * (1.0f / (float)kQMax) : 0.f;
+    return good ? (float)kQMax * __frcp_rn(m) : 0.f;
+}
+// Warp-wide maximum of non-negative floats / sum of ints with one reduction instruction each.
+__device__ __forceinline__ float warp_max_abs(float m) {
+    return __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(m)));
+}
+
+// Write eight class-shifted operands (columns k8..k8+7 of one token) as three byte vectors.
+__device__ __forceinline__ void store_terms(const uint32_t (&Y)[8], int8_t* r0, int stride, int k8) {
+    // Y = 65536*b2 + 256*b1 + b0 with signed bytes: b0 = byte 0 of Y, b1 = byte 1 of
+    // Y + 0x80, b2 = byte 2 of Y + 0x8080
+    const int pos = xq_pos(k8);
+#pragma unroll
+    for (int w = 0; w < 2; ++w) {
+        const uint32_t y0 = Y[4 * w], y1 = Y[4 * w + 1], y2 = Y[4 * w + 2], y3 = Y[4 * w + 3];
+        const uint32_t z0 = y0 + 0x80u, z1 = y1 + 0x80u, z2 = y2 + 0x80u, z3 = y3 + 0x80u;
+        const uint32_t u0 = y0 + 0x8080u, u1 = y1 + 0x8080u, u2 = y2 + 0x8080u, u3 = y3 + 0x8080u;
+        const uint32_t b0 = __byte_perm(__byte_perm(y0, y1, 0x0040), __byte_perm(y2, y3, 0x0040), 0x5410);
+        const uint32_t b1 = __byte_perm(__byte_perm(z0, z1, 0x0051), __byte_perm(z2, z3, 0x0051), 0x5410);
+        const uint32_t b2 = __byte_perm(__byte_perm(u0, u1, 0x0062), __byte_perm(u2, u3, 0x0062), 0x5410);
+        *reinterpret_cast<uint32_t*>(r0 + pos + 8 * w) = b0;
+        *reinterpret_cast<uint32_t*>(r0 + stride + pos + 8 * w) = b1;
+        *reinterpret_cast<uint32_t*>(r0 + 2 * stride + pos + 8 * w) = b2;
+    }
 }
 
 // Quantise the input vectors of a job into shared memory.
-//   xq: 3*T int8 vectors (row 3*tok + term, term 0 = least significant byte), `stride` bytes apart,
-//       columns in xq_pos() order; columns K..Kpad are zero.
-//   ps.sumx[tok]: sum of the (unshifted) fixed-point values, ps.unit[tok]: value of one unit.
-// Register path: at most NB blocks of eight columns per thread; every value is loaded once, with all loads
-// of the thread in flight together, and stays in registers between the max pass and the conversion.
-// Block f = tid + i * threads covers token f / nv8, columns (f % nv8) * 8; nv8 is a multiple of 32, so a
-// warp's block belongs to one token.
-template <int IN_KIND, int NB>
-__device__ __noinline__ void quantise_regs(const void* in, long long ld_in, const void* pre, int K, int chunks, int T,
-                                           int8_t* xq, int stride, PhaseState* ps, TagCtx* tcp) {
-    const int tid = threadIdx.x, lane = tid & 31;
-    const int nv8 = chunks * 32, items = T * nv8;
-    constexpr bool kHasPre = (IN_KIND != KIND_T);
-    TagCtx tc = *tcp;
-    float p[NB][8];
-    int tt[NB], kk[NB];
-    uint4 xr[NB], sr[NB];
-#pragma unroll
-    for (int i = 0; i < NB; ++i) {
-        const int f = tid + i * kGemvThreads;
-        const int t = (f >= nv8) + (f >= 2 * nv8) + (f >= 3 * nv8);
-        tt[i] = f < items ? t : -1;
-        kk[i] = (f - t * nv8) * 8;
-        xr[i] = sr[i] = make_uint4(0u, 0u, 0u, 0u);
-        if (kHasPre && tt[i] >= 0 && kk[i] < K) {
-            xr[i] = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(in) + t * ld_in + kk[i]);
-            sr[i] = __ldg(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(pre) + kk[i]));
-        }
-    }
-    if (!tc.begun) tag_begin(tc, tc.status - 2, tc.limit);   // behind the input loads: the round trips overlap
-    float wm[kMaxTok];   // this warp's maximum per token
-#pragma unroll
-    for (int t = 0; t < kMaxTok; ++t) wm[t] = 0.f;
-#pragma unroll
-    for (int i = 0; i < NB; ++i) {
-        if (kHasPre) {
-            float s[8];
-            to_float8<IN_KIND>(xr[i], p[i]);
-            to_float8<IN_KIND>(sr[i], s);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) p[i][e] *= s[e];
-        } else {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) p[i][e] = 0.f;
-            if (tt[i] >= 0 && kk[i] < K) load8_tagged(in, tt[i] * ld_in + kk[i], p[i], tc);
-        }
-        float m = 0.f;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) m = fmaxf(m, fabsf(p[i][e]));
-#pragma unroll
-        for (int t = 0; t < kMaxTok; ++t) wm[t] = tt[i] == t ? fmaxf(wm[t], m) : wm[t];
-    }
-#pragma unroll
-    for (int t = 0; t < kMaxTok; ++t) {
-        if (t < T) {
-            const unsigned r = __reduce_max_sync(0xffffffffu, __float_as_uint(wm[t]));
-            if (lane == 0 && r != 0u) atomicMax(&ps->smax[t], r);
-        }
-    }
-    asm volatile("" ::"r"(tc.tag));   // the tag has arrived in this thread before the CTA can arrive at the counter
-    NQ_TRACE(2);
-    __syncthreads();
-    NQ_TRACE(3);
-#pragma unroll
-    for (int i = 0; i < NB; ++i) {
-        if (tt[i] >= 0) {      // warp-uniform
-            float unit;
-            const float inv = scale_from_max(__uint_as_float(ps->smax[tt[i]]), unit);
-            if (kk[i] == 0) ps->unit[tt[i]] = unit;
-            int acc = convert8(p[i], inv, kk[i], xq + (3 * tt[i]) * stride, stride);
-            acc = __reduce_add_sync(0xffffffffu, acc);
-            if (lane == 0 && acc != 0) atomicAdd(&ps->sumx[tt[i]], acc);
-        }
-    }
-    *tcp = tc;
-    NQ_TRACE(4);
-    __syncthreads();
-}
-
-// Loop path for wider inputs (still 16-byte aligned rows, K % 8 == 0): two passes over the input, four blocks
-// of a thread in flight; the second pass finds 16-bit inputs in L1 and the tagged intermediate valid.
+//   xq: 3*T int8 vectors (row 3*tok + term, term 0 = least significant byte), `stride`
+//       bytes apart, columns in xq_pos() order; columns K..Kpad are zero.
+//   sumx[tok]: sum of the (unshifted) fixed-point values, delta[tok]: value of one unit.
+// The code is kept as small loops on purpose: it runs once per phase, where
+// instruction fetch and latency, not arithmetic, set the pace.
+//
+// Vector path: rows of `in` / `pre` 16-byte aligned, K % 8 == 0; eight columns per thread and step.
 template <int IN_KIND>
-__device__ __noinline__ void quantise_loop(const void* in, long long ld_in, const void* pre, int K, int chunks, int T,
-                                           int8_t* xq, int stride, PhaseState* ps, TagCtx* tcp) {
-    const int tid = threadIdx.x, lane = tid & 31;
-    const int Kpad = chunks * 256;
+__device__ __noinline__ void quantise_vec(const Job& jb, int T, int8_t* xq, int stride, float* red,
+                                          int* sumx, float* delta, TagCtx& tc) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int K = jb.K, Kpad = jb.chunks * 256;
     constexpr bool kHasPre = (IN_KIND != KIND_T);
-    constexpr int kBatch = 4;
-    constexpr int kStep = kGemvThreads * 8;
-    TagCtx tc = *tcp;
-    if (!tc.begun) tag_begin(tc, tc.status - 2, tc.limit);
-    auto load_products = [&](int t, int k0, float (&p)[kBatch][8]) {
-        uint4 xr[kBatch], sr[kBatch];
-#pragma unroll
-        for (int u = 0; u < kBatch; ++u) {
-            const int k8 = k0 + u * kStep;
-            xr[u] = sr[u] = make_uint4(0u, 0u, 0u, 0u);
-            if (kHasPre && k8 < K) {
-                xr[u] = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(in) + t * ld_in + k8);
-                sr[u] = __ldg(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(pre) + k8));
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < kBatch; ++u) {
-            const int k8 = k0 + u * kStep;
-            if (kHasPre) {
-                float s[8];
-                to_float8<IN_KIND>(xr[u], p[u]);
-                to_float8<IN_KIND>(sr[u], s);
-#pragma unroll
-                for (int e = 0; e < 8; ++e) p[u][e] *= s[e];
-            } else {
-#pragma unroll
-                for (int e = 0; e < 8; ++e) p[u][e] = 0.f;
-                if (k8 < K) load8_tagged(in, t * ld_in + k8, p[u], tc);
-            }
-        }
-    };
+    constexpr int kBatch = 4;                       // blocks whose loads are issued before the first use:
+    constexpr int kStep = kGemvThreads * 8;         // one memory round trip per batch instead of one per block
+    tag_ensure(tc);
+    // pass 1: per-token max |in * pre|
 #pragma unroll 1
     for (int t = 0; t < T; ++t) {
         float m = 0.f;
 #pragma unroll 1
         for (int k0 = tid * 8; k0 < K; k0 += kStep * kBatch) {
-            float p[kBatch][8];
-            load_products(t, k0, p);
-#pragma unroll
-            for (int u = 0; u < kBatch; ++u)
-#pragma unroll
-                for (int e = 0; e < 8; ++e) m = fmaxf(m, fabsf(p[u][e]));
-        }
-        const unsigned r = __reduce_max_sync(0xffffffffu, __float_as_uint(m));
-        if (lane == 0 && r != 0u) atomicMax(&ps->smax[t], r);
-    }
-    asm volatile("" ::"r"(tc.tag));
-    NQ_TRACE(2);
-    __syncthreads();
-    NQ_TRACE(3);
-#pragma unroll 1
-    for (int t = 0; t < T; ++t) {
-        float unit;
-        const float inv = scale_from_max(__uint_as_float(ps->smax[t]), unit);
-        if (tid == 0) ps->unit[t] = unit;
-        int acc = 0;
-#pragma unroll 1
-        for (int k0 = tid * 8; k0 < Kpad; k0 += kStep * kBatch) {
-            float p[kBatch][8];
-            load_products(t, k0, p);
+            Raw8<IN_KIND> x[kBatch], sc[kBatch];
 #pragma unroll
             for (int u = 0; u < kBatch; ++u) {
                 const int k8 = k0 + u * kStep;
-                if (k8 < Kpad) acc += convert8(p[u], inv, k8, xq + (3 * t) * stride, stride);   // columns K..Kpad are zero
+                x[u].a = x[u].b = make_uint4(0u, 0u, 0u, 0u);     // a zero block does not move the maximum
+                sc[u].a = sc[u].b = make_uint4(0u, 0u, 0u, 0u);
+                if (k8 < K) {
+                    load_raw<IN_KIND>(jb.in, t * jb.ld_in + k8, x[u], tc);
+                    if (kHasPre) load_raw<IN_KIND>(jb.pre, k8, sc[u], tc);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+                float v[8], s[8];
+                to_float8<IN_KIND>(x[u], v);
+                if (kHasPre) to_float8<IN_KIND>(sc[u], s);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) m = fmaxf(m, fabsf(kHasPre ? v[e] * s[e] : v[e]));
+            }
+        }
+        m = warp_max_abs(m);
+        if (lane == 0) red[t * kGemvWarps + warp] = m;
+    }
+    if (tid < kMaxTok) sumx[tid] = 0;
+    asm volatile("" ::"r"(tc.tag));   // the tag is in this thread's hands before the CTA can arrive at the counter
+    __syncthreads();
+    // pass 2: |p * inv| <= kQMax + 2^-7 by construction (same products as in pass 1), no clamp needed
+#pragma unroll 1
+    for (int t = 0; t < T; ++t) {
+        const float inv = token_inv(red, t, tid == 0, delta);
+        int8_t* r0 = xq + (3 * t) * stride;
+        int acc = 0;
+#pragma unroll 1
+        for (int k0 = tid * 8; k0 < Kpad; k0 += kStep * kBatch) {
+            Raw8<IN_KIND> x[kBatch], sc[kBatch];
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+                const int k8 = k0 + u * kStep;
+                x[u].a = x[u].b = make_uint4(0u, 0u, 0u, 0u);     // columns K..Kpad quantise to zero
+                sc[u].a = sc[u].b = make_uint4(0u, 0u, 0u, 0u);
+                if (k8 < K) {
+                    load_raw<IN_KIND>(jb.in, t * jb.ld_in + k8, x[u], tc);
+                    if (kHasPre) load_raw<IN_KIND>(jb.pre, k8, sc[u], tc);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+                const int k8 = k0 + u * kStep;
+                if (k8 < Kpad) {
+                    const int j = (k8 >> 5) & 7;
+                    float v[8], s[8];
+                    to_float8<IN_KIND>(x[u], v);
+                    if (kHasPre) to_float8<IN_KIND>(sc[u], s);
+                    uint32_t Y[8];  // class-shifted operands
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        const int X = __float2int_rn((kHasPre ? v[e] * s[e] : v[e]) * inv);
+                        acc += X;
+                        Y[e] = (uint32_t)class_shift(X, j);
+                    }
+                    store_terms(Y, r0, stride, k8);
+                }
             }
         }
         acc = __reduce_add_sync(0xffffffffu, acc);
-        if (lane == 0 && acc != 0) atomicAdd(&ps->sumx[t], acc);
+        if (lane == 0 && acc != 0) atomicAdd(&sumx[t], acc);
     }
-    *tcp = tc;
-    NQ_TRACE(4);
+    __syncthreads();
+}
+
+// Vector path for inputs with at most one 8-column block per thread (T * Kpad / 8 <= threads, e.g. one token of
+// 4096 columns): each value is loaded once and stays in registers between the max pass and the conversion, so
+// the phase pays a single memory round trip for its input.  Kpad / 8 is a multiple of 32: a warp serves one token.
+template <int IN_KIND>
+__device__ __noinline__ void quantise_one(const Job& jb, int T, int8_t* xq, int stride, float* red,
+                                          int* sumx, float* delta, TagCtx& tc) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int K = jb.K, nv8 = jb.chunks * 32;
+    constexpr bool kHasPre = (IN_KIND != KIND_T);
+    const int t = tid / nv8, k8 = (tid - t * nv8) * 8;
+    const bool active = t < T;
+    float p[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) p[e] = 0.f;
+    if (!kHasPre) tag_ensure(tc);          // the tagged intermediate is compared with the tag as it is loaded
+    Raw8<IN_KIND> xr, sr;
+    xr.a = xr.b = sr.a = sr.b = make_uint4(0u, 0u, 0u, 0u);
+    if (active && k8 < K) {
+        load_raw<IN_KIND>(jb.in, t * jb.ld_in + k8, xr, tc);
+        if (kHasPre) load_raw<IN_KIND>(jb.pre, k8, sr, tc);
+    }
+    if (kHasPre) tag_ensure(tc);           // behind the input loads: the two round trips overlap
+    if (active && k8 < K) {
+        to_float8<IN_KIND>(xr, p);
+        if (kHasPre) {
+            float s[8];
+            to_float8<IN_KIND>(sr, s);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) p[e] *= s[e];
+        }
+    }
+    float m = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) m = fmaxf(m, fabsf(p[e]));
+    m = warp_max_abs(m);
+    // per-warp maxima in the [token][warp] table: a warp contributes to its token only
+    if (lane < kMaxTok) red[lane * kGemvWarps + warp] = (active && lane == t) ? m : 0.f;
+    if (tid < kMaxTok) sumx[tid] = 0;
+    asm volatile("" ::"r"(tc.tag));   // the tag is in this thread's hands before the CTA can arrive at the counter
+    __syncthreads();
+    if (active) {
+        const float inv = token_inv(red, t, k8 == 0, delta);
+        const int j = (k8 >> 5) & 7;
+        uint32_t Y[8];
+        int acc = 0;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const int X = __float2int_rn(p[e] * inv);
+            acc += X;
+            Y[e] = (uint32_t)class_shift(X, j);
+        }
+        store_terms(Y, xq + (3 * t) * stride, stride, k8);
+        acc = __reduce_add_sync(0xffffffffu, acc);
+        if (lane == 0 && acc != 0) atomicAdd(&sumx[t], acc);
+    }
+    __syncthreads();
+}
+
+// The same with NI (2 or 4) blocks per thread: item f = tid + i * threads covers token f / nv8, columns
+// (f % nv8) * 8.  All NI loads of a thread are in flight together (the tagged intermediate is polled item by
+// item, but its later items are valid by then), nothing is loaded twice, and several tokens cost one memory
+// round trip instead of one per token and pass.
+template <int IN_KIND, int NI>
+__device__ __noinline__ void quantise_few(const Job& jb, int T, int8_t* xq, int stride, float* red,
+                                          int* sumx, float* delta, TagCtx& tc) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int K = jb.K, nv8 = jb.chunks * 32, items = T * nv8;
+    constexpr bool kHasPre = (IN_KIND != KIND_T);
+    float p[NI][8];
+    int tt[NI], kk[NI];
+    Raw8<IN_KIND> x[NI], sc[NI];
+    if (!kHasPre) tag_ensure(tc);
+#pragma unroll
+    for (int i = 0; i < NI; ++i) {
+        const int f = tid + i * kGemvThreads;
+        const int t = f / nv8;
+        tt[i] = f < items ? t : -1;
+        kk[i] = (f - t * nv8) * 8;
+        x[i].a = x[i].b = make_uint4(0u, 0u, 0u, 0u);
+        sc[i].a = sc[i].b = make_uint4(0u, 0u, 0u, 0u);
+        if (tt[i] >= 0 && kk[i] < K) {
+            load_raw<IN_KIND>(jb.in, t * jb.ld_in + kk[i], x[i], tc);
+            if (kHasPre) load_raw<IN_KIND>(jb.pre, kk[i], sc[i], tc);
+        }
+    }
+    if (kHasPre) tag_ensure(tc);           // behind the input loads: the two round trips overlap
+    float wm[kMaxTok];   // this warp's maximum per token (a warp's item belongs to one token)
+#pragma unroll
+    for (int q = 0; q < kMaxTok; ++q) wm[q] = 0.f;
+#pragma unroll
+    for (int i = 0; i < NI; ++i) {
+        float s[8], m = 0.f;
+        to_float8<IN_KIND>(x[i], p[i]);
+        if (kHasPre) {
+            to_float8<IN_KIND>(sc[i], s);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) p[i][e] *= s[e];
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) m = fmaxf(m, fabsf(p[i][e]));
+        m = warp_max_abs(m);
+#pragma unroll
+        for (int q = 0; q < kMaxTok; ++q) wm[q] = tt[i] == q ? fmaxf(wm[q], m) : wm[q];
+    }
+    if (lane < kMaxTok) {
+        float v = wm[0];
+#pragma unroll
+        for (int q = 1; q < kMaxTok; ++q) v = lane == q ? wm[q] : v;
+        red[lane * kGemvWarps + warp] = v;
+    }
+    if (tid < kMaxTok) sumx[tid] = 0;
+    asm volatile("" ::"r"(tc.tag));   // the tag is in this thread's hands before the CTA can arrive at the counter
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < NI; ++i) {
+        if (tt[i] >= 0) {      // warp-uniform
+            const float inv = token_inv(red, tt[i], kk[i] == 0, delta);
+            const int j = (kk[i] >> 5) & 7;
+            uint32_t Y[8];
+            int acc = 0;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const int X = __float2int_rn(p[i][e] * inv);
+                acc += X;
+                Y[e] = (uint32_t)class_shift(X, j);
+            }
+            store_terms(Y, xq + (3 * tt[i]) * stride, stride, kk[i]);
+            acc = __reduce_add_sync(0xffffffffu, acc);
+            if (lane == 0 && acc != 0) atomicAdd(&sumx[tt[i]], acc);
+        }
+    }
     __syncthreads();
 }
 
 // Scalar path for unaligned or ragged inputs (any K, any alignment).
-__device__ __noinline__ void quantise_scalar(const void* in, long long ld_in, const void* pre, int K, int chunks, int T,
-                                             int in_kind, int scale_kind, int8_t* xq, int stride, PhaseState* ps,
-                                             TagCtx* tcp) {
-    const int tid = threadIdx.x, lane = tid & 31;
-    const int Kpad = chunks * 256;
-    TagCtx tc = *tcp;
-    if (!tc.begun) tag_begin(tc, tc.status - 2, tc.limit);
-    auto product = [&](int t, int k) {
-        const float s = pre ? load_as_float(pre, k, scale_kind) : 1.f;
-        return (in_kind == KIND_T ? load1_tagged(in, t * ld_in + k, tc) : load_as_float(in, t * ld_in + k, in_kind)) * s;
-    };
+__device__ __noinline__ void quantise_scalar(const Job& jb, int T, int scale_kind, int8_t* xq, int stride,
+                                             float* red, int* sumx, float* delta, TagCtx& tc) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int K = jb.K, Kpad = jb.chunks * 256;
+    tag_ensure(tc);
 #pragma unroll 1
     for (int t = 0; t < T; ++t) {
         float m = 0.f;
-        for (int k = tid; k < K; k += kGemvThreads) m = fmaxf(m, fabsf(product(t, k)));
-        const unsigned r = __reduce_max_sync(0xffffffffu, __float_as_uint(m));
-        if (lane == 0 && r != 0u) atomicMax(&ps->smax[t], r);
+        for (int k = tid; k < K; k += kGemvThreads) {
+            const float s = jb.pre ? load_as_float(jb.pre, k, scale_kind) : 1.f;
+            m = fmaxf(m, fabsf((jb.in_kind == KIND_T ? load1_tagged(jb.in, t * jb.ld_in + k, tc) : load_as_float(jb.in, t * jb.ld_in + k, jb.in_kind)) * s));
+        }
+        m = warp_max_abs(m);
+        if (lane == 0) red[t * kGemvWarps + warp] = m;
     }
-    asm volatile("" ::"r"(tc.tag));
+    if (tid < kMaxTok) sumx[tid] = 0;
+    asm volatile("" ::"r"(tc.tag));   // the tag is in this thread's hands before the CTA can arrive at the counter
     __syncthreads();
 #pragma unroll 1
     for (int t = 0; t < T; ++t) {
-        float unit;
-        const float inv = scale_from_max(__uint_as_float(ps->smax[t]), unit);
-        if (tid == 0) ps->unit[t] = unit;
+        const float inv = token_inv(red, t, tid == 0, delta);
         int acc = 0;
         for (int k = tid; k < Kpad; k += kGemvThreads) {
-            const int X = k < K ? __float2int_rn(product(t, k) * inv) : 0;
+            int X = 0;
+            if (k < K) {
+                const float s = jb.pre ? load_as_float(jb.pre, k, scale_kind) : 1.f;
+                X = __float2int_rn((jb.in_kind == KIND_T ? load1_tagged(jb.in, t * jb.ld_in + k, tc) : load_as_float(jb.in, t * jb.ld_in + k, jb.in_kind)) * s * inv);
+            }
             acc += X;
-            const uint32_t z = (uint32_t)(X * class_mult((k >> 5) & 7) + 0x808080) ^ 0x808080u;
+            const int y = class_shift(X, (k >> 5) & 7);
             const int pos = xq_pos(k);
-            xq[(3 * t) * stride + pos] = (int8_t)(z & 0xFF);
-            xq[(3 * t + 1) * stride + pos] = (int8_t)((z >> 8) & 0xFF);
-            xq[(3 * t + 2) * stride + pos] = (int8_t)((z >> 16) & 0xFF);
+            xq[(3 * t) * stride + pos] = (int8_t)(y & 0xFF);
+            xq[(3 * t + 1) * stride + pos] = (int8_t)(((y + 0x80) >> 8) & 0xFF);
+            xq[(3 * t + 2) * stride + pos] = (int8_t)(((y + 0x8080) >> 16) & 0xFF);
         }
         acc = __reduce_add_sync(0xffffffffu, acc);
-        if (lane == 0 && acc != 0) atomicAdd(&ps->sumx[t], acc);
+        if (lane == 0 && acc != 0) atomicAdd(&sumx[t], acc);
     }
-    *tcp = tc;
     __syncthreads();
 }
 
-template <int NB>
-__device__ __forceinline__ void quantise_regs_kind(const Work& w, int T, int8_t* xq, int stride, PhaseState* ps, TagCtx* tc) {
-    if (w.in_kind == KIND_T) quantise_regs<KIND_T, NB>(w.in, w.ld_in, w.pre, w.K, w.chunks, T, xq, stride, ps, tc);
-    else if (w.in_kind == KIND_F16) quantise_regs<KIND_F16, NB>(w.in, w.ld_in, w.pre, w.K, w.chunks, T, xq, stride, ps, tc);
-    else quantise_regs<KIND_BF16, NB>(w.in, w.ld_in, w.pre, w.K, w.chunks, T, xq, stride, ps, tc);
+__device__ __forceinline__ void quantise_input(const Job& jb, int T, int scale_kind, int8_t* xq, int stride,
+                                               float* red, int* sumx, float* delta, TagCtx& tc) {
+    if (!jb.vec) quantise_scalar(jb, T, scale_kind, xq, stride, red, sumx, delta, tc);
+    else if (T * jb.chunks * 32 <= kGemvThreads) {
+        if (jb.in_kind == KIND_T) quantise_one<KIND_T>(jb, T, xq, stride, red, sumx, delta, tc);
+        else if (jb.in_kind == KIND_F16) quantise_one<KIND_F16>(jb, T, xq, stride, red, sumx, delta, tc);
+        else quantise_one<KIND_BF16>(jb, T, xq, stride, red, sumx, delta, tc);
+    }
+    else if (T * jb.chunks * 32 <= 2 * kGemvThreads) {
+        if (jb.in_kind == KIND_T) quantise_few<KIND_T, 2>(jb, T, xq, stride, red, sumx, delta, tc);
+        else if (jb.in_kind == KIND_F16) quantise_few<KIND_F16, 2>(jb, T, xq, stride, red, sumx, delta, tc);
+        else quantise_few<KIND_BF16, 2>(jb, T, xq, stride, red, sumx, delta, tc);
+    }
+    else if (T > 1 && T * jb.chunks * 32 <= 4 * kGemvThreads) {   // one token of that width: quantise_vec measured faster
+        if (jb.in_kind == KIND_T) quantise_few<KIND_T, 4>(jb, T, xq, stride, red, sumx, delta, tc);
+        else if (jb.in_kind == KIND_F16) quantise_few<KIND_F16, 4>(jb, T, xq, stride, red, sumx, delta, tc);
+        else quantise_few<KIND_BF16, 4>(jb, T, xq, stride, red, sumx, delta, tc);
+    }
+    else if (jb.in_kind == KIND_T) quantise_vec<KIND_T>(jb, T, xq, stride, red, sumx, delta, tc);
+    else if (jb.in_kind == KIND_F16) quantise_vec<KIND_F16>(jb, T, xq, stride, red, sumx, delta, tc);
+    else quantise_vec<KIND_BF16>(jb, T, xq, stride, red, sumx, delta, tc);
 }
 
-__device__ __forceinline__ void quantise_input(const Work& w, int T, int scale_kind, int8_t* xq, int stride,
-                                               PhaseState* ps, TagCtx* tc) {
-    const int blocks = T * w.chunks * 32;
-    if (!w.vec) quantise_scalar(w.in, w.ld_in, w.pre, w.K, w.chunks, T, w.in_kind, scale_kind, xq, stride, ps, tc);
-    else if (blocks <= kGemvThreads) quantise_regs_kind<1>(w, T, xq, stride, ps, tc);
-    else if (blocks <= 2 * kGemvThreads) quantise_regs_kind<2>(w, T, xq, stride, ps, tc);
-    else if (blocks <= 4 * kGemvThreads) quantise_regs_kind<4>(w, T, xq, stride, ps, tc);
-    else if (w.in_kind == KIND_T) quantise_loop<KIND_T>(w.in, w.ld_in, w.pre, w.K, w.chunks, T, xq, stride, ps, tc);
-    else if (w.in_kind == KIND_F16) quantise_loop<KIND_F16>(w.in, w.ld_in, w.pre, w.K, w.chunks, T, xq, stride, ps, tc);
-    else quantise_loop<KIND_BF16>(w.in, w.ld_in, w.pre, w.K, w.chunks, T, xq, stride, ps, tc);
-}
-
-__device__ __forceinline__ void cp_async16(unsigned smem_dst, const void* gmem_src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(gmem_src) : "memory");
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-// Per-warp cursor over this warp's items of one job.  An item is one 256-column chunk of a row unit; a row
-// unit is a pair of 16-row groups (tiles A and B, 1 KB together, sharing their B fragments) or, when a CTA
-// has too few pairs to occupy its warps, a single group (tile B then repeats tile A and is discarded).
-struct ItemStream {
-    const uint4* next;    // tile A of the next item to fetch (this lane's 16 bytes)
-    int offB;             // tile B of that item, in uint4, relative to tile A (0: none)
-    int n_items;          // items of this warp
-    int n_fetched;
-    int f_c, f_ru;        // chunk and row unit of the next item to fetch
-    int c0, ru0;          // chunk and row unit of this warp's first item
-    int rpu;              // row groups per unit: 1 or 2
+// Per-warp cursor over the (tile, chunk) pairs of one job: 1 KB of packed weights per
+// pair (two row groups x 256 columns), pairs tile-major, one contiguous range per warp.
+struct PairStream {
+    int my_items;   // row tiles (32 rows) of this CTA in the job
+    int first;      // the first of them (they are consecutive)
+    int my_pairs;   // pairs of this warp
+    int begin_il, begin_c;   // first pair of this warp: local tile index, chunk
+    int l_il, l_c, l_n;      // next pair to fetch
+    int slot;                // which half of the output-scale staging buffer this job uses
 };
 
-__device__ __forceinline__ void stream_issue(ItemStream& st, unsigned ring_lane, int chunks, int cnt) {
-    if (st.n_fetched < st.n_items) {
-        const unsigned dst = ring_lane + (unsigned)(st.n_fetched % kStages) * 1024u;
-        cp_async16(dst, st.next);
-        cp_async16(dst + 512u, st.next + st.offB);
-        st.next += 32;
-        ++st.n_fetched;
-        if (++st.f_c == chunks) {      // next row unit: skip tile B's row group
-            st.f_c = 0;
-            ++st.f_ru;
-            st.next += (st.rpu - 1) * chunks * 32;
-            st.offB = (st.rpu == 2 && 2 * st.f_ru + 1 < cnt) ? chunks * 32 : 0;
-        }
+// The row tiles (32 rows) of all jobs of a phase form one flattened list that is cut into gridDim.x
+// contiguous ranges, one per CTA (the first tiles_r CTAs get one tile more).  A CTA therefore prepares the
+// input of one job only, unless its range crosses a job boundary, and streams consecutive memory.  The split
+// is precomputed on the host: this runs on the latency-critical path between two jobs.
+// Returns the CTA's tiles of `jb`: first tile, count.
+__device__ __forceinline__ int my_tiles(const Job& jb, const Phase& ph, int& first) {
+    const int b = (int)blockIdx.x;
+    const int lo = ph.tiles_q * b + min(b, ph.tiles_r);
+    const int hi = lo + ph.tiles_q + (b < ph.tiles_r ? 1 : 0);
+    const int a = max(lo, jb.tile_start);
+    const int e = min(hi, jb.tile_start + jb.items);
+    first = a - jb.tile_start;
+    return e > a ? e - a : 0;
+}
+
+// The constants of a job that the weight stream needs, held in registers: a read of the shared-memory
+// descriptor behind an `asm volatile` with a memory clobber would be re-issued in every iteration.
+struct StreamJob {
+    const uint4* tiles;
+    int row_groups, chunks;
+};
+__device__ __forceinline__ StreamJob stream_job(const Job& jb) {
+    StreamJob sj;
+    sj.tiles = jb.tiles;
+    sj.row_groups = (jb.rows + 15) >> 4;
+    sj.chunks = jb.chunks;
+    return sj;
+}
+
+__device__ __forceinline__ void stream_issue(PairStream& st, const StreamJob& sj, uint4* ring, int lane) {
+    if (st.l_n < st.my_pairs) {
+        const int rg = 2 * (st.first + st.l_il);
+        const int rgb = (rg + 1 < sj.row_groups) ? rg + 1 : rg;  // odd tail: re-read, result discarded
+        uint4* dst = ring + (st.l_n % kStages) * 64 + lane;
+        cp_async16(dst, sj.tiles + ((size_t)rg * sj.chunks + st.l_c) * 32 + lane);
+        cp_async16(dst + 32, sj.tiles + ((size_t)rgb * sj.chunks + st.l_c) * 32 + lane);
+        if (++st.l_c == sj.chunks) { st.l_c = 0; ++st.l_il; }
+        ++st.l_n;
     }
     cp_async_commit();  // always commit so that group counting stays uniform
 }
 
-// Set the cursor up and start the first weight loads of a job.  They do not depend on the job's input
-// vector, so this runs before the input is ready.
-__device__ __forceinline__ void stream_begin(ItemStream& st, const Work& w, unsigned ring_lane, int warp, int lane) {
-    const int pairs = (w.cnt + 1) >> 1;
-    st.rpu = (pairs * w.chunks >= kGemvWarps) ? 2 : 1;
-    const int units = st.rpu == 2 ? pairs : w.cnt;
-    const int total = units * w.chunks;                       // < 2^20: the products below fit 32 bits
-    const int begin = total * warp / kGemvWarps;
-    st.n_items = total * (warp + 1) / kGemvWarps - begin;
-    st.ru0 = 0;
-    st.c0 = begin;
-    while (st.c0 >= w.chunks) { st.c0 -= w.chunks; ++st.ru0; }   // at most `units` steps
-    st.f_c = st.c0; st.f_ru = st.ru0; st.n_fetched = 0;
-    st.next = w.tiles + ((size_t)(w.rg0 + st.ru0 * st.rpu) * w.chunks + st.c0) * 32 + lane;
-    st.offB = (st.rpu == 2 && 2 * st.ru0 + 1 < w.cnt) ? w.chunks * 32 : 0;
+// Set the cursor up and start the first weight loads of a job.  They do not depend on
+// the job's input vector, so this runs before the input is ready (for a phase-2 job:
+// before the wait for the tagged intermediate, which then overlaps with the loads).
+__device__ __forceinline__ void stream_begin(PairStream& st, const Job& jb, const Phase& ph, uint4* ring, int warp,
+                                             int lane, uint16_t* post_s, int max_items) {
+    st.my_items = my_tiles(jb, ph, st.first);
+    const int npairs = st.my_items * jb.chunks;            // < 2^27: the products below fit 32 bits
+    const int p_begin = npairs * warp / kGemvWarps;
+    st.my_pairs = npairs * (warp + 1) / kGemvWarps - p_begin;
+    st.begin_il = 0;
+    st.begin_c = p_begin;
+    while (st.begin_c >= jb.chunks) { st.begin_c -= jb.chunks; ++st.begin_il; }   // at most my_items steps
+    st.l_il = st.begin_il; st.l_c = st.begin_c; st.l_n = 0;
+    st.slot ^= 1;
+    // The output scales of this CTA's rows are needed right after the main loop: copy them into shared
+    // memory now (part of this thread's first copy group, complete when the main loop has drained).
+    if (jb.post_vec) {
+        const int row0 = 32 * st.first;
+        const int nrows = min(32 * st.my_items, jb.rows - row0);
+        const int i = (int)threadIdx.x;
+        if (8 * i < nrows)
+            cp_async16(post_s + st.slot * (32 * max_items) + 8 * i,
+                       static_cast<const uint16_t*>(jb.post) + row0 + 8 * i);
+    }
+    const StreamJob sj = stream_job(jb);
 #pragma unroll
-    for (int d = 0; d < kStages - 1; ++d) stream_issue(st, ring_lane, w.chunks, w.cnt);
+    for (int d = 0; d < kStages - 1; ++d) stream_issue(st, sj, ring, lane);
 }
 
-// The descriptor of the job this CTA works on in `phase` (cnt = 0: none), read with uniform accesses.
-__device__ __forceinline__ void find_work(const GemvParams& P, int phase, Work& w) {
-    w.cnt = 0;
-    int sel = -1, rg0 = 0, cnt = 0;
-#pragma unroll
-    for (int j = 0; j < kMaxJobs; ++j) {
-        if (j < P.njobs) {
-            const JobDesc& J = P.job[phase][j];
-            const int b = (int)blockIdx.x - J.cta0;
-            if (b >= 0 && b < J.ncta) {
-                sel = j;
-                cnt = J.rg_q + (b < J.rg_r ? 1 : 0);
-                rg0 = b * J.rg_q + min(b, J.rg_r);
-            }
-        }
-    }
-    if (sel < 0 || cnt == 0) return;
-    const JobDesc& J = P.job[phase][sel];
-    w.tiles = J.tiles; w.in = J.in; w.pre = J.pre; w.post = J.post; w.out = J.out; w.bias = J.bias; w.resid = J.resid;
-    w.ld_in = J.ld_in; w.ld_out = J.ld_out; w.ld_res = J.ld_res;
-    w.rows = J.rows; w.K = J.K; w.chunks = J.chunks;
-    w.in_kind = J.in_kind; w.out_kind = J.out_kind; w.vec = J.vec; w.post_vec = J.post_vec;
-    w.rg0 = rg0; w.cnt = cnt;
+__device__ __forceinline__ bool cta_has_items(const Job& jb, const Phase& ph) {
+    int f;
+    return my_tiles(jb, ph, f) > 0;
 }
 
-// Pull every packed byte this CTA will read in a phase towards L2 (bulk prefetches; the range is contiguous).
-__device__ __forceinline__ void prefetch_tiles(const Work& w) {
-    const char* p = reinterpret_cast<const char*>(w.tiles + (size_t)w.rg0 * w.chunks * 32);
-    unsigned bytes = (unsigned)w.cnt * (unsigned)w.chunks * 512u;
-    while (bytes > 0) {   // pieces well inside the instruction's size field
-        const unsigned n = bytes > (1u << 20) ? (1u << 20) : bytes;
-        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(n) : "memory");
-        p += n;
-        bytes -= n;
-    }
-}
-
-// Output scales (and bias) of this CTA's rows into shared memory, as part of the thread's first copy group.
-__device__ __forceinline__ void stage_row_vectors(const Work& w, uint16_t* post_s, uint16_t* bias_s) {
-    if (!w.post_vec) return;
-    const int row0 = 16 * w.rg0;
-    const int nrows = min(16 * w.cnt, w.rows - row0);
-    const int i = (int)threadIdx.x;
-    if (8 * i < nrows) {
-        if (w.post)
-            cp_async16((unsigned)__cvta_generic_to_shared(post_s + 8 * i), static_cast<const uint16_t*>(w.post) + row0 + 8 * i);
-        if (w.bias)
-            cp_async16((unsigned)__cvta_generic_to_shared(bias_s + 8 * i), static_cast<const uint16_t*>(w.bias) + row0 + 8 * i);
-    }
-}
-
-// The whole launch for one CTA: its job of phase 1, then its job of phase 2 (which polls the tagged
-// intermediate).  CG = column groups of 8 MMA columns (3 columns per token).
+// The whole launch for one CTA: the jobs of phase 1, then the jobs of phase 2 (which poll the
+// tagged intermediate).  CG = column groups of 8 MMA columns (3 columns per token).
 template <int CG>
-__global__ void __launch_bounds__(kGemvThreads, 1) gemv_group_kernel(const __grid_constant__ GemvParams P) {
-    extern __shared__ __align__(16) unsigned char smem[];
+__device__ __forceinline__ bool run_all(const Phase* phases, const GemvParams& P, unsigned char* smem) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, q = lane & 3;
     constexpr int kCols = 8 * CG;
-    NQ_TRACE(0);
     // shared memory carve-up
-    PhaseState* pstate = reinterpret_cast<PhaseState*>(smem);                         // [2]
-    const unsigned ring_lane = (unsigned)__cvta_generic_to_shared(smem + kStateBytes) +
-                               (unsigned)warp * (kStages * 1024u) + (unsigned)lane * 16u;
-    const uint4* ring_rd = reinterpret_cast<const uint4*>(smem + kStateBytes) + warp * (kStages * 64) + lane;
-    int* s1_ph[2];
-    s1_ph[0] = reinterpret_cast<int*>(smem + kStateBytes + kRingBytes);
-    s1_ph[1] = s1_ph[0] + P.rows_cap[0] * kCols;
-    int8_t* xq = reinterpret_cast<int8_t*>(s1_ph[1] + P.rows_cap[1] * kCols);
-    uint16_t* post_ph[2];
-    post_ph[0] = reinterpret_cast<uint16_t*>(xq + (size_t)3 * P.T * P.xq_stride);
-    post_ph[1] = post_ph[0] + P.rows_cap[0];
-    uint16_t* bias_s = post_ph[1] + P.rows_cap[1];
+    float* red = reinterpret_cast<float*>(smem);                          // [warps][4] + [4]
+    int* sumx = reinterpret_cast<int*>(smem + kRedBytes);                 // [4]
+    float* delta = reinterpret_cast<float*>(smem + kRedBytes + 16);       // [4]
+    uint4* ring = reinterpret_cast<uint4*>(smem + kFixedBytes) + warp * (kStages * 64);  // [stage][2][32]
+    int* s1 = reinterpret_cast<int*>(smem + kFixedBytes + kRingBytes);    // [max_items][32 rows][kCols]
+    int8_t* xq = reinterpret_cast<int8_t*>(smem + kFixedBytes + kRingBytes + (size_t)P.max_items * (128 * kCols));
+    // output scales of the current and the next job: [2][max_items][32] two-byte entries behind the int8 vectors
+    uint16_t* post_s = reinterpret_cast<uint16_t*>(xq + (size_t)3 * P.T * P.xq_stride);
 
-    Work wk[2];
-    find_work(P, 0, wk[0]);
-    find_work(P, 1, wk[1]);
-    if (tid == 0 && wk[0].cnt > 0) prefetch_tiles(wk[0]);
-    if (tid == 32 && wk[1].cnt > 0) prefetch_tiles(wk[1]);
-    ItemStream st;
-    st.n_items = 0;
-    int ph = wk[0].cnt > 0 ? 0 : 1;
-    if (wk[ph].cnt > 0) {
-        stage_row_vectors(wk[ph], post_ph[ph], bias_s);
-        stream_begin(st, wk[ph], ring_lane, warp, lane);
-        // the input scales are constants of the layer: pull this thread's part towards L1 under the previous kernel's tail
-        if (ph == 0 && wk[0].pre && tid * 8 < wk[0].K)
-            asm volatile("prefetch.global.L1 [%0];" ::"l"(static_cast<const char*>(wk[0].pre) + 16 * (size_t)tid));
+    const int njobs = phases[0].njobs;        // same count in both phases
+    auto job_of = [&](int s) -> const Job& { return phases[s >= njobs].job[s >= njobs ? s - njobs : s]; };
+    auto next_step = [&](int s) {             // first step >= s in which this CTA owns row tiles
+        while (s < 2 * njobs && !cta_has_items(job_of(s), phases[s >= njobs])) ++s;
+        return s;
+    };
+    PairStream st;
+    st.slot = 0;
+    int s = next_step(0);
+    if (s < 2 * njobs) {
+        const Job& j0 = job_of(s);
+        stream_begin(st, j0, phases[s >= njobs], ring, warp, lane, post_s, P.max_items);
+        // the input scales are constants of the layer: pull them towards L2 while the previous kernel drains
+        if (s < njobs && j0.pre && tid * 64 < j0.K)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(static_cast<const char*>(j0.pre) + 128 * (size_t)tid));
     }
-    if (tid < (int)(2 * sizeof(PhaseState) / 4)) reinterpret_cast<unsigned*>(pstate)[tid] = 0u;
-    for (int i = tid; i < (P.rows_cap[0] + P.rows_cap[1]) * kCols; i += kGemvThreads) s1_ph[0][i] = 0;
-    __syncthreads();   // the zeroed state is in place before any warp can reach the atomics that use it
-    NQ_TRACE(9);
-    // Programmatic dependent launch: everything above may overlap with the tail of the previous kernel in the
-    // stream; the activations and the scratch (shared with that kernel) are only touched after it has completed.
+    // Programmatic dependent launch: everything above (descriptor copy, first weight loads) may overlap
+    // with the tail of the previous kernel in the stream; the activations and the scratch (shared with
+    // that kernel) are only touched after it has completed.  No-ops without the launch attribute.
     asm volatile("griddepcontrol.wait;" ::: "memory");
     // All CTAs of this cooperative grid are resident, so CTAs of the next kernel that start early cannot keep one
     // of ours from being scheduled: let the next kernel begin its prologue wherever an SM frees up.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    NQ_TRACE(10);
-    // tag of this launch for the intermediate's {value, tag} words
+    // tag of this launch for the intermediate's {value, tag} pairs (and this CTA's arrival, which nobody waits for)
     TagCtx tc;
-    tc.tag = 0u; tc.limit = P.spin_limit; tc.status = P.header + 2; tc.begun = 0u;   // read behind the first data loads
+    tc.tag = 0u; tc.limit = P.spin_limit; tc.status = P.header + 2; tc.begun = 0u;   // read behind the first input loads
     bool arrived = false;
-
 #pragma unroll 1
-    for (; ph < 2; ++ph) {
-        const Work& w = wk[ph];
-        if (w.cnt == 0) continue;     // no rows of phase 2 for this CTA
-        PhaseState* ps = pstate + ph;
-        int* s1 = s1_ph[ph];
-        quantise_input(w, P.T, P.scale_kind, xq, P.xq_stride, ps, &tc);
-        if (!arrived) {   // behind a CTA barrier that every thread passes with its tag in hand
+    while (true) {
+        if (s >= 2 * njobs) break;
+        const Job& jb = job_of(s);
+        const int chunks = jb.chunks;
+        for (int i = tid; i < st.my_items * (32 * kCols); i += kGemvThreads) s1[i] = 0;
+        quantise_input(jb, P.T, P.scale_kind, xq, P.xq_stride, red, sumx, delta, tc);
+        if (!arrived) {   // behind the CTA barriers of the quantiser
             if (tid == 0) launch_arrive(reinterpret_cast<unsigned long long*>(P.header), blockIdx.x == 0, gridDim.x);
             arrived = true;
         }
-        NQ_TRACE(5);
 
         // MMA column n = 8*cg + g reads int8 vector n (= 3*tok + term); unused columns re-read a valid one
-        const int ncols = 3 * P.T;
-        const int8_t* bbase = xq + (g < ncols ? g : ncols - 1) * P.xq_stride + 8 * q;
-        const int boff1 = CG > 1 ? ((8 + g < ncols ? 8 + g : ncols - 1) - (g < ncols ? g : ncols - 1)) * P.xq_stride : 0;
-        const int chunks = w.chunks, cnt = w.cnt, n_items = st.n_items, rpu = st.rpu;
-        int acc[2][2][CG][4];    // [tile A / B][even / odd mask: two independent MMA chains][column group][fragment]
+        const int8_t* bbase[CG];
 #pragma unroll
-        for (int a = 0; a < 2; ++a)
+        for (int cg = 0; cg < CG; ++cg) {
+            const int n = 8 * cg + g;
+            bbase[cg] = xq + (n < 3 * P.T ? n : 3 * P.T - 1) * P.xq_stride + 8 * q;
+        }
+        int accA[CG][4], accB[CG][4];
 #pragma unroll
-            for (int h = 0; h < 2; ++h)
+        for (int cg = 0; cg < CG; ++cg)
 #pragma unroll
-                for (int cg = 0; cg < CG; ++cg)
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) acc[a][h][cg][i] = 0;
-        int c_c = st.c0, c_ru = st.ru0;
+            for (int i = 0; i < 4; ++i) { accA[cg][i] = 0; accB[cg][i] = 0; }
+        int c_il = st.begin_il, c_c = st.begin_c;
+        const StreamJob sj = stream_job(jb);
+        const int my_pairs = st.my_pairs;
 #pragma unroll 1
-        for (int n = 0; n < n_items; ++n) {
-            stream_issue(st, ring_lane, chunks, cnt);
+        for (int n = 0; n < my_pairs; ++n) {
+            stream_issue(st, sj, ring, lane);
             cp_async_wait<kStages - 1>();
-            // a lane reads back exactly the 32 bytes it copied itself: no warp synchronisation needed
-            const uint4* slot = ring_rd + (n % kStages) * 64;
+            __syncwarp();
+            const uint4* slot = ring + (n % kStages) * 64 + lane;
             const uint4 ta = slot[0], tb = slot[32];
-            const int8_t* bp = bbase + c_c * 256;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 const uint32_t m = 0x01010101u << j;
 #pragma unroll
                 for (int cg = 0; cg < CG; ++cg) {
-                    const uint2 b = *reinterpret_cast<const uint2*>(bp + (cg ? boff1 : 0) + 32 * j);
-                    mma_s8(acc[0][j & 1][cg], ta.x & m, ta.y & m, ta.z & m, ta.w & m, b.x, b.y);
-                    mma_s8(acc[1][j & 1][cg], tb.x & m, tb.y & m, tb.z & m, tb.w & m, b.x, b.y);
+                    const uint2 b = *reinterpret_cast<const uint2*>(bbase[cg] + c_c * 256 + 32 * j);
+                    mma_s8(accA[cg], ta.x & m, ta.y & m, ta.z & m, ta.w & m, b.x, b.y);
+                    mma_s8(accB[cg], tb.x & m, tb.y & m, tb.z & m, tb.w & m, b.x, b.y);
                 }
             }
-            // when this warp leaves the row unit, fold its partial sums into shared memory:
-            // lane (g, q) holds rows g / g+8 of both tiles, columns 2q, 2q+1 of each column group
-            if (++c_c == chunks || n + 1 == n_items) {
-                int* dst = s1 + c_ru * rpu * (16 * kCols);
-                const bool has_b = rpu == 2 && 2 * c_ru + 1 < cnt;
+            __syncwarp();  // every lane has read the slot before it is refilled
+            // when this warp leaves the row tile, fold its partial sums into shared memory:
+            // lane (g, q) holds rows g / g+8 of both row groups, columns 2q, 2q+1 of each column group
+            if (++c_c == chunks || n + 1 == my_pairs) {
+                int* dst = s1 + c_il * (32 * kCols);
 #pragma unroll
                 for (int cg = 0; cg < CG; ++cg) {
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         const int col = 8 * cg + 2 * q + (i & 1);
                         const int ra = g + 8 * (i >> 1);
-                        const int va = acc[0][0][cg][i] + acc[0][1][cg][i];
-                        const int vb = acc[1][0][cg][i] + acc[1][1][cg][i];
-                        if (col < ncols) {
-                            if (va != 0) atomicAdd(&dst[ra * kCols + col], va);
-                            if (has_b && vb != 0) atomicAdd(&dst[(16 + ra) * kCols + col], vb);
-                        }
-                        acc[0][0][cg][i] = 0; acc[0][1][cg][i] = 0;
-                        acc[1][0][cg][i] = 0; acc[1][1][cg][i] = 0;
+                        if (accA[cg][i] != 0) atomicAdd(&dst[ra * kCols + col], accA[cg][i]);
+                        if (accB[cg][i] != 0) atomicAdd(&dst[(16 + ra) * kCols + col], accB[cg][i]);
+                        accA[cg][i] = 0;
+                        accB[cg][i] = 0;
                     }
                 }
-                if (c_c == chunks) { c_c = 0; ++c_ru; }
+                if (c_c == chunks) { c_c = 0; ++c_il; }
             }
         }
         cp_async_wait<0>();
-        NQ_TRACE(11);
-        // This warp's ring is free again (a lane only ever reads its own bytes): start the weight stream and the
-        // output scales of the phase-2 job before the barrier and the epilogue, whose latencies the loads overlap.
-        if (ph == 0 && wk[1].cnt > 0) {
-            stage_row_vectors(wk[1], post_ph[1], bias_s);
-            stream_begin(st, wk[1], ring_lane, warp, lane);
-        }
         __syncthreads();
-        NQ_TRACE(6);
-        // finalise: the three column sums of a token are the byte terms of 128 * sum_{bit=1}(X);
-        // result = sum(X) - 2 * sum_{bit=1}(X) = sum(X) - terms / 64 (terms is a multiple of 128).
-        const int row0 = 16 * w.rg0;
-        const int nrows = min(16 * cnt, w.rows - row0);
-        const uint16_t* my_post = post_ph[ph];
-#pragma unroll 1
-        for (int tok = 0; tok < P.T; ++tok) {
-            const long long sx = ps->sumx[tok];
-            const float unit = ps->unit[tok];
-#pragma unroll 1
-            for (int idx = tid; idx < nrows; idx += kGemvThreads) {
-                const int row = row0 + idx;
-                float extra = 0.f;       // bias and residual of this output, fetched before the arithmetic
-                if (w.bias) extra = w.post_vec ? load_as_float(bias_s, idx, P.scale_kind) : load_as_float(w.bias, row, P.scale_kind);
-                if (w.resid) extra += load_as_float(w.resid, tok * w.ld_res + row, P.scale_kind);
-                const int* c = s1 + idx * kCols + 3 * tok;
-                const long long terms = (long long)c[2] * 65536 + (long long)c[1] * 256 + (long long)c[0];
-                const long long r = sx - (terms >> 6);
-                // exact split: both halves convert without rounding, the sum rounds once
-                float val = ((float)(int)(r >> 20) * 1048576.0f + (float)(int)(r & 0xFFFFF)) * unit;
-                if (w.post) val *= w.post_vec ? load_as_float(my_post, idx, P.scale_kind) : load_as_float(w.post, row, P.scale_kind);
-                if (w.out_kind == KIND_T) {
-                    store_tagged(w.out, tok * w.ld_out + row, val, tc.tag);
-                } else {
-                    val += extra;
-                    if (w.out_kind == KIND_F16) {
-                        // same saturation bounds as the reference epilogue
-                        val = fminf(fmaxf(val, -64504.0f), 64504.0f);
-                        static_cast<__half*>(w.out)[tok * w.ld_out + row] = __float2half(val);
+        const int my_items = st.my_items;
+        const int first_tile_of_job = st.first;
+        const uint16_t* my_post = post_s + st.slot * (32 * P.max_items);
+        // finalise: thread -> (token slot, row slot); tokens beyond the slot count and rows beyond the 128 row
+        // slots are covered by the strides.  The three column sums of a token are the byte terms of
+        // 128 * sum_{bit=1}(X); result = sum(X) - 2 * sum_{bit=1}(X) = sum(X) - terms / 64 (terms is a multiple of 128).
+        for (int tok = tid >> 7; tok < P.T; tok += kGemvThreads >> 7) {
+            const long long sx = sumx[tok];
+            const float dl = delta[tok];
+            for (int idx = tid & 127; idx < my_items * 32; idx += 128) {
+                const int row = 32 * first_tile_of_job + idx;
+                if (row < jb.rows) {
+                    float extra = 0.f;       // bias and residual of this output (phase 2), fetched before the arithmetic
+                    if (jb.bias) extra = load_as_float(jb.bias, row, P.scale_kind);
+                    if (jb.resid) extra += load_as_float(jb.resid, tok * jb.ld_res + row, P.scale_kind);
+                    const int* c = s1 + idx * kCols + 3 * tok;
+                    const long long terms = (long long)c[2] * 65536 + (long long)c[1] * 256 + (long long)c[0];
+                    float val = (float)(sx - (terms >> 6)) * dl;
+                    if (jb.post) val *= jb.post_vec ? load_as_float(my_post, idx, P.scale_kind)
+                                                    : load_as_float(jb.post, row, P.scale_kind);
+                    if (jb.out_kind == KIND_T) {
+                        store_tagged(jb.out, tok * jb.ld_out + row, val, tc.tag);
+                    } else if (jb.out_kind == KIND_F16) {
+                        // bias and residual in fp32 behind the output scale; same saturation bounds as the reference epilogue
+                        val = fminf(fmaxf(val + extra, -64504.0f), 64504.0f);
+                        static_cast<__half*>(jb.out)[tok * jb.ld_out + row] = __float2half(val);
                     } else {
-                        val = fminf(fmaxf(val, -3.3895313892515355e+38f), 3.3895313892515355e+38f);
-                        static_cast<__nv_bfloat16*>(w.out)[tok * w.ld_out + row] = __float2bfloat16(val);
+                        val = fminf(fmaxf(val + extra, -3.3895313892515355e+38f), 3.3895313892515355e+38f);
+                        static_cast<__nv_bfloat16*>(jb.out)[tok * jb.ld_out + row] = __float2bfloat16(val);
                     }
                 }
             }
         }
-        NQ_TRACE(12);
+        // Start the next job's weight stream after this job's results are on their way (their stores then
+        // overlap the address arithmetic below) and before any barrier, whose wait the loads overlap.
+        const int s_next = next_step(s + 1);
+        if (s_next < 2 * njobs)
+            stream_begin(st, job_of(s_next), phases[s_next >= njobs], ring, warp, lane, post_s, P.max_items);
+        __syncthreads();  // xq / s1 are reused by the next job
+        s = s_next;
     }
-    if (!arrived) {   // a CTA without rows in either phase still counts towards the launch
-        if (!tc.begun) tag_begin(tc, tc.status - 2, tc.limit);
+    if (!arrived) {   // a CTA without row tiles in either phase still counts towards the launch
+        tag_ensure(tc);
         asm volatile("" ::"r"(tc.tag));
         __syncthreads();
         if (tid == 0) launch_arrive(reinterpret_cast<unsigned long long*>(P.header), blockIdx.x == 0, gridDim.x);
     }
+    return true;
+}
+
+template <int CG>
+__global__ void __launch_bounds__(kGemvThreads, NQ_GEMV_MIN_CTAS) gemv_group_kernel(const __grid_constant__ GemvParams P) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    // The descriptors are read with runtime indices; one cooperative copy out of the
+    // parameter bank into shared memory replaces many serial constant-cache misses.
+    __shared__ __align__(16) Phase sphase[2];
+    {
+        const uint32_t* src = reinterpret_cast<const uint32_t*>(&P.phase[0]);
+        uint32_t* dst = reinterpret_cast<uint32_t*>(&sphase[0]);
+        for (int i = threadIdx.x; i < (int)(sizeof(Phase) * 2 / 4); i += kGemvThreads) dst[i] = src[i];
+        __syncthreads();
+    }
+    run_all<CG>(sphase, P, smem);
 }
 
 static size_t round_up(size_t v, size_t m) { return (v + m - 1) / m * m; }
@@ -778,38 +853,6 @@ static int dynamic_smem_limit(int dev, int* out) {
     return NQ_OK;
 }
 
-// Deal the CTAs of the grid to the jobs of a phase: every job gets a contiguous range, sized so that the
-// longest per-CTA stream (row groups x chunks) is as short as possible; a CTA never owns rows of two jobs.
-// Returns the most row groups a CTA owns.
-static int plan_phase(JobDesc* jobs, int njobs, int grid) {
-    int rg[kMaxJobs], n[kMaxJobs];
-    for (int j = 0; j < njobs; ++j) {
-        rg[j] = (jobs[j].rows + 15) / 16;
-        n[j] = 1;
-    }
-    for (int used = njobs; used < grid; ++used) {
-        int best = -1;
-        long long best_cost = -1;
-        for (int j = 0; j < njobs; ++j) {
-            if (n[j] >= rg[j]) continue;      // one row group per CTA already
-            const long long cost = (long long)((rg[j] + n[j] - 1) / n[j]) * jobs[j].chunks;
-            if (cost > best_cost) { best_cost = cost; best = j; }
-        }
-        if (best < 0) break;
-        ++n[best];
-    }
-    int c0 = 0, cap = 0;
-    for (int j = 0; j < njobs; ++j) {
-        jobs[j].cta0 = c0;
-        jobs[j].ncta = n[j];
-        jobs[j].rg_q = rg[j] / n[j];
-        jobs[j].rg_r = rg[j] % n[j];
-        const int most = jobs[j].rg_q + (jobs[j].rg_r ? 1 : 0);
-        cap = most > cap ? most : cap;
-        c0 += n[j];
-    }
-    return cap;
-}
 
 // ---------------------------------------------------------------------------
 // GEMV without caller-provided scratch
@@ -839,7 +882,7 @@ static int static_scratch_ptr(void** out) {
     return NQ_OK;
 }
 
-static unsigned g_spin_limit = kSpinLimit;
+static unsigned g_spin_limit = kSpinLimit;   // polls before a wait for the tagged intermediate gives up
 
 }  // namespace nq
 
@@ -890,77 +933,89 @@ int nq_gemv_group_fwd(const nq_linear_desc* d, int n_linears, int T, int dtype, 
         if (st != NQ_OK) return st;
     }
     const int grid = sm_count();
-    if (grid < kMaxJobs || (unsigned)grid >= kTagSpan) return NQ_ERR_UNSUPPORTED;
+    int tot1 = 0, tot2 = 0;
+    for (int i = 0; i < n_linears; ++i) {
+        tot1 += (d[i].R + 31) / 32;
+        tot2 += (d[i].M + 31) / 32;
+    }
+    const int tot = tot1 > tot2 ? tot1 : tot2;
+    const int max_items = (tot + grid - 1) / grid;       // longest contiguous range a CTA can get
     const int kpad = (maxK + 255) / 256 * 256;
     const int stride = kpad + 32;  // 32 mod 128: conflict-free 64-bit fragment loads
-
-    GemvParams P;
-    memset(&P, 0, sizeof(P));
-    P.header = static_cast<unsigned*>(scratch);
-    P.scale_kind = dtype;
-    P.xq_stride = stride;
-    P.njobs = n_linears;
-    P.spin_limit = g_spin_limit;
-    const size_t esz = 2;
-    size_t off = kHeaderBytes;
-    for (int i = 0; i < n_linears; ++i) {
-        const nq_linear_desc& L = d[i];
-        void* tbuf = static_cast<char*>(scratch) + off;   // {fp32, tag} words, 8 bytes per element
-        off += round_up((size_t)kMaxTok * (size_t)L.R * sizeof(uint2), 256);
-        JobDesc& a = P.job[0][i];
-        a.tiles = static_cast<const uint4*>(L.v_tiles);
-        a.in = L.x;
-        a.pre = L.s_in;
-        a.post = L.s_mid;
-        a.out = tbuf;
-        a.ld_in = L.ldx;
-        a.ld_out = L.R;
-        a.rows = L.R;
-        a.K = L.N;
-        a.chunks = (L.N + 255) / 256;
-        a.in_kind = dtype;
-        a.out_kind = KIND_T;
-        a.post_vec = L.s_mid && (L.R % 8 == 0) && aligned16(L.s_mid);
-        JobDesc& b = P.job[1][i];
-        b.tiles = static_cast<const uint4*>(L.u_tiles);
-        b.in = tbuf;
-        b.post = L.s_out;
-        b.out = L.y;
-        b.bias = L.bias;
-        b.resid = L.residual;
-        b.ld_in = L.R;
-        b.ld_out = L.ldy;
-        b.ld_res = L.ldr;
-        b.rows = L.M;
-        b.K = L.R;
-        b.chunks = (L.R + 255) / 256;
-        b.in_kind = KIND_T;
-        b.out_kind = dtype;
-        b.vec = (L.R % 8 == 0);  // the intermediate lives in the 256-byte aligned scratch
-        b.post_vec = (L.M % 8 == 0) && aligned16(L.s_out) && (!L.bias || aligned16(L.bias));
-    }
-    for (int ph = 0; ph < 2; ++ph) P.rows_cap[ph] = 16 * plan_phase(P.job[ph], n_linears, grid);
 
     // tokens are processed in groups that fit the MMA columns (3 per token) and shared memory
     auto cg_for = [](int t) { return t <= 2 ? 1 : 2; };
     auto smem_for = [&](int t) {
-        const size_t rows = (size_t)P.rows_cap[0] + P.rows_cap[1];
-        return kStateBytes + kRingBytes + rows * (32 * cg_for(t)) + (size_t)3 * t * stride +
-               round_up(rows * 2, 16) + round_up((size_t)P.rows_cap[1] * 2, 16) + 32;
+        return kFixedBytes + kRingBytes + (size_t)max_items * (128 * 8 * cg_for(t)) + (size_t)3 * t * stride +
+               (size_t)max_items * 128;   // + output scales of two jobs
     };
     int tg = T < kMaxTok ? T : kMaxTok;
     while (tg > 1 && smem_for(tg) > (size_t)smem_limit) --tg;
     if (smem_for(tg) > (size_t)smem_limit) return NQ_ERR_UNSUPPORTED;
 
+    const size_t esz = 2;
     for (int t0 = 0; t0 < T; t0 += tg) {
         const int tn = (T - t0) < tg ? (T - t0) : tg;
+        GemvParams P;
+        memset(&P, 0, sizeof(P));
+        P.header = static_cast<unsigned*>(scratch);
+        P.spin_limit = g_spin_limit;
         P.T = tn;
+        P.scale_kind = dtype;
+        P.xq_stride = stride;
+        P.max_items = max_items;
+        P.phase[0].njobs = P.phase[1].njobs = n_linears;
+        size_t off = kHeaderBytes;
+        int tiles_a = 0, tiles_b = 0;   // running tile counts of the two phases
         for (int i = 0; i < n_linears; ++i) {
             const nq_linear_desc& L = d[i];
-            P.job[0][i].in = static_cast<const char*>(L.x) + (size_t)t0 * L.ldx * esz;
-            P.job[0][i].vec = (L.N % 8 == 0) && (L.ldx % 8 == 0) && aligned16(P.job[0][i].in) && aligned16(L.s_in);
-            P.job[1][i].out = static_cast<char*>(L.y) + (size_t)t0 * L.ldy * esz;
-            if (L.residual) P.job[1][i].resid = static_cast<const char*>(L.residual) + (size_t)t0 * L.ldr * esz;
+            void* tbuf = static_cast<char*>(scratch) + off;   // {fp32, tag} pairs, 8 bytes per element
+            off += round_up((size_t)kMaxTok * (size_t)L.R * sizeof(uint2), 256);
+            Job& a = P.phase[0].job[i];
+            a.tiles = static_cast<const uint4*>(L.v_tiles);
+            a.in = static_cast<const char*>(L.x) + (size_t)t0 * L.ldx * esz;
+            a.pre = L.s_in;
+            a.post = L.s_mid;
+            a.out = tbuf;
+            a.ld_in = L.ldx;
+            a.ld_out = L.R;
+            a.rows = L.R;
+            a.K = L.N;
+            a.chunks = (L.N + 255) / 256;
+            a.items = (L.R + 31) / 32;
+            a.in_kind = dtype;
+            a.out_kind = KIND_T;
+            a.vec = (L.N % 8 == 0) && (L.ldx % 8 == 0) && aligned16(a.in) && aligned16(L.s_in);
+            a.post_vec = L.s_mid && (L.R % 8 == 0) && aligned16(L.s_mid);
+            a.tile_start = tiles_a;
+            tiles_a += a.items;
+            Job& b = P.phase[1].job[i];
+            b.tiles = static_cast<const uint4*>(L.u_tiles);
+            b.in = tbuf;
+            b.pre = nullptr;
+            b.post = L.s_out;
+            b.out = static_cast<char*>(L.y) + (size_t)t0 * L.ldy * esz;
+            b.bias = L.bias;
+            b.resid = L.residual ? static_cast<const char*>(L.residual) + (size_t)t0 * L.ldr * esz : nullptr;
+            b.ld_res = L.ldr;
+            b.ld_in = L.R;
+            b.ld_out = L.ldy;
+            b.rows = L.M;
+            b.K = L.R;
+            b.chunks = (L.R + 255) / 256;
+            b.items = (L.M + 31) / 32;
+            b.in_kind = KIND_T;
+            b.out_kind = dtype;
+            b.vec = (L.R % 8 == 0);  // the intermediate lives in the 256-byte aligned scratch
+            b.post_vec = (L.M % 8 == 0) && aligned16(L.s_out);
+            b.tile_start = tiles_b;
+            tiles_b += b.items;
+        }
+        P.phase[0].total_tiles = tiles_a;
+        P.phase[1].total_tiles = tiles_b;
+        for (int ph = 0; ph < 2; ++ph) {
+            P.phase[ph].tiles_q = P.phase[ph].total_tiles / grid;
+            P.phase[ph].tiles_r = P.phase[ph].total_tiles % grid;
         }
         void* args[] = {&P};
         const void* fn = cg_for(tn) == 1 ? (const void*)gemv_group_kernel<1> : (const void*)gemv_group_kernel<2>;
@@ -1018,14 +1073,6 @@ int nq_gemv_fwd_static(const void* x, const void* s_in, const void* v_tiles, con
 }
 
 size_t nq_gemv_static_max_rank(void) { return (size_t)kStaticMaxRank; }
-
-#ifdef NQ_GEMV_TRACE
-int nq_debug_read_trace(unsigned long long* host_out) {
-    NQ_CUDA_TRY(cudaDeviceSynchronize());
-    NQ_CUDA_TRY(cudaMemcpyFromSymbol(host_out, g_trace, sizeof(unsigned long long) * 148 * 16 * 32 * 2));
-    return NQ_OK;
-}
-#endif
 
 unsigned nq_gemv_set_wait_limit(unsigned polls) {
     const unsigned old = g_spin_limit;
