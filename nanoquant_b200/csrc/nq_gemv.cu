@@ -69,6 +69,7 @@ constexpr size_t kRedBytes = 384;   // per-warp maxima: kMaxTok * kGemvWarps flo
 constexpr size_t kFixedBytes = 512;
 constexpr size_t kRingBytes = (size_t)kGemvWarps * kStages * 1024;
 constexpr size_t kHeaderBytes = 256;
+constexpr unsigned kPollBackoffNs = 200;   // pause between two polls of the tagged intermediate
 
 // KIND_T: the rank-R intermediate between the phases, one 8-byte {fp32 value, launch tag} pair per element
 enum : int { KIND_F16 = 0, KIND_BF16 = 1, KIND_T = 2 };
@@ -87,15 +88,14 @@ struct Job {
     int items;            // ceil(rows / 32)
     int in_kind, out_kind;
     int vec;              // rows of `in` / `pre` are 16-byte aligned and K % 8 == 0
-    int tile_start;       // index of this job's row tile 0 in the phase's flattened tile list
+    int cta0, ncta;       // CTAs [cta0, cta0 + ncta) work on this job
+    int t_q, t_r;         // row tiles per CTA of the range: t_q, one more for its first t_r CTAs
     int post_vec;         // `post` is 16-byte aligned and rows % 8 == 0: staged in shared memory with 16-byte copies
 };
 
 struct Phase {
     Job job[kMaxJobs];
     int njobs;
-    int total_tiles;      // row tiles (32 rows) of all jobs of the phase
-    int tiles_q, tiles_r; // total_tiles = tiles_q * gridDim.x + tiles_r: CTA b owns tiles_q (+1 if b < tiles_r) tiles
 };
 
 struct GemvParams {
@@ -136,6 +136,7 @@ __device__ __forceinline__ void load8_tagged(const void* base, long long i, floa
         for (int k = 0; k < 8; ++k) ok = ok && (unsigned)(e[k] >> 32) == tc.tag;
         if (ok) break;
         if (spins >= tc.limit) { tag_wait_expired(tc); break; }
+        __nanosleep(kPollBackoffNs);   // failed polls of 148 CTAs load the L2 lines the producers are storing to
     }
 #pragma unroll
     for (int k = 0; k < 8; ++k) v[k] = __uint_as_float((unsigned)e[k]);
@@ -176,6 +177,7 @@ __device__ __forceinline__ void load8(const void* base, long long i, float (&v)[
 __device__ __forceinline__ void tag_ensure(TagCtx& tc) {
     if (!tc.begun) tag_begin(tc, tc.status - 2, tc.limit);
 }
+
 
 // The same split in two: the raw 128-bit loads of a block (so that several blocks can be in flight before
 // the first conversion) and the conversion.
@@ -580,19 +582,17 @@ struct PairStream {
     int slot;                // which half of the output-scale staging buffer this job uses
 };
 
-// The row tiles (32 rows) of all jobs of a phase form one flattened list that is cut into gridDim.x
-// contiguous ranges, one per CTA (the first tiles_r CTAs get one tile more).  A CTA therefore prepares the
-// input of one job only, unless its range crosses a job boundary, and streams consecutive memory.  The split
-// is precomputed on the host: this runs on the latency-critical path between two jobs.
+// Every job of a phase has a contiguous range of CTAs of its own, sized by the host in proportion to its
+// packed bytes, and a CTA of the range owns a contiguous run of the job's row tiles (32 rows).  A CTA therefore
+// prepares the input of exactly one job per phase: a CTA with rows of two jobs would quantise two inputs one
+// after the other, a tail of 1.6-2 us that every other CTA waits for in the next phase or launch.
 // Returns the CTA's tiles of `jb`: first tile, count.
-__device__ __forceinline__ int my_tiles(const Job& jb, const Phase& ph, int& first) {
-    const int b = (int)blockIdx.x;
-    const int lo = ph.tiles_q * b + min(b, ph.tiles_r);
-    const int hi = lo + ph.tiles_q + (b < ph.tiles_r ? 1 : 0);
-    const int a = max(lo, jb.tile_start);
-    const int e = min(hi, jb.tile_start + jb.items);
-    first = a - jb.tile_start;
-    return e > a ? e - a : 0;
+__device__ __forceinline__ int my_tiles(const Job& jb, int& first) {
+    const int b = (int)blockIdx.x - jb.cta0;
+    first = 0;
+    if (b < 0 || b >= jb.ncta) return 0;
+    first = b * jb.t_q + min(b, jb.t_r);
+    return jb.t_q + (b < jb.t_r ? 1 : 0);
 }
 
 // The constants of a job that the weight stream needs, held in registers: a read of the shared-memory
@@ -625,9 +625,9 @@ __device__ __forceinline__ void stream_issue(PairStream& st, const StreamJob& sj
 // Set the cursor up and start the first weight loads of a job.  They do not depend on
 // the job's input vector, so this runs before the input is ready (for a phase-2 job:
 // before the wait for the tagged intermediate, which then overlaps with the loads).
-__device__ __forceinline__ void stream_begin(PairStream& st, const Job& jb, const Phase& ph, uint4* ring, int warp,
+__device__ __forceinline__ void stream_begin(PairStream& st, const Job& jb, uint4* ring, int warp,
                                              int lane, uint16_t* post_s, int max_items) {
-    st.my_items = my_tiles(jb, ph, st.first);
+    st.my_items = my_tiles(jb, st.first);
     const int npairs = st.my_items * jb.chunks;            // < 2^27: the products below fit 32 bits
     const int p_begin = npairs * warp / kGemvWarps;
     st.my_pairs = npairs * (warp + 1) / kGemvWarps - p_begin;
@@ -651,9 +651,9 @@ __device__ __forceinline__ void stream_begin(PairStream& st, const Job& jb, cons
     for (int d = 0; d < kStages - 1; ++d) stream_issue(st, sj, ring, lane);
 }
 
-__device__ __forceinline__ bool cta_has_items(const Job& jb, const Phase& ph) {
+__device__ __forceinline__ bool cta_has_items(const Job& jb) {
     int f;
-    return my_tiles(jb, ph, f) > 0;
+    return my_tiles(jb, f) > 0;
 }
 
 // The whole launch for one CTA: the jobs of phase 1, then the jobs of phase 2 (which poll the
@@ -676,7 +676,7 @@ __device__ __forceinline__ bool run_all(const Phase* phases, const GemvParams& P
     const int njobs = phases[0].njobs;        // same count in both phases
     auto job_of = [&](int s) -> const Job& { return phases[s >= njobs].job[s >= njobs ? s - njobs : s]; };
     auto next_step = [&](int s) {             // first step >= s in which this CTA owns row tiles
-        while (s < 2 * njobs && !cta_has_items(job_of(s), phases[s >= njobs])) ++s;
+        while (s < 2 * njobs && !cta_has_items(job_of(s))) ++s;
         return s;
     };
     PairStream st;
@@ -684,10 +684,7 @@ __device__ __forceinline__ bool run_all(const Phase* phases, const GemvParams& P
     int s = next_step(0);
     if (s < 2 * njobs) {
         const Job& j0 = job_of(s);
-        stream_begin(st, j0, phases[s >= njobs], ring, warp, lane, post_s, P.max_items);
-        // the input scales are constants of the layer: pull them towards L2 while the previous kernel drains
-        if (s < njobs && j0.pre && tid * 64 < j0.K)
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(static_cast<const char*>(j0.pre) + 128 * (size_t)tid));
+        stream_begin(st, j0, ring, warp, lane, post_s, P.max_items);
     }
     // Programmatic dependent launch: everything above (descriptor copy, first weight loads) may overlap
     // with the tail of the previous kernel in the stream; the activations and the scratch (shared with
@@ -803,7 +800,7 @@ __device__ __forceinline__ bool run_all(const Phase* phases, const GemvParams& P
         // overlap the address arithmetic below) and before any barrier, whose wait the loads overlap.
         const int s_next = next_step(s + 1);
         if (s_next < 2 * njobs)
-            stream_begin(st, job_of(s_next), phases[s_next >= njobs], ring, warp, lane, post_s, P.max_items);
+            stream_begin(st, job_of(s_next), ring, warp, lane, post_s, P.max_items);
         __syncthreads();  // xq / s1 are reused by the next job
         s = s_next;
     }
@@ -932,14 +929,44 @@ int nq_gemv_group_fwd(const nq_linear_desc* d, int n_linears, int T, int dtype, 
         const int st = dynamic_smem_limit(dev, &smem_limit);
         if (st != NQ_OK) return st;
     }
-    const int grid = sm_count();
-    int tot1 = 0, tot2 = 0;
-    for (int i = 0; i < n_linears; ++i) {
-        tot1 += (d[i].R + 31) / 32;
-        tot2 += (d[i].M + 31) / 32;
+    // Number of CTAs: the dependent chain of a launch (broadcast of the input, hand-over of the intermediate,
+    // barriers, completion) costs about 15 ns per participating CTA, the stream gains from every SM.  Small
+    // launches therefore run on fewer CTAs than there are SMs (measured optimum on 148 SMs: 80-96 CTAs up to
+    // 5 MB of packed factors, 128 around 10 MB, all of them from 20 MB), which also lets the next kernel's CTAs
+    // start their prologue on the idle SMs.
+    const int sms = sm_count();
+    size_t packed = 0;
+    for (int i = 0; i < n_linears; ++i) packed += (size_t)d[i].R * ((size_t)d[i].N + d[i].M) / 8;
+    int grid = packed < (size_t)(3 << 20) ? sms * 3 / 5 : packed < (size_t)(7 << 20) ? sms * 13 / 20
+               : packed < (size_t)(20 << 20) ? sms * 7 / 8 : sms;
+    if (grid < kMaxJobs) grid = sms;
+    int cta_n[2][kMaxJobs];
+    int max_items = 1;
+    for (int ph = 0; ph < 2; ++ph) {
+        // deal the CTAs to the jobs of the phase: every job gets a contiguous range, sized so that the longest
+        // per-CTA stream (row tiles x chunks) is as short as possible
+        int items[kMaxJobs], chunks[kMaxJobs];
+        for (int i = 0; i < n_linears; ++i) {
+            items[i] = ((ph ? d[i].M : d[i].R) + 31) / 32;
+            chunks[i] = ((ph ? d[i].R : d[i].N) + 255) / 256;
+            cta_n[ph][i] = 1;
+        }
+        for (int used = n_linears; used < grid; ++used) {
+            int best = -1;
+            long long best_cost = -1;
+            for (int i = 0; i < n_linears; ++i) {
+                if (cta_n[ph][i] >= items[i]) continue;      // one tile per CTA already
+                const long long cost = (long long)((items[i] + cta_n[ph][i] - 1) / cta_n[ph][i]) * chunks[i];
+                if (cost > best_cost) { best_cost = cost; best = i; }
+            }
+            if (best < 0) break;
+            ++cta_n[ph][best];
+        }
+        for (int i = 0; i < n_linears; ++i) {
+            const int most = (items[i] + cta_n[ph][i] - 1) / cta_n[ph][i];
+            max_items = most > max_items ? most : max_items;
+        }
     }
-    const int tot = tot1 > tot2 ? tot1 : tot2;
-    const int max_items = (tot + grid - 1) / grid;       // longest contiguous range a CTA can get
     const int kpad = (maxK + 255) / 256 * 256;
     const int stride = kpad + 32;  // 32 mod 128: conflict-free 64-bit fragment loads
 
@@ -966,7 +993,7 @@ int nq_gemv_group_fwd(const nq_linear_desc* d, int n_linears, int T, int dtype, 
         P.max_items = max_items;
         P.phase[0].njobs = P.phase[1].njobs = n_linears;
         size_t off = kHeaderBytes;
-        int tiles_a = 0, tiles_b = 0;   // running tile counts of the two phases
+        int cta_a = 0, cta_b = 0;       // first CTA of the next job's range in the two phases
         for (int i = 0; i < n_linears; ++i) {
             const nq_linear_desc& L = d[i];
             void* tbuf = static_cast<char*>(scratch) + off;   // {fp32, tag} pairs, 8 bytes per element
@@ -987,8 +1014,11 @@ int nq_gemv_group_fwd(const nq_linear_desc* d, int n_linears, int T, int dtype, 
             a.out_kind = KIND_T;
             a.vec = (L.N % 8 == 0) && (L.ldx % 8 == 0) && aligned16(a.in) && aligned16(L.s_in);
             a.post_vec = L.s_mid && (L.R % 8 == 0) && aligned16(L.s_mid);
-            a.tile_start = tiles_a;
-            tiles_a += a.items;
+            a.cta0 = cta_a;
+            a.ncta = cta_n[0][i];
+            a.t_q = a.items / a.ncta;
+            a.t_r = a.items % a.ncta;
+            cta_a += a.ncta;
             Job& b = P.phase[1].job[i];
             b.tiles = static_cast<const uint4*>(L.u_tiles);
             b.in = tbuf;
@@ -1008,14 +1038,11 @@ int nq_gemv_group_fwd(const nq_linear_desc* d, int n_linears, int T, int dtype, 
             b.out_kind = dtype;
             b.vec = (L.R % 8 == 0);  // the intermediate lives in the 256-byte aligned scratch
             b.post_vec = (L.M % 8 == 0) && aligned16(L.s_out);
-            b.tile_start = tiles_b;
-            tiles_b += b.items;
-        }
-        P.phase[0].total_tiles = tiles_a;
-        P.phase[1].total_tiles = tiles_b;
-        for (int ph = 0; ph < 2; ++ph) {
-            P.phase[ph].tiles_q = P.phase[ph].total_tiles / grid;
-            P.phase[ph].tiles_r = P.phase[ph].total_tiles % grid;
+            b.cta0 = cta_b;
+            b.ncta = cta_n[1][i];
+            b.t_q = b.items / b.ncta;
+            b.t_r = b.items % b.ncta;
+            cta_b += b.ncta;
         }
         void* args[] = {&P};
         const void* fn = cg_for(tn) == 1 ? (const void*)gemv_group_kernel<1> : (const void*)gemv_group_kernel<2>;
