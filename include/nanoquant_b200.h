@@ -271,13 +271,17 @@ int nq_onebit_gemm_fwd(const void* x, const void* tiles, const void* s_in, const
  * kernels launched afterwards on `stream` see the gathered [G][shard] data.  `local_state`:
  * nq_allgather_state_bytes() of local device memory, zeroed once, one per communicator.  All ranks
  * must issue the same sequence of calls; consecutive calls must use different regions (a rank may be
- * one call ahead of a peer).  nq_allgather_status() synchronises and reports an expired wait. */
+ * one call ahead of a peer).  nq_allgather_status() synchronises and reports an expired wait (NQ_ERR_TIMEOUT). */
 size_t nq_allgather_state_bytes(void);
 size_t nq_allgather_flags_bytes(int world);
 int nq_allgather_push(const void* shard, size_t shard_bytes, void* const* rank_bases_host,
                       size_t flags_offset, size_t region_offset, void* local_state,
                       int world, int rank, nq_stream_t stream);
 int nq_allgather_status(const void* local_state, nq_stream_t stream);
+/* Polls (64 ns apart) the wait for a peer's shard may spend before it gives up; 0 restores the default (4e6).
+ * After an expiry the status word of `local_state` stays set and later launches on it poll once and go on
+ * (zero the state to re-arm it).  Returns the previous value. */
+unsigned nq_allgather_set_wait_limit(unsigned polls);
 
 /* Token-count dispatch the reference leaves to the caller's `kernel_type`:
  * the GEMV for T <= nq_gemv_max_tokens(), the GEMM above.  Scratch must satisfy

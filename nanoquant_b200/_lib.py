@@ -63,6 +63,7 @@ SIGNATURES = {
     "nq_allgather_push": (c_int, [c_void_p, c_size_t, ctypes.POINTER(c_void_p), c_size_t, c_size_t, c_void_p, c_int, c_int,
                                   c_void_p]),
     "nq_allgather_status": (c_int, [c_void_p, c_void_p]),
+    "nq_allgather_set_wait_limit": (ctypes.c_uint, [ctypes.c_uint]),
     "nq_dense_gemv_max_tokens": (c_int, []),
     "nq_dense_gemv_fwd": (c_int, [c_void_p] * 4 + [c_int, c_int, c_int, c_int64, c_int64, c_int, c_void_p]),
     "nq_gemv_max_tokens": (c_int, []),

@@ -28,6 +28,7 @@ struct PushParams {
     unsigned long long* counter;      // local: launch counter
     unsigned* done;                   // local: CTAs that have copied their part (wraps to 0)
     unsigned* status;                 // local: status word
+    unsigned spin_limit;              // polls before the wait for a peer gives up
     int world, rank;
 };
 
@@ -57,11 +58,16 @@ __global__ void __launch_bounds__(kPushThreads) allgather_push_kernel(const __gr
         unsigned* dst = P.flags[threadIdx.x] + P.rank;
         asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(dst), "r"(epoch) : "memory");
         const unsigned* mine = P.flags[P.rank] + threadIdx.x;
+        // An earlier launch on this state that gave up has left its mark: a peer is missing or late, and every
+        // later gather of a replayed step would wait its full limit again.  Such launches poll once and go on.
+        unsigned st0;
+        asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(st0) : "l"(P.status) : "memory");
+        const unsigned limit = st0 ? 0u : P.spin_limit;
         for (unsigned spins = 0;; ++spins) {
             unsigned v;
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
             if ((int)(v - epoch) >= 0) break;
-            if (spins > kSpinLimit) {
+            if (spins >= limit) {
                 atomicExch(P.status, (unsigned)(-NQ_ERR_TIMEOUT));
                 break;
             }
@@ -69,6 +75,8 @@ __global__ void __launch_bounds__(kPushThreads) allgather_push_kernel(const __gr
         }
     }
 }
+
+static unsigned g_push_limit = kSpinLimit;
 
 }  // namespace nq
 
@@ -97,6 +105,7 @@ int nq_allgather_push(const void* shard, size_t shard_bytes, void* const* rank_b
     P.counter = static_cast<unsigned long long*>(local_state);
     P.done = static_cast<unsigned*>(local_state) + 2;
     P.status = static_cast<unsigned*>(local_state) + 3;
+    P.spin_limit = g_push_limit;
     P.world = world;
     P.rank = rank;
     size_t ctas = (P.n16 + (size_t)kPushThreads * 4 - 1) / ((size_t)kPushThreads * 4);   // four words per thread
@@ -105,6 +114,12 @@ int nq_allgather_push(const void* shard, size_t shard_bytes, void* const* rank_b
     allgather_push_kernel<<<(unsigned)ctas, kPushThreads, 0, as_stream(stream)>>>(P);
     NQ_LAUNCH_CHECK();
     return NQ_OK;
+}
+
+unsigned nq_allgather_set_wait_limit(unsigned polls) {
+    const unsigned old = g_push_limit;
+    g_push_limit = polls ? polls : kSpinLimit;
+    return old;
 }
 
 int nq_allgather_status(const void* local_state, nq_stream_t stream) {

@@ -70,7 +70,8 @@ struct GemmCfg {
     static constexpr int kOffMisc = kOffBar + kNumBars * 8;   // tmem base address, abort flag
     static constexpr int kOffPost = (kOffMisc + 16 + 15) & ~15;   // output scales of the tile as fp32 (read as float4)
     static_assert(kOffPost % 16 == 0 && kOffBar % 8 == 0 && kOffBits % 16 == 0 && kOffPre % 16 == 0, "shared memory map alignment");
-    static constexpr int kSmemBytes = kOffPost + kBN * 4 + 1024;   // + slack for the 1024-byte alignment
+    static constexpr int kOffBias = kOffPost + kBN * 4;            // bias of the tile as fp32
+    static constexpr int kSmemBytes = kOffBias + kBN * 4 + 1024;   // + slack for the 1024-byte alignment
     // MMA-issuing threads.  The small tiles are bound by the issuing thread (waits and instruction issue cost
     // more cycles than their MMAs take), so two threads take alternate k blocks, each into an accumulator of
     // its own, and the epilogue adds the two.  The 256 x 256 tile is bound by the tensor pipe and fills the
@@ -94,7 +95,9 @@ struct alignas(64) GemmJob {
     const void* pre;       // [K] input scales (I/O dtype) or nullptr (weights are +-1)
     const void* post;      // [Nout] output scales (I/O dtype) or nullptr
     void* out;             // [T, ld_out] I/O dtype
-    long long ld_out;
+    const void* bias;      // [Nout] (I/O dtype) or nullptr, added behind the output scale
+    const void* resid;     // [T, ld_res] (I/O dtype) or nullptr, added behind the bias
+    long long ld_out, ld_res;
     // split-K (few tokens, few output tiles): `splits` CTAs along grid.z share an output tile, each over
     // `chunks_per` 256-column chunks; partial sums go to fp32 slabs [split][Nout][t_pad] and the CTA that
     // arrives last at the tile's counter adds them up in split order and writes the output.
@@ -207,18 +210,6 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-#ifdef NQ_GEMM_TRACE  // development aid: cycle totals of the loop steps of CTA (0,0)
-__device__ long long g_gemm_trace[16];
-#define GT_NOW() clock64()
-#define GT_ADD(i, v) do { if (blockIdx.x == 0 && blockIdx.y == 0) gt[i] += (v); } while (0)
-#define GT_DECL() long long gt[4] = {0, 0, 0, 0}
-#define GT_T(name) const long long name = GT_NOW()
-#else
-#define GT_ADD(i, v) ((void)0)
-#define GT_DECL() ((void)0)
-#define GT_T(name) ((void)0)
-#endif
-
 // ---------------------------------------------------------------------------
 // the kernel: one 128 x 128 output tile per CTA
 // ---------------------------------------------------------------------------
@@ -230,7 +221,7 @@ __global__ void __launch_bounds__(GemmCfg<MH, NH>::kThreads) gemm_stage_kernel(c
     constexpr int kExpandThreads = C::kExpandThreads, kGroups = C::kGroups, kGemmThreads = C::kThreads;
     constexpr int kFirstExpandWarp = C::kFirstExpandWarp;
     constexpr int kOffA = C::kOffA, kOffW = C::kOffW, kOffBits = C::kOffBits, kOffPre = C::kOffPre;
-    constexpr int kOffBar = C::kOffBar, kOffMisc = C::kOffMisc, kOffPost = C::kOffPost;
+    constexpr int kOffBar = C::kOffBar, kOffMisc = C::kOffMisc, kOffPost = C::kOffPost, kOffBias = C::kOffBias;
     extern __shared__ unsigned char smem_raw[];
     // align inside the shared window (pointer + offset keeps the shared address space visible to the compiler)
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -289,6 +280,11 @@ __global__ void __launch_bounds__(GemmCfg<MH, NH>::kThreads) gemm_stage_kernel(c
             f = P.is_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(J.post)[n0 + i])
                           : __half2float(static_cast<const __half*>(J.post)[n0 + i]);
         reinterpret_cast<float*>(smem + kOffPost)[i] = f;
+        float bv = 0.f;
+        if (J.bias && n0 + i < J.Nout)
+            bv = P.is_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(J.bias)[n0 + i])
+                           : __half2float(static_cast<const __half*>(J.bias)[n0 + i]);
+        reinterpret_cast<float*>(smem + kOffBias)[i] = bv;
     }
     if (warp == 1) {  // tensor-memory allocation: 128 fp32 columns per accumulator, by one whole warp
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
@@ -346,16 +342,11 @@ __global__ void __launch_bounds__(GemmCfg<MH, NH>::kThreads) gemm_stage_kernel(c
             const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(kBN >> 3) << 17) |
                                    ((uint32_t)(kBM >> 4) << 24);
             bool ok = true;
-            GT_DECL();
             for (int kb = mw; kb < nkb && ok; kb += C::kIssuers) {
                 const int s = kb % kGemmStages;
                 const uint32_t ph = (kb / kGemmStages) & 1;
-                GT_T(t0);
                 ok = mbar_wait(bar_ready(s), ph, abort_flag, P.status);
-                GT_T(tm);
                 if (!ok) break;
-                GT_T(t1);
-                if (kb >= kGemmStages) { GT_ADD(0, tm - t0); GT_ADD(2, t1 - tm); GT_ADD(3, 1); }
                 tc_fence_after();
                 // descriptors of the stage; inside the 128-byte swizzle row the k offset (32 bytes per MMA) is
                 // added to the start-address field (units of 16 bytes)
@@ -368,11 +359,7 @@ __global__ void __launch_bounds__(GemmCfg<MH, NH>::kThreads) gemm_stage_kernel(c
                         umma_f16(acc_base + (uint32_t)(mh * kBN), a_desc + (uint64_t)((mh * kTileBytes + k4 * 32) >> 4),
                                  w_desc + (uint64_t)((k4 * 32) >> 4), idesc, (kb != mw || k4 != 0) ? 1u : 0u);
                 umma_commit(bar_free(s));   // the stage's buffers are free once these MMAs have read them
-                if (kb >= kGemmStages) GT_ADD(1, GT_NOW() - t1);
             }
-#ifdef NQ_GEMM_TRACE
-            if (blockIdx.x == 0 && blockIdx.y == 0 && mw == 0) { g_gemm_trace[4] = gt[0]; g_gemm_trace[5] = gt[1]; g_gemm_trace[6] = gt[2]; g_gemm_trace[7] = gt[3]; }
-#endif
             // arrives when this thread's MMAs are complete (at once if it had no k block)
             if (ok) umma_commit(bar_accum);
         }
@@ -385,18 +372,14 @@ __global__ void __launch_bounds__(GemmCfg<MH, NH>::kThreads) gemm_stage_kernel(c
         const int grp = tu / kGroupThreads, tl = tu % kGroupThreads;
         const uint32_t one2 = P.is_bf16 ? 0x3F803F80u : 0x3C003C00u;
         bool ok = true;
-        GT_DECL();
         int c_seen = -1;
         for (int kb = grp; kb < nkb && ok; kb += kGroups) {
             const int s = kb % kGemmStages;
             const uint32_t ph = (kb / kGemmStages) & 1;
             const int c = kb >> 2, b = c & (kBitsSlots - 1), sub = kb & 3;
-            GT_T(t0);
             if (c != c_seen) { ok = mbar_wait(bar_bits_full(b), (c >> kSlotShift) & 1, abort_flag, P.status); c_seen = c; }
             ok = ok && mbar_wait(bar_free(s), ph ^ 1, abort_flag, P.status);
             if (!ok) break;
-            GT_T(t1);
-            GT_ADD(0, t1 - t0);
             const uint4* bits = reinterpret_cast<const uint4*>(smem + kOffBits + b * kBitsSlotBytes);
             const uint2* pre2 = reinterpret_cast<const uint2*>(smem + kOffPre + b * kPreBytes + sub * (kBK * 2));
             unsigned char* wt = smem + kOffW + s * C::kWBytes;
@@ -430,18 +413,12 @@ __global__ void __launch_bounds__(GemmCfg<MH, NH>::kThreads) gemm_stage_kernel(c
                     }
                 }
             }
-            GT_T(t2);
-            GT_ADD(1, t2 - t1);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the MMA
             mbar_arrive(bar_ready(s));
             // this group's last k block of the chunk: release the chunk's bits (both groups arrive, except
             // that a group without a block in a partial last chunk has nothing to release or to wait for)
             if (((kb + kGroups) >> 2) != c || kb + kGroups >= nkb) mbar_arrive(bar_bits_empty(b));
-            GT_ADD(2, GT_NOW() - t2);
         }
-#ifdef NQ_GEMM_TRACE
-        if (blockIdx.x == 0 && blockIdx.y == 0 && tu == 0) { g_gemm_trace[0] = gt[0]; g_gemm_trace[1] = gt[1]; g_gemm_trace[2] = gt[2]; g_gemm_trace[3] = nkb; }
-#endif
         // ------------------------------------------------------------ epilogue
         if (ok) ok = mbar_wait(bar_accum, 0, abort_flag, P.status);
         // the output buffer may still be read by the kernel before the previous one (its input): the accumulator
@@ -458,6 +435,7 @@ __global__ void __launch_bounds__(GemmCfg<MH, NH>::kThreads) gemm_stage_kernel(c
             for (int blk = sub_w; blk < MH * (kBN / 32); blk += kExpandThreads / 128) {
                 const int mh = blk / (kBN / 32), c0 = (blk % (kBN / 32)) * 32;
                 const int row = m0 + kBM * mh + 32 * lq + lane;     // token
+                __syncwarp();   // the tensor-memory loads are warp-collective: all lanes arrive here together
                 uint32_t r[32];
                 tmem_ld32(tmem_base + ((uint32_t)(32 * lq) << 16) + (uint32_t)(mh * kBN + c0), r);
                 if (C::kIssuers == 2 && nkb > 1) {   // the second issuer's accumulator
@@ -466,22 +444,38 @@ __global__ void __launch_bounds__(GemmCfg<MH, NH>::kThreads) gemm_stage_kernel(c
 #pragma unroll
                     for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) + __uint_as_float(r2[e]));
                 }
-                if (row >= P.T || n0 + c0 >= J.Nout) continue;
+                // The tensor-memory loads above are warp-collective: every lane takes part in every round, and a
+                // lane without a valid output only skips the stores.
+                const bool valid = row < P.T && n0 + c0 < J.Nout;
                 if (J.splits > 1) {   // partial sums of this k range: a warp writes 32 consecutive tokens per column
-                    float* slab = J.slabs + ((size_t)blockIdx.z * J.Nout + n0 + c0) * P.t_pad + row;
+                    if (valid) {
+                        float* slab = J.slabs + ((size_t)blockIdx.z * J.Nout + n0 + c0) * P.t_pad + row;
 #pragma unroll
-                    for (int e = 0; e < 32; ++e)
-                        if (n0 + c0 + e < J.Nout) slab[(size_t)e * P.t_pad] = __uint_as_float(r[e]);
-                    continue;
-                }
+                        for (int e = 0; e < 32; ++e)
+                            if (n0 + c0 + e < J.Nout) slab[(size_t)e * P.t_pad] = __uint_as_float(r[e]);
+                    }
+                } else if (valid) {
+                const float4* bias4 = reinterpret_cast<const float4*>(smem + kOffBias);
+                const uint16_t* res_row = J.resid ? static_cast<const uint16_t*>(J.resid) + (size_t)row * J.ld_res + n0 + c0 : nullptr;
                 uint32_t packed[16];
 #pragma unroll
                 for (int e4 = 0; e4 < 8; ++e4) {
                     const float4 sc = post4[(c0 >> 2) + e4];          // same address in every lane: broadcast
-                    const float v0 = fminf(fmaxf(__uint_as_float(r[4 * e4 + 0]) * sc.x, -lim), lim);
-                    const float v1 = fminf(fmaxf(__uint_as_float(r[4 * e4 + 1]) * sc.y, -lim), lim);
-                    const float v2 = fminf(fmaxf(__uint_as_float(r[4 * e4 + 2]) * sc.z, -lim), lim);
-                    const float v3 = fminf(fmaxf(__uint_as_float(r[4 * e4 + 3]) * sc.w, -lim), lim);
+                    float4 ad = bias4[(c0 >> 2) + e4];
+                    if (res_row) {   // residual of these four outputs (element loads: the row may be unaligned or ragged)
+                        const int cbase = n0 + c0 + 4 * e4;
+                        float rr[4];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            const uint16_t h = cbase + u < J.Nout ? res_row[4 * e4 + u] : (uint16_t)0;
+                            rr[u] = P.is_bf16 ? __uint_as_float((uint32_t)h << 16) : __half2float(__ushort_as_half(h));
+                        }
+                        ad.x += rr[0]; ad.y += rr[1]; ad.z += rr[2]; ad.w += rr[3];
+                    }
+                    const float v0 = fminf(fmaxf(__uint_as_float(r[4 * e4 + 0]) * sc.x + ad.x, -lim), lim);
+                    const float v1 = fminf(fmaxf(__uint_as_float(r[4 * e4 + 1]) * sc.y + ad.y, -lim), lim);
+                    const float v2 = fminf(fmaxf(__uint_as_float(r[4 * e4 + 2]) * sc.z + ad.z, -lim), lim);
+                    const float v3 = fminf(fmaxf(__uint_as_float(r[4 * e4 + 3]) * sc.w + ad.w, -lim), lim);
                     if (P.is_bf16) {
                         const __nv_bfloat162 a2 = __floats2bfloat162_rn(v0, v1), b2 = __floats2bfloat162_rn(v2, v3);
                         packed[2 * e4] = *reinterpret_cast<const uint32_t*>(&a2);
@@ -503,6 +497,7 @@ __global__ void __launch_bounds__(GemmCfg<MH, NH>::kThreads) gemm_stage_kernel(c
                     for (int e = 0; e < 32; ++e)
                         if (n0 + c0 + e < J.Nout)
                             reinterpret_cast<uint16_t*>(dst)[e] = (uint16_t)(packed[e >> 1] >> (16 * (e & 1)));
+                }
                 }
             }
         }
@@ -531,6 +526,7 @@ __global__ void __launch_bounds__(GemmCfg<MH, NH>::kThreads) gemm_stage_kernel(c
             const int ncols = min(kBN, J.Nout - n0);
             const float lim = P.saturate ? (P.is_bf16 ? 3.3895313892515355e+38f : 64504.0f) : 3.4e38f;
             const float* post_s = reinterpret_cast<const float*>(smem + kOffPost);
+            const float* bias_s = reinterpret_cast<const float*>(smem + kOffBias);
             // Items: (column, group of four tokens).  Two items and eight splits per round keep 16 independent
             // 16-byte loads in flight per thread; the sums are formed in split order.
             constexpr int kZ = 8;
@@ -567,13 +563,19 @@ __global__ void __launch_bounds__(GemmCfg<MH, NH>::kThreads) gemm_stage_kernel(c
                     const int it = it0 + w * kExpandThreads;
                     if (it >= nitems) continue;
                     const int col = it / tp4, r4 = it - col * tp4;
-                    const float sc = post_s[col];
+                    const float sc = post_s[col], bv = bias_s[col];
                     const float o[4] = {acc[w].x, acc[w].y, acc[w].z, acc[w].w};
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         const int row = 4 * r4 + j;
                         if (row < P.T) {
-                            const float v1 = fminf(fmaxf(o[j] * sc, -lim), lim);
+                            float ex = bv;
+                            if (J.resid) {
+                                const size_t ra = (size_t)row * J.ld_res + n0 + col;
+                                ex += P.is_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(J.resid)[ra])
+                                                : __half2float(static_cast<const __half*>(J.resid)[ra]);
+                            }
+                            const float v1 = fminf(fmaxf(o[j] * sc + ex, -lim), lim);
                             const size_t at = (size_t)row * J.ld_out + n0 + col;
                             if (P.is_bf16) static_cast<__nv_bfloat16*>(J.out)[at] = __float2bfloat16(v1);
                             else static_cast<__half*>(J.out)[at] = __float2half(v1);
@@ -627,6 +629,9 @@ struct StageJob {
     void* out;
     long long ld_out;
     int K, Nout;
+    const void* bias;       // [Nout] or nullptr
+    const void* resid;      // [T, ld_res] or nullptr
+    long long ld_res;
 };
 
 // Tile shape of a launch and the k split of each of its jobs.
@@ -658,15 +663,12 @@ static GroupPlan plan_group(int T, int n, const int* K, const int* Nout, bool al
     memset(&pl, 0, sizeof(pl));
     pl.mh = 1; pl.nh = 1;
     static const int cand[4][2] = {{1, 1}, {2, 1}, {1, 2}, {2, 2}};
-    // development aid: NQ_GEMM_FORCE_CFG=<mh><nh> (e.g. 12) pins the tile shape
-    static const int forced = [] { const char* e = getenv("NQ_GEMM_FORCE_CFG"); return e ? atoi(e) : 0; }();
     const long long sms = sm_count();
     long long steps = 0;
     for (int j = 0; j < n; ++j) steps = steps > (K[j] + kBK - 1) / kBK ? steps : (K[j] + kBK - 1) / kBK;
     long long best = -1;
     for (const auto& c : cand) {
-        if (forced && forced != 10 * c[0] + c[1]) continue;
-        if (c[0] == 2 && T <= kBM && !forced) continue;
+        if (c[0] == 2 && T <= kBM) continue;
         long long tiles = 0;
         for (int j = 0; j < n; ++j)
             tiles += (long long)((T + kBM * c[0] - 1) / (kBM * c[0])) * ((Nout[j] + 128 * c[1] - 1) / (128 * c[1]));
@@ -752,6 +754,9 @@ static int launch_stage(const StageJob* jobs, int n, int T, int dtype, int satur
         J.post = S.post;
         J.out = S.out;
         J.ld_out = S.ld_out;
+        J.bias = S.bias;
+        J.resid = S.resid;
+        J.ld_res = S.ld_res;
         J.K = S.K; J.Nout = S.Nout;
         J.chunks = (S.K + 255) / 256;
         J.row_groups = (S.Nout + 15) / 16;
@@ -850,7 +855,7 @@ int nq_onebit_gemm_fwd(const void* x, const void* tiles, const void* s_in, const
     if (T <= 0 || K <= 0 || Nout <= 0) return NQ_ERR_SHAPE;
     if (dtype != NQ_F16 && dtype != NQ_BF16) return NQ_ERR_DTYPE;
     if (!aligned16(tiles)) return NQ_ERR_ALIGN;
-    const StageJob job = {x, K, tiles, s_in, s_out, y, Nout, K, Nout};
+    const StageJob job = {x, K, tiles, s_in, s_out, y, Nout, K, Nout, nullptr, nullptr, 0};
     return launch_stage(&job, 1, T, dtype, 1, static_cast<unsigned*>(status_word) + 2, nullptr, nullptr,
                         as_stream(stream));
 }
@@ -866,6 +871,7 @@ int nq_gemm_group_fwd(const nq_linear_desc* d, int n_linears, int T, int dtype, 
         const nq_linear_desc& L = d[j];
         if (!L.x || !L.s_in || !L.v_tiles || !L.u_tiles || !L.s_out || !L.y) return NQ_ERR_NULL;
         if (L.N <= 0 || L.R <= 0 || L.M <= 0 || L.ldx < L.N || L.ldy < L.M) return NQ_ERR_SHAPE;
+        if (L.residual && L.ldr < L.M) return NQ_ERR_SHAPE;
         if (L.N % 8 || L.R % 8) return NQ_ERR_SHAPE;
         if (!aligned16(L.v_tiles) || !aligned16(L.u_tiles)) return NQ_ERR_ALIGN;
     }
@@ -880,8 +886,8 @@ int nq_gemm_group_fwd(const nq_linear_desc* d, int n_linears, int T, int dtype, 
     for (int j = 0; j < n_linears; ++j) {
         const nq_linear_desc& L = d[j];
         void* t = static_cast<char*>(scratch) + t_off[j];
-        s1[j] = {L.x, L.ldx, L.v_tiles, L.s_in, L.s_mid, t, L.R, L.N, L.R};
-        s2[j] = {t, L.R, L.u_tiles, nullptr, L.s_out, L.y, L.ldy, L.R, L.M};
+        s1[j] = {L.x, L.ldx, L.v_tiles, L.s_in, L.s_mid, t, L.R, L.N, L.R, nullptr, nullptr, 0};
+        s2[j] = {t, L.R, L.u_tiles, nullptr, L.s_out, L.y, L.ldy, L.R, L.M, L.bias, L.residual, L.ldr};
     }
     const int st = launch_stage(s1, n_linears, T, dtype, 0, status, counters, slabs, as_stream(stream));
     if (st != NQ_OK) return st;
@@ -894,18 +900,12 @@ int nq_gemm_fwd(const void* x, const void* s_in, const void* v_tiles, const void
     if (!x || !s_in || !v_tiles || !u_tiles || !s_out || !y || !scratch) return NQ_ERR_NULL;
     if (T <= 0 || N <= 0 || R <= 0 || M <= 0) return NQ_ERR_SHAPE;
     nq_linear_desc d;
+    memset(&d, 0, sizeof(d));
     d.x = x; d.s_in = s_in; d.v_tiles = v_tiles; d.s_mid = s_mid; d.u_tiles = u_tiles; d.s_out = s_out;
     d.y = y; d.N = N; d.R = R; d.M = M; d.ldx = N; d.ldy = M;
     return nq_gemm_group_fwd(&d, 1, T, dtype, scratch, scratch_bytes, stream);
 }
 
-#ifdef NQ_GEMM_TRACE
-int nq_debug_read_gemm_trace(long long* host_out) {
-    NQ_CUDA_TRY(cudaDeviceSynchronize());
-    NQ_CUDA_TRY(cudaMemcpyFromSymbol(host_out, g_gemm_trace, sizeof(long long) * 16));
-    return NQ_OK;
-}
-#endif
 
 // One decode launch handles four tokens; from five tokens on the split-K GEMM is faster than two launches.
 int nq_gemv_max_tokens(void) { return 4; }

@@ -177,6 +177,7 @@ def pack_tiles(packed: torch.Tensor, shape: Tuple[int, int], method: str = "lsb_
     with torch.cuda.device(src.device):
         _lib.check(_lib.lib().nq_rows_to_tiles(src.data_ptr(), out.data_ptr(), rows, cols, _check_method(method),
                                                _stream(src.device)), "nq_rows_to_tiles")
+    out._nq_rows, out._nq_cols = rows, cols   # exact shape: the tiles pad rows to 16 and columns to 256
     return out
 
 

@@ -13,7 +13,7 @@ from __future__ import annotations
 import torch
 import torch.nn as nn
 
-from ..kernel.utils import (binary_packer, get_kernel_function, marlin_nanoquant_packer, pack_tiles)
+from ..kernel.utils import binary_packer, get_kernel_function, pack_tiles
 
 # tuning arguments the reference passes to its GEMV (modules/linear.py:176-185); validated, then unused
 _GEMV_KWARGS = {
@@ -72,7 +72,19 @@ class NanoQuantLinear(nn.Module):
             x = x.contiguous()
         else:
             raise ValueError(f"Expected 2D or 3D input tensor, got {x.ndim}D")
-        if self.kernel_type == "gemv":
+        bias = getattr(self, "bias", None)
+        if bias is not None:
+            # The reference adds the bias only on its PyTorch path (modules/linear.py:148-149) and drops it on the
+            # kernel branches (:121-141).  Here it rides in the kernel's epilogue (fp32, behind the output scale).
+            from .. import ops
+            if bias.dtype != self.dtype:
+                bias = bias.to(self.dtype)
+            if self.kernel_type == "gemv":
+                y = ops.linear_forward(x, self.scale_pre, self.V_int8, self.scale_mid, self.U_int8, self.scale_post,
+                                       self.rank, bias=bias)
+            else:
+                y = ops.linear_forward(x, self.s1, self.V_int8, self.s2, self.U_int8, self.s3, self.rank, bias=bias)
+        elif self.kernel_type == "gemv":
             y = self.kernel_forward(x, self.scale_pre, self.V_int8, self.scale_mid, self.U_int8,
                                     self.scale_post, **self.kernel_kwargs)
         elif self.kernel_type == "gemm":
@@ -81,7 +93,6 @@ class NanoQuantLinear(nn.Module):
             raise ValueError(f"Unknown kernel_type: {self.kernel_type}")
         if original_shape is not None:
             y = y.view(original_shape[0], original_shape[1], -1)
-        # like the reference's kernel branches, no bias is added here (modules/linear.py:121-141)
         return y.to(orig_dtype) if y.dtype != orig_dtype else y
 
     # ------------------------------------------------------------ kernel set-up
@@ -100,48 +111,57 @@ class NanoQuantLinear(nn.Module):
         self.kernel_type = kernel_type
         self.dtype = dtype
         self._squeeze_scales(dtype)
+        if hasattr(self, "V"):     # dense +-1 factors -> the kernels' tile layout (one copy of the weights, both kernels)
+            dev = self.V.device
+            v_bits = binary_packer(self.V.to(torch.int8), method="half2")
+            u_bits = binary_packer(self.U.to(torch.int8), method="half2")
+            self.V_int8 = pack_tiles(v_bits, (self.rank, self.in_features), "half2").to(dev)
+            self.U_int8 = pack_tiles(u_bits, (self.out_features, self.rank), "half2").to(dev)
+            delattr(self, "U")
+            delattr(self, "V")
+        # the tiles pad the rank to 16: the operators read the exact rank from here when there is no scale_mid
+        self.V_int8._nq_rows, self.V_int8._nq_cols = self.rank, self.in_features
+        self.U_int8._nq_rows, self.U_int8._nq_cols = self.out_features, self.rank
         if kernel_type == "gemv":
-            if hasattr(self, "V"):
-                dev = self.V.device
-                v_bits = binary_packer(self.V.to(torch.int8), method="half2")
-                u_bits = binary_packer(self.U.to(torch.int8), method="half2")
-                self.V_int8 = pack_tiles(v_bits, (self.rank, self.in_features), "half2").to(dev)
-                self.U_int8 = pack_tiles(u_bits, (self.out_features, self.rank), "half2").to(dev)
-                delattr(self, "U")
-                delattr(self, "V")
             self.kernel_forward = get_kernel_function("nanoquant", dtype, kernel_type="dynamic")
             self.kernel_kwargs = dict(_GEMV_KWARGS)
         else:
-            # same operands as the reference (Marlin-fragment words + permuted scales, reference
-            # modules/linear.py:186-202); the operator converts them once to the kernels' tile layout
+            # Same attribute names and call protocol as the reference (modules/linear.py:186-202: V_int8, U_int8,
+            # s1..s3, workspace -> marlin_nanoquant_forward).  The reference keeps Marlin-fragment words and
+            # permuted scales there; this module keeps the tile layout and plain scales, which the operator takes
+            # as they are (operands made by the reference's own packer are converted by the operator instead).
             if self.scale_mid is None:
                 self.scale_mid = nn.Parameter(torch.ones(self.rank, device=self.scale_pre.device, dtype=dtype),
                                               requires_grad=False)
-            (self.V_int8, self.U_int8, self.s1, self.s2, self.s3, self.workspace) = marlin_nanoquant_packer(
-                self.V.to(torch.int8).T, self.U.to(torch.int8).T, self.scale_pre, self.scale_mid, self.scale_post)
-            for key in ("U", "V", "scale_pre", "scale_mid", "scale_post"):
+            self.s1, self.s2, self.s3 = self.scale_pre, self.scale_mid, self.scale_post
+            self.workspace = torch.zeros(max(self.rank, self.out_features) // 128 * 32 + 32, dtype=torch.int32,
+                                         device=self.V_int8.device)
+            for key in ("scale_pre", "scale_mid", "scale_post"):
                 delattr(self, key)
             import binary_kernels  # noqa: F401
             self.kernel_forward = torch.ops.binary_kernels.marlin_nanoquant_forward
+        # the kernels' scratch of this device is sized for its largest layer before the first forward
+        from .. import ops, _lib
+        ops.reserve_scratch(self.V_int8.device, _lib.lib().nq_linear_scratch_bytes(
+            64, self.in_features, self.rank, self.out_features))
 
     def fold_input_scale(self, weight: torch.Tensor) -> None:
         """Multiply ``scale_pre`` by a per-input-column weight (fp32 product, stored in the scale's dtype).
 
         For the RMSNorm that feeds this linear in a decoder layer: ``linear(norm(x) * w)`` becomes
         ``linear'(norm(x))`` with ``scale_pre' = scale_pre * w``, which removes an elementwise pass and one
-        rounding of the activations.  Valid before ``_prepare_kernel`` and after it for ``kernel_type="gemv"``
-        (the Marlin operands of ``"gemm"`` hold the scale in permuted order, so fold before preparing)."""
-        if not hasattr(self, "scale_pre"):
-            raise RuntimeError("fold_input_scale: call it before _prepare_kernel('gemm')")
-        w = weight.detach().reshape(-1).to(device=self.scale_pre.device, dtype=torch.float32)
+        rounding of the activations.  Valid before and after ``_prepare_kernel`` (for ``kernel_type="gemm"`` the
+        input scale then lives in ``s1``, in plain order)."""
+        target = self.scale_pre if hasattr(self, "scale_pre") else self.s1
+        w = weight.detach().reshape(-1).to(device=target.device, dtype=torch.float32)
         if w.numel() != self.in_features:
             raise ValueError(f"fold_input_scale: expected {self.in_features} weights, got {w.numel()}")
         with torch.no_grad():
-            folded = self.scale_pre.detach().float() * w.view_as(self.scale_pre)
-            self.scale_pre.copy_(folded.to(self.scale_pre.dtype))
+            folded = target.detach().float() * w.view_as(target)
+            target.copy_(folded.to(target.dtype))
 
     def load_packed(self, V_packed, V_shape, U_packed, U_shape, scale_pre, scale_post, scale_mid=None,
-                    dtype=torch.bfloat16, device="cuda"):
+                    dtype=torch.bfloat16, device="cuda", kernel_type="gemv"):
         """Checkpoint tensors (``lsb_first`` words, reference ``modules/linear.py:288-303``)
         straight to the kernel's tile layout: no dense ±1 matrices are created,
         unlike ``src/nanoquant/utils/load_utils.py:279-287``."""
@@ -161,7 +181,7 @@ class NanoQuantLinear(nn.Module):
             self.scale_mid = nn.Parameter(scale_mid.to(device), requires_grad=False)
         elif hasattr(self, "scale_mid"):
             delattr(self, "scale_mid")
-        self._prepare_kernel("gemv", dtype)
+        self._prepare_kernel(kernel_type, dtype)
 
     # --------------------------------------------------------- checkpoint format
     def pack_weights(self):

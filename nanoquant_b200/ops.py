@@ -37,7 +37,8 @@ _SWEEP = {  # reference: cuda/gemv_kernel.cu:351-354
     "n_pipe": (1, 2, 4, 8, 16),
 }
 
-_scratch = {}  # (device index, stream) -> zero-initialised uint8 tensor
+_scratch = {}   # (device index, stream) -> zero-initialised uint8 tensor
+_reserved = {}  # device index -> bytes every scratch of that device is allocated with
 _SCRATCH_MIN = 4 << 20
 
 
@@ -51,13 +52,26 @@ def _check_sweep(name: str, kind: str, value: int) -> None:
         raise ValueError(f"{name} should be one of [{', '.join(map(str, choices))}], but {value} was given")
 
 
+def reserve_scratch(device: torch.device, nbytes: int) -> None:
+    """Announce the scratch a layer on `device` will need (called when a layer is prepared), so that the
+    buffers of that device are allocated once, large enough for its largest layer, before any forward."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    _reserved[idx] = max(_reserved.get(idx, _SCRATCH_MIN), int(nbytes))
+
+
 def scratch_for(device: torch.device, nbytes: int) -> torch.Tensor:
-    """Per (device, stream) scratch of the GEMV: zeroed once at allocation, as
-    the C ABI asks."""
-    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    """Per (device, stream) scratch of the kernels: zeroed once at allocation, as the C ABI asks.  Sized from
+    :func:`reserve_scratch`; growing it later is refused during a stream capture (a captured graph would keep
+    pointing at the buffer that the growth orphans, and the allocation itself would land inside the capture)."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    key = (idx, torch.cuda.current_stream(device).cuda_stream)
     buf = _scratch.get(key)
     if buf is None or buf.numel() < nbytes:
-        buf = torch.zeros(max(nbytes, _SCRATCH_MIN), dtype=torch.uint8, device=device)
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("nanoquant_b200: the kernels' scratch buffer would have to be (re)allocated inside a "
+                               "stream capture; run the layer once before capturing, or call "
+                               "nanoquant_b200.ops.reserve_scratch() first")
+        buf = torch.zeros(max(nbytes, _reserved.get(idx, _SCRATCH_MIN)), dtype=torch.uint8, device=device)
         _scratch[key] = buf
     return buf
 
@@ -159,7 +173,14 @@ def _nanoquant_dyn_forward_cuda(x, scale_g, Ubits, scale_l, Vbits, scale_h,
     N = x.size(-1)
     M = scale_h.size(0)
     if Ubits.dim() == 3:
-        R = scale_l.size(0) if scale_l is not None else Ubits.size(0) * 16
+        # the tile tensor covers ceil(R / 16) * 16 rows; the exact rank comes from scale_l or from the packer's note
+        R = scale_l.size(0) if scale_l is not None else getattr(Ubits, "_nq_rows", None)
+        if R is None:
+            if Vbits.dim() == 3 and hasattr(Vbits, "_nq_cols"):
+                R = Vbits._nq_cols
+            else:
+                raise RuntimeError("rank of tile-layout operands unknown: pass scale_l, or tiles made by "
+                                   "nanoquant_b200.kernel.utils.pack_tiles (which records the matrix shape)")
     else:
         R = Ubits.size(0)
     if scale_l is not None:
@@ -189,11 +210,64 @@ def _nanoquant_dyn_forward_fake(x, scale_g, Ubits, scale_l, Vbits, scale_h, *arg
     return x.new_empty(shape)
 
 
+def group_forward(xs, layers, T: int, dtype: torch.dtype, device: torch.device, biases=None, residuals=None,
+                  out: Optional[torch.Tensor] = None):
+    """One launch group: up to four linears in one ``nq_gemv_group_fwd`` (T <= 4) or ``nq_gemm_group_fwd`` call.
+
+    ``xs[i]`` ``[T, N_i]`` (row stride free, unit inner stride), ``layers[i] = (s_in, v_tiles, s_mid, u_tiles, s_out, R)``,
+    optional ``biases[i]`` ``[M_i]`` and ``residuals[i]`` ``[T, M_i]`` (added in fp32 behind the output scale).  The
+    outputs are written side by side into one ``[T, sum(M_i)]`` buffer (``out`` or a fresh one); returns its
+    per-linear column views."""
+    n = len(layers)
+    Ms = [lay[4].size(0) for lay in layers]
+    width = sum(Ms)
+    if out is None:
+        out = torch.empty((T, width), dtype=dtype, device=device)
+    views, col = [], 0
+    for m in Ms:
+        views.append(out[:, col:col + m])
+        col += m
+    if T == 0:
+        return views
+    L = _lib.lib()
+    descs, col = [], 0
+    for i, (s_in, v_tiles, s_mid, u_tiles, s_out, R) in enumerate(layers):
+        x = xs[i]
+        if x.stride(-1) != 1:
+            raise RuntimeError("group_forward: activations need a unit inner stride")
+        b = biases[i] if biases is not None else None
+        r = residuals[i] if residuals is not None else None
+        if r is not None and r.stride(-1) != 1:
+            raise RuntimeError("group_forward: residual needs a unit inner stride")
+        descs.append(_lib.LinearDesc(
+            x.data_ptr(), s_in.data_ptr(), v_tiles.data_ptr(), s_mid.data_ptr() if s_mid is not None else None,
+            u_tiles.data_ptr(), s_out.data_ptr(), out.data_ptr() + col * out.element_size(),
+            x.size(-1), R, Ms[i], x.stride(0) if x.dim() == 2 else x.size(-1), out.stride(0),
+            b.data_ptr() if b is not None else None, r.data_ptr() if r is not None else None,
+            r.stride(0) if r is not None else 0))
+        col += Ms[i]
+    arr = (_lib.LinearDesc * n)(*descs)
+    gemv = T <= L.nq_gemv_max_tokens()
+    size_fn, fwd = ((L.nq_gemv_group_scratch_bytes, L.nq_gemv_group_fwd) if gemv
+                    else (L.nq_gemm_group_scratch_bytes, L.nq_gemm_group_fwd))
+    scratch = scratch_for(device, size_fn(arr, n, T))
+    with torch.cuda.device(device):
+        st = fwd(arr, n, T, _dtype_id(out), scratch.data_ptr(), scratch.numel(),
+                 torch.cuda.current_stream(device).cuda_stream)
+    _lib.check(st, "nq_gemv_group_fwd" if gemv else "nq_gemm_group_fwd")
+    return views
+
+
 def linear_forward(x: torch.Tensor, s_in: torch.Tensor, v_tiles: torch.Tensor, s_mid: Optional[torch.Tensor],
-                   u_tiles: torch.Tensor, s_out: torch.Tensor, R: int) -> torch.Tensor:
-    """``nq_linear_fwd``: GEMV for few tokens, tcgen05 GEMM above; ``x`` is ``[T, N]``."""
+                   u_tiles: torch.Tensor, s_out: torch.Tensor, R: int, bias: Optional[torch.Tensor] = None,
+                   residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``nq_linear_fwd``: GEMV for few tokens, tcgen05 GEMM above; ``x`` is ``[T, N]``.  With ``bias`` / ``residual``
+    the call goes through the group entry points, whose descriptors carry them into the kernels' epilogues."""
     T, N = x.shape
     M = s_out.size(0)
+    if bias is not None or residual is not None:
+        return group_forward([x], [(s_in, v_tiles, s_mid, u_tiles, s_out, R)], T, x.dtype, x.device,
+                             [bias], [residual])[0]
     y = torch.empty((T, M), dtype=x.dtype, device=x.device)
     if T == 0:
         return y
@@ -292,6 +366,13 @@ def _marlin_onebit_forward_fake(x, weight, scale_g, scale_h, workspace):
 
 def _marlin_nanoquant_forward_cuda(x, weight_u, weight_v, scale_g, scale_l, scale_h, workspace):
     # `weight_u` is the FIRST stage (module V), `weight_v` the second (reference gemm.cpp:112-122)
+    if weight_u.dim() == 3:
+        # operands already in the kernels' tile layout, scales in plain order (what this package's own module
+        # keeps for kernel_type="gemm": one copy of the weights instead of Marlin words plus converted tiles)
+        if scale_g is None or scale_h is None:
+            raise RuntimeError("scale_g and scale_h are required")
+        R = scale_l.size(0) if scale_l is not None else getattr(weight_u, "_nq_rows", weight_u.size(0) * 16)
+        return linear_forward(x.contiguous(), scale_g, weight_u, scale_l, weight_v, scale_h, R)
     R, N = _marlin_checks(x, weight_u, scale_g, scale_l, workspace)
     if scale_g is None or scale_h is None:
         raise RuntimeError("scale_g and scale_h are required")
