@@ -136,7 +136,9 @@ class ClockSampler:
 class CpuLayer:
     """One decoder layer (7 quantised linears) of the reference's PyTorch dequantise-then-matmul
     path on the host cores: dense +-1 matrices in bf16, as the reference module keeps them
-    (src/nanoquant/modules/linear.py:69-76,90), through the oracle's restatement of its forward."""
+    (src/nanoquant/modules/linear.py:69-76,90).  When the reference's own module has been staged
+    (oracle/make_ref.py -> oracle/_ref), its `forward` (PyTorch branch, linear.py:143-150) is what runs
+    (`kind` "reference"); otherwise the oracle's restatement of those four lines (`kind` "port")."""
 
     def __init__(self, T):
         import torch
@@ -146,18 +148,41 @@ class CpuLayer:
         torch.set_num_threads(self.cores)
         g = torch.Generator().manual_seed(0)
         dt = torch.bfloat16
+        ref = None
+        try:
+            from oracle import make_ref
+            if make_ref.load() is not None:
+                import importlib
+                ref = importlib.import_module("nanoquant_ref.modules.linear")
+        except Exception:
+            ref = None
+        self.kind = "reference" if ref is not None else "port"
         self.layers = []
         for (_, N, R, M, _, _) in layer_linears():
             V = (torch.randint(0, 2, (R, N), generator=g) * 2 - 1).to(dt)
             U = (torch.randint(0, 2, (M, R), generator=g) * 2 - 1).to(dt)
             sc = lambda n: ((torch.rand(n, generator=g) + 0.5) * 0.01).to(dt)
-            self.layers.append((torch.randn(T, N, generator=g).to(dt), V, U, sc(N), sc(R), sc(M)))
+            x, a, b, c = torch.randn(T, N, generator=g).to(dt), sc(N), sc(R), sc(M)
+            if ref is not None:
+                lin = torch.nn.Linear(N, M, bias=False)
+                lin.__class__ = ref.NanoQuantLinear           # the reference loader's class swap
+                lin.init_for_inference(rank=R, has_scale_mid=True)
+                with torch.no_grad():
+                    lin.V.copy_(V); lin.U.copy_(U)
+                    lin.scale_pre.copy_(a[None]); lin.scale_mid.copy_(b[None]); lin.scale_post.copy_(c[None])
+                self.layers.append((x, lin))
+            else:
+                self.layers.append((x, V, U, a, b, c))
 
     def run_once(self):
         with self.torch.no_grad():
             t0 = time.perf_counter()
-            for (x, V, U, a, b, c) in self.layers:
-                self.oc.torch_cpu_forward(x, V, U, a, b, c)
+            if self.kind == "reference":
+                for (x, lin) in self.layers:
+                    lin(x)
+            else:
+                for (x, V, U, a, b, c) in self.layers:
+                    self.oc.torch_cpu_forward(x, V, U, a, b, c)
             return time.perf_counter() - t0
 
     def timed(self, budget_s, min_reps=5, max_reps=2000):
@@ -169,8 +194,10 @@ class CpuLayer:
         return statistics.median(times), len(times)
 
 
-def cpu_sample_text(T, reps):
-    return (f"1 of {LAYERS} decoder layers (7 linears, dense +-1 bf16 matmuls, T={T}), "
+def cpu_sample_text(T, reps, kind="port"):
+    what = ("the reference's NanoQuantLinear.forward, PyTorch branch" if kind == "reference"
+            else "oracle restatement of the reference's PyTorch branch")
+    return (f"1 of {LAYERS} decoder layers (7 linears, {what}, dense +-1 bf16 matmuls, T={T}), "
             f"median of {reps} runs, x{LAYERS} layers")
 
 
@@ -196,8 +223,8 @@ def reference_arm(args):
         "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
         "config": workload_config(T),
-        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cpu.cores, "kind": "port",
-                         "sample": cpu_sample_text(T, len(times))},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cpu.cores, "kind": cpu.kind,
+                         "sample": cpu_sample_text(T, len(times), cpu.kind)},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(out), flush=True)
@@ -216,9 +243,17 @@ def workload_config(T):
 # --------------------------------------------------------------------------------------------
 # GPU arm
 # --------------------------------------------------------------------------------------------
-# dram__bytes_read.sum + dram__bytes_write.sum over the algorithmic bytes of the captured decode launches
-# (o, gate+up, down groups: 17.50 MB against 16.82 MB; no writes reach DRAM)
-DRAM_TRAFFIC_RATIO = 1.04
+def dram_traffic_ratio():
+    """dram__bytes_read.sum + dram__bytes_write.sum over the algorithmic bytes of the captured decode launches, read
+    from the line `traffic_ratio: <x>` of the tracked ncu summary of this kernel; None when there is none."""
+    path = os.path.join(ROOT, "profiles", "gemv_group_kernel_qwen3_8b_decode.md")
+    try:
+        for line in open(path):
+            if line.strip().startswith("traffic_ratio:"):
+                return float(line.split(":", 1)[1].split()[0])
+    except (OSError, ValueError):
+        pass
+    return None
 
 
 class Step:
@@ -321,6 +356,52 @@ class StepCycle:
         return max(st.status() for st in self.steps)
 
 
+def check_step(T, dtype, device):
+    """The launch structure of the timed step on ONE decoder layer with real factors: seeded +-1 matrices packed on
+    the GPU (nq_pack_rows, nq_rows_to_tiles), the same four group launches (q/k/v, o, gate/up, down), every output
+    against the fp64 oracle.  Outside the timed region; returns max |y - y64| / max |y64| over the 7 linears."""
+    import numpy as np
+    import torch
+    from nanoquant_b200 import _lib
+    from nanoquant_b200.kernel import utils as ku
+    from oracle import nanoquant_oracle as oc
+    L = _lib.lib()
+    g = torch.Generator(device=device).manual_seed(1234)
+    scale = lambda n: ((torch.rand(n, generator=g, device=device) + 0.5) * 0.01).to(dtype)
+    x = {"h": torch.randn(T, HIDDEN, generator=g, device=device).to(dtype),
+         "i": torch.randn(T, INTER, generator=g, device=device).to(dtype)}
+    signs = lambda r, c: (torch.randint(0, 2, (r, c), generator=g, device=device, dtype=torch.int8) * 2 - 1)
+    tiles = lambda w: ku.pack_tiles(ku.pack_binary_gemv(w, method="half2"), tuple(w.shape), "half2")
+    groups, keep = {}, []
+    for (name, N, R, M, src, grp) in layer_linears():
+        V, U = signs(R, N), signs(M, R)
+        t = dict(V=V, U=U, v=tiles(V), u=tiles(U), s_in=scale(N), s_mid=scale(R), s_out=scale(M),
+                 y=torch.empty(T, M, device=device, dtype=dtype), x=x[src], name=name)
+        keep.append(t)
+        groups.setdefault(grp, []).append(
+            _lib.LinearDesc(x[src].data_ptr(), t["s_in"].data_ptr(), t["v"].data_ptr(), t["s_mid"].data_ptr(),
+                            t["u"].data_ptr(), t["s_out"].data_ptr(), t["y"].data_ptr(), N, R, M, N, M))
+    use_gemm = T >= (GEMM_MIN_TOKENS or L.nq_gemv_max_tokens() + 1)
+    fwd = L.nq_gemm_group_fwd if use_gemm else L.nq_gemv_group_fwd
+    size_fn = L.nq_gemm_group_scratch_bytes if use_gemm else L.nq_gemv_group_scratch_bytes
+    st = torch.cuda.current_stream(device).cuda_stream
+    for grp in sorted(groups):
+        arr = (_lib.LinearDesc * len(groups[grp]))(*groups[grp])
+        nb = size_fn(arr, len(arr), T)
+        scratch = torch.zeros(nb, dtype=torch.uint8, device=device)
+        _lib.check(fwd(arr, len(arr), T, _lib.NQ_BF16 if dtype == torch.bfloat16 else _lib.NQ_F16,
+                       scratch.data_ptr(), nb, st), "check launch")
+        if L.nq_scratch_status(scratch.data_ptr(), st) != 0:
+            raise SystemExit("bench.py --check: a device-side wait timed out")
+    worst = 0.0
+    f64 = lambda t_: t_.float().cpu().numpy().astype(np.float64)
+    for t in keep:
+        y64 = oc.forward_fp64(f64(t["x"]), t["V"].cpu().numpy(), t["U"].cpu().numpy(), f64(t["s_in"]), f64(t["s_mid"]),
+                              f64(t["s_out"]))
+        worst = max(worst, oc.rel_err(f64(t["y"]), y64))
+    return worst
+
+
 VOCAB = {"qwen3-8b": 151936, "llama-3.2-1b": 128256}
 
 
@@ -381,9 +462,11 @@ def side_numbers(device, dtype, step_ms):
         del step
         torch.cuda.empty_cache()
     out["lm_head_gemv"] = measure_head(device, dtype, 1, step_ms)
-    tf, ms, _, _, _ = measure_prefill(2048, 4, 3, 3, device)
-    out["prefill_2048_tokens"] = {"value": tf, "unit": "TFLOP/s", "ms_per_step": ms,
-                                  "frac_of_sustained_bf16_peak": tf / tensor_peak()[0]}
+    for model in ("llama-2-7b", "qwen3-8b"):
+        for tokens in (2048, 512, 128):
+            tf, ms, _, _, _ = measure_prefill(tokens, 4, 5, 3, device, model=model)
+            out[f"prefill_{tokens}_tokens_{model}"] = {"value": tf, "unit": "TFLOP/s", "ms_per_step": ms,
+                                                       "frac_of_sustained_bf16_peak": tf / tensor_peak()[0]}
     return out
 
 
@@ -420,6 +503,10 @@ def gpu_arm(args):
         dist.init_process_group("nccl", device_id=device)
     T = args.batch
     dtype = torch.bfloat16
+    # the launches that are about to be timed, on real factors, against the oracle (bf16 outputs: 2e-3 + half an ulp)
+    check_err = check_step(T, dtype, device) if (rank == 0 and not args.no_check) else None
+    if check_err is not None and not check_err <= 2e-3 + 2.0 ** -8:
+        raise SystemExit(f"bench.py: output check failed, max|y-y64|/max|y64| = {check_err:.3e}")
     step = StepCycle(T, dtype, device, args.layers)
     step.capture()
 
@@ -479,12 +566,16 @@ def gpu_arm(args):
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     ms, e2e_ms = times.tolist()
+    # N > 1: the replicas above are the weak-scaling value; the sharded configuration (tensor parallelism over the
+    # GPUs of this run) is measured beside it, every rank taking part
+    tp = tp_record(args, device, world, rank) if (world > 1 and not args.no_side_numbers) else None
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
 
     peak, peak_src = hbm_peak()
+    ratio = dram_traffic_ratio()
     step_s = ms * 1e-3 / args.steps
     achieved = step.bytes / step_s / 1e9
     if args.layers != LAYERS:   # profiling aid: fewer layers resident; report per-step numbers of what ran
@@ -498,13 +589,13 @@ def gpu_arm(args):
         "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": ("bf16 tcgen05 mma / f32 accumulate; bf16 in/out" if step.per_linear
                   else "s8 mma / s32 accumulate on 16-bit fixed point; bf16 in/out"), "data": "synthetic",
-        "config": dict(workload_config(T), layers_timed=args.layers,
-                       parallelism=("single gpu" if world == 1 else f"{world} independent replicas")),
+        "config": workload_config(T),
+        "parallelism": "single gpu" if world == 1 else f"{world} independent replicas",
+        "layers_timed": args.layers,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": (step.bytes / step.kernels_per_step * DRAM_TRAFFIC_RATIO if not step.per_linear else None),
-                     "traffic_source": ("ncu dram__bytes_read+write of three captured launches = 1.04 x their algorithmic "
-                                        "bytes (profiles/gemv_group_kernel_qwen3_8b_decode.md), scaled to the average launch"
-                                        if not step.per_linear else None),
+                     "traffic": (step.bytes / step.kernels_per_step * ratio if (ratio and not step.per_linear) else None),
+                     "traffic_source": ("dram__bytes_read+write over algorithmic bytes of three launches captured with ncu, "
+                                        "scaled to the average launch" if (ratio and not step.per_linear) else None),
                      "kernel": step.kernel_name,
                      "bytes_per_launch": step.bytes / step.kernels_per_step, "us_per_launch": launch_us,
                      "peak_source": peak_src},
@@ -512,6 +603,7 @@ def gpu_arm(args):
                 "h2d_bytes_per_step": sum(v.numel() * v.element_size() for v in hx.values()),
                 "d2h_bytes_per_step": hy.numel() * hy.element_size()},
         "gpu_launches": step.kernels_per_step * args.steps,
+        "checked": check_err is not None, "max_rel_err": check_err,
         "clocks": clocks,
     }
     if out_note:
@@ -520,11 +612,13 @@ def gpu_arm(args):
         del step
         torch.cuda.empty_cache()
         out["other_operating_points"] = side_numbers(device, dtype, step_s * 1e3)
+    if tp is not None:
+        out["tp"] = tp
     if not args.no_cpu_baseline and world == 1:   # the CPU baseline is reported on rank 0 of a single-GPU run only
         cpu = CpuLayer(T)
         t_layer, reps = cpu.timed(budget_s=12.0)
         out["cpu_baseline"] = {"value": T / (t_layer * LAYERS), "unit": "tokens/s", "cores": cpu.cores,
-                               "kind": "port", "sample": cpu_sample_text(T, reps)}
+                               "kind": cpu.kind, "sample": cpu_sample_text(T, reps, cpu.kind)}
     print(json.dumps(out), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -544,35 +638,31 @@ def tp_layer_linears():
     return [(n, N, rank_for_bits(N, M, BPW), M, src, grp) for (n, N, M, src, grp) in spec]
 
 
-def tp_arm(args):
-    """One decode step of the 70B-shaped linears with every U sharded over the ranks: per launch
-    group the local GEMV, then one NCCL all-gather of the group's [T, sum(M/G)] shards.  Strong scaling."""
+def measure_tp(T, layers, steps, warmup, collective, device, world, rank, shard=True):
+    """One decode (or prefill) step of `layers` Llama-3-70B-shaped layers with every U sharded by output rows over the
+    ranks: per launch group the local kernel(s), then one all-gather of the group's [T, sum(M/G)] shards.  With
+    shard=False the same step runs unsharded on this GPU alone (the one-GPU figure the sharded ones are compared
+    with).  Needs an initialised process group when world > 1.  Returns a dict (times are the max over ranks)."""
     import torch
     import torch.distributed as dist
     from nanoquant_b200 import _lib
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    device = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=device)
     L = _lib.lib()
-    T, dtype, layers = args.batch, torch.bfloat16, args.tp_layers
+    G = world if shard else 1
+    dtype = torch.bfloat16
     g = torch.Generator(device=device).manual_seed(0)   # same seed on every rank: replicated tensors agree
     rnd_bits = lambda rows, cols: torch.randint(-2**31, 2**31 - 1, ((rows + 15) // 16, (cols + 255) // 256, 128),
                                                 generator=g, device=device, dtype=torch.int32)
     scale = lambda n: ((torch.rand(n, generator=g, device=device) + 0.5) * 0.01).to(dtype)
     x = {"h": torch.randn(T, TP_HIDDEN, generator=g, device=device).to(dtype),
          "i": torch.randn(T, TP_INTER, generator=g, device=device).to(dtype)}
-    keep, steps, nbytes, scratch_bytes = [], [], 0, 0
+    keep, steps_, nbytes, scratch_bytes = [], [], 0, 0
     # collective: "peer" = nq_allgather_push on symmetric memory (one kernel per gather, graph-capturable),
     # "nccl" = all_gather_into_tensor, issued eagerly
     peer = None
-    if world > 1 and args.tp_collective == "peer":
+    if G > 1 and collective == "peer":
         from nanoquant_b200 import tp as nq_tp
         esz = 2
-        gathered = sum(world * T * sum(M // world for (_, _, _, M, _, g_) in tp_layer_linears() if g_ == grp) * esz + 256
+        gathered = sum(G * T * sum(M // G for (_, _, _, M, _, g_) in tp_layer_linears() if g_ == grp) * esz + 256
                        for grp in range(4)) * layers
         try:
             peer = nq_tp.PeerGather(gathered + 4096)
@@ -594,13 +684,13 @@ def tp_arm(args):
             # The shards of a launch group (q/k/v, gate/up) are written side by side into one [T, sum(M/G)]
             # buffer, so one all-gather per group brings every rank's block: the gathered layout is
             # [rank][T][q_r | k_r | v_r].
-            width = sum(M // world for (_, _, _, M, _, _) in groups[grp])
+            width = sum(M // G for (_, _, _, M, _, _) in groups[grp])
             ybuf = torch.empty(T, width, device=device, dtype=dtype)
             full = (peer.region((T, width), dtype) if peer is not None
-                    else torch.empty(world * T, width, device=device, dtype=dtype))
+                    else torch.empty(G * T, width, device=device, dtype=dtype))
             descs, col = [], 0
             for (name, N, R, M, src, _) in groups[grp]:
-                m = M // world
+                m = M // G
                 t = dict(v=rnd_bits(R, N), u=rnd_bits(m, R), s_in=scale(N), s_mid=scale(R), s_out=scale(m))
                 keep.append(t)
                 yptr = ybuf.data_ptr() + col * ybuf.element_size()
@@ -611,29 +701,31 @@ def tp_arm(args):
                 nbytes += R * N // 8 + R * m // 8 + 2 * (N + R + m) + 2 * T * (N + m)
             arr = (_lib.LinearDesc * len(descs))(*descs)
             scratch_bytes = max(scratch_bytes, group_bytes(arr, len(arr), T))
-            steps.append((arr, ybuf, full))
+            steps_.append((arr, ybuf, full))
     scratch = torch.zeros(scratch_bytes, dtype=torch.uint8, device=device)
-    launches_per_step = (2 if use_gemm else 1) * len(steps)
+    launches_per_step = (2 if use_gemm else 1) * len(steps_)
 
     def run():
         st = torch.cuda.current_stream(device).cuda_stream
-        for arr, ybuf, full in steps:
+        for arr, ybuf, full in steps_:
             _lib.check(group_fwd(arr, len(arr), T, _lib.NQ_BF16, scratch.data_ptr(), scratch.numel(), st), "group_fwd")
             if peer is not None:
                 peer.gather(ybuf, full)
-            elif world > 1:
+            elif G > 1:
                 dist.all_gather_into_tensor(full, ybuf)
 
     # One GPU, or the peer-memory collective: the step is replayed as a CUDA graph.  With NCCL the launches
-    # and the collectives are issued eagerly in stream order (a first attempt to capture NCCL collectives
-    # together with the cooperative GEMV launches hung; that combination is not used).
+    # and the collectives are issued eagerly in stream order: a captured NCCL collective runs on a stream of
+    # its own beside the next cooperative launch, which cannot become resident while the collective's CTAs hold
+    # SMs and wait for a peer that is itself waiting for its cooperative launch: that combination can deadlock
+    # and is not used.
     graph = None
     for _ in range(2):
         run()
     torch.cuda.synchronize(device)
     if world > 1:
         dist.barrier()
-    if world == 1 or peer is not None:
+    if G == 1 or peer is not None:
         s = torch.cuda.Stream(device)
         s.wait_stream(torch.cuda.current_stream(device))
         with torch.cuda.stream(s):
@@ -649,12 +741,12 @@ def tp_arm(args):
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize(device)
-    for _ in range(max(args.warmup, 3)):
+    for _ in range(max(warmup, 3)):
         replay()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(args.steps):
+    for _ in range(steps):
         replay()
     e1.record()
     barrier()
@@ -665,28 +757,59 @@ def tp_arm(args):
         raise SystemExit("bench.py: a device-wide wait timed out inside the GEMV kernel")
     if peer is not None and peer.status() != 0:
         raise SystemExit("bench.py: a wait for a peer's shard timed out inside the all-gather kernel")
+    step_s = ms.item() * 1e-3 / steps * (TP_LAYERS / layers)
+    per_gpu = nbytes * (TP_LAYERS / layers) / step_s / 1e9
+    res = {"tokens_per_s": T / step_s, "ms_per_step": step_s * 1e3, "per_gpu_gbs": per_gpu,
+           "hbm_frac_per_gpu": per_gpu / hbm_peak()[0], "gpus": G, "batch": T, "layers_timed": layers,
+           "collective": ("none" if G == 1 else "peer-memory kernel, CUDA graph" if peer is not None else "NCCL, eager"),
+           "kernel": "gemm_stage_kernel" if use_gemm else "gemv_group_kernel", "launches_per_step": launches_per_step}
+    del keep, steps_, scratch, graph, peer
+    torch.cuda.empty_cache()
+    return res
+
+
+def tp_record(args, device, world, rank):
+    """The sharded 70B-shaped step at this number of GPUs beside the same step on one GPU: decode batch 1 and 16
+    and a 512-token prefill, 8 of 80 layers timed and scaled.  Per-GPU roofline bytes: R*N/8 + R*M/(8G) + scales +
+    activations (the rank-R stage is replicated by design)."""
+    out = {"workload": f"llama-3-70b-shaped decoder linears at {BPW} bpw, U split by output rows over {world} GPUs, "
+                       "one all-gather per launch group", "scaling": "strong"}
+    for T in (1, 16, 512):
+        steps = 10 if T <= 16 else 3
+        sharded = measure_tp(T, 8, steps, 3, args.tp_collective, device, world, rank, shard=True)
+        single = measure_tp(T, 8, steps, 3, args.tp_collective, device, world, rank, shard=False)
+        sharded["speedup_over_one_gpu"] = sharded["tokens_per_s"] / single["tokens_per_s"]
+        out[f"batch{T}" if T <= 16 else f"prefill{T}"] = {"sharded": sharded, "one_gpu": single}
+    return out
+
+
+def tp_arm(args):
+    """`--mode tp`: the sharded step alone (strong scaling), one JSON line."""
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    T = args.batch
+    r = measure_tp(T, args.tp_layers, args.steps, args.warmup, args.tp_collective, device, world, rank)
     if rank == 0:
-        step_s = ms.item() * 1e-3 / args.steps * (TP_LAYERS / layers)
-        peaks = {}
-        try:
-            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-        except (OSError, ValueError):
-            pass
-        peak = float(peaks.get("hbm_gbs", 6650.0))
-        per_gpu = nbytes * (TP_LAYERS / layers) / step_s / 1e9
         print(json.dumps({
-            "mode": "tp", "metric": "decode tok/s (quantised linears of one decode step)", "value": T / step_s,
+            "mode": "tp", "metric": "decode tok/s (quantised linears of one decode step)", "value": r["tokens_per_s"],
             "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-            "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": ("bf16 tcgen05 mma / f32 accumulate; bf16 in/out" if use_gemm else "s8 mma / s32 accumulate; bf16 in/out"),
+            "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": ("bf16 tcgen05 mma / f32 accumulate; bf16 in/out" if r["kernel"].startswith("gemm")
+                      else "s8 mma / s32 accumulate; bf16 in/out"),
             "data": "synthetic",
             "config": {"workload": f"llama-3-70b-shaped decoder linears at {BPW} bpw, decode batch {T}, U split by output "
-                                   f"rows over {world} GPUs + one all-gather per launch group "
-                                   f"({'peer-memory kernel, CUDA graph' if peer is not None else 'NCCL, eager'})",
-                       "layers_timed": layers, "layers": TP_LAYERS, "parallelism": f"tp{world}"},
-            "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s per GPU", "frac": per_gpu / peak,
-                         "traffic": None},
-            "gpu_launches": launches_per_step * args.steps}), flush=True)
+                                   f"rows over {world} GPUs + one all-gather per launch group ({r['collective']})",
+                       "layers_timed": args.tp_layers, "layers": TP_LAYERS, "parallelism": f"tp{world}"},
+            "roofline": {"bound": "hbm", "achieved": r["per_gpu_gbs"], "peak": hbm_peak()[0], "unit": "GB/s per GPU",
+                         "frac": r["hbm_frac_per_gpu"], "traffic": None},
+            "gpu_launches": r["launches_per_step"] * args.steps}), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
@@ -694,16 +817,22 @@ def tp_arm(args):
 # --------------------------------------------------------------------------------------------
 # prefill arm (--mode prefill): Llama-2-7B-shaped layer GEMMs at 1.0 bpw, T tokens per GEMM
 # --------------------------------------------------------------------------------------------
-def measure_prefill(T, layers, steps, warmup, device, profile=False, min_seconds=0.0, e2e=False):
-    """TFLOP/s of nq_gemm_fwd on the 7 linears of `layers` Llama-2-7B-shaped layers (hidden 4096, intermediate
-    11008, ranks from the rank formula at 1.0 bpw), T tokens per GEMM.  Returns (TFLOP/s, ms per step, launches
-    per step, clock record or None)."""
+PREFILL_SHAPES = {   # name -> (hidden, intermediate, kv width, bits per weight)
+    "llama-2-7b": (4096, 11008, 4096, 1.0),
+    "qwen3-8b": (4096, 12288, 1024, 0.8),
+}
+
+
+def measure_prefill(T, layers, steps, warmup, device, profile=False, min_seconds=0.0, e2e=False, model="llama-2-7b"):
+    """TFLOP/s of nq_gemm_fwd on the 7 linears of `layers` decoder layers of `model`'s shape (ranks from the rank
+    formula at its bit budget), T tokens per GEMM.  Returns (TFLOP/s, ms per step, launches per step, clock record
+    or None, end-to-end record or None)."""
     import torch
     from nanoquant_b200 import _lib
     L = _lib.lib()
     dtype = torch.bfloat16
-    H, I = 4096, 11008
-    shapes = [(H, H)] * 4 + [(H, I), (H, I), (I, H)]
+    H, I, KVW, bpw = PREFILL_SHAPES[model]
+    shapes = [(H, H), (H, KVW), (H, KVW), (H, H), (H, I), (H, I), (I, H)]
     g = torch.Generator(device=device).manual_seed(0)
     rnd_bits = lambda rows, cols: torch.randint(-2**31, 2**31 - 1, ((rows + 15) // 16, (cols + 255) // 256, 128),
                                                 generator=g, device=device, dtype=torch.int32)
@@ -712,7 +841,7 @@ def measure_prefill(T, layers, steps, warmup, device, profile=False, min_seconds
     calls, flops, scratch_bytes = [], 0.0, 0
     for _ in range(layers):
         for (N, M) in shapes:
-            R = rank_for_bits(N, M, 1.0)
+            R = rank_for_bits(N, M, bpw)
             t = dict(v=rnd_bits(R, N), u=rnd_bits(M, R), a=scale(N), b=scale(R), c=scale(M),
                      y=torch.empty(T, M, device=device, dtype=dtype))
             calls.append((t, N, R, M))
@@ -786,16 +915,17 @@ def prefill_arm(args):
     torch.cuda.set_device(device)
     T = args.tokens
     layers = args.layers if args.layers != LAYERS else 4
+    model = args.prefill_model
     tf, ms, launches, clocks, e2e = measure_prefill(T, layers, args.steps, args.warmup, device, profile=True,
-                                                    min_seconds=1.0, e2e=True)
+                                                    min_seconds=1.0, e2e=True, model=model)
     peak, peak_src = tensor_peak()
     print(json.dumps({
         "mode": "prefill", "metric": "prefill TFLOP/s (quantised linears, 2*T*R*(N+M) flops)", "value": tf,
         "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 (fp32 accumulate)",
         "data": "synthetic",
-        "config": {"workload": f"llama-2-7b-shaped layer GEMMs at 1.0 bpw, {T} tokens per GEMM, {layers} layers",
-                   "tokens": T},
+        "config": {"workload": f"{model}-shaped layer GEMMs at {PREFILL_SHAPES[model][3]} bpw, {T} tokens per GEMM, "
+                               f"{layers} layers", "tokens": T},
         "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak,
                      "traffic": None, "kernel": "gemm_stage_kernel", "peak_source": peak_src},
         "e2e": e2e,
@@ -919,6 +1049,60 @@ def linear_arm(args):
         "gpu_launches": launches * copies * args.steps, "clocks": clocks}), flush=True)
 
 
+def pack_arm(args):
+    """`--mode pack`: the pack / layout kernels on a 12288 x 4096 matrix, GB/s of algorithmic bytes against the measured
+    HBM peak.  Inputs are rotated over enough separate matrices to exceed 2 x L2."""
+    import torch
+    from nanoquant_b200 import _lib
+    L = _lib.lib()
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(device)
+    rows, cols = 12288, 4096
+    st = torch.cuda.current_stream(device).cuda_stream
+    g = torch.Generator(device=device).manual_seed(0)
+    n_dense = max(2, int(2 * L2_BYTES // (rows * cols)) + 1)            # 1 byte per weight
+    n_packed = max(2, int(2 * L2_BYTES // (rows * cols // 8 * 2)) + 1)  # 1/8 byte per weight, read + written
+    dense = [(torch.randint(0, 2, (rows, cols), generator=g, device=device, dtype=torch.int8) * 2 - 1) for _ in range(n_dense)]
+    words = [torch.randint(-2**31, 2**31 - 1, (rows, cols // 32), generator=g, device=device, dtype=torch.int32)
+             for _ in range(n_packed)]
+    out_words = torch.empty(rows, cols // 32, dtype=torch.int32, device=device)
+    out_dense = torch.empty(rows, cols, dtype=torch.int8, device=device)
+    out_marlin = torch.empty(cols // 16, rows // 2, dtype=torch.int32, device=device)
+    out_tiles = torch.empty(L.nq_tiles_bytes(rows, cols), dtype=torch.uint8, device=device)
+    W = rows * cols
+    cases = [
+        ("nq_pack_rows", W + W / 8, n_dense, lambda i: L.nq_pack_rows(dense[i].data_ptr(), out_words.data_ptr(), rows, cols, _lib.NQ_HALF2, st)),
+        ("nq_unpack_rows", W / 8 + W, n_packed, lambda i: L.nq_unpack_rows(words[i].data_ptr(), out_dense.data_ptr(), rows, cols, _lib.NQ_LSB_FIRST, st)),
+        ("nq_pack_marlin", W + W / 8, n_dense, lambda i: L.nq_pack_marlin(dense[i].data_ptr(), out_marlin.data_ptr(), rows, cols, st)),
+        ("nq_rows_to_tiles", W / 8 + W / 8, n_packed, lambda i: L.nq_rows_to_tiles(words[i].data_ptr(), out_tiles.data_ptr(), rows, cols, _lib.NQ_LSB_FIRST, st)),
+        ("nq_reorder_words", W / 8 + W / 8, n_packed, lambda i: L.nq_reorder_words(words[i].data_ptr(), out_words.data_ptr(), rows * (cols // 32), _lib.NQ_LSB_FIRST, _lib.NQ_HALF2, st)),
+    ]
+    peak, peak_src = hbm_peak()
+    res = {}
+    for name, nbytes, n, fn in cases:
+        for i in range(n):
+            _lib.check(fn(i), name)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize(device)
+        e0.record()
+        for _ in range(args.steps):
+            for i in range(n):
+                fn(i)
+        e1.record()
+        torch.cuda.synchronize(device)
+        us = e0.elapsed_time(e1) * 1e3 / (args.steps * n)
+        res[name] = {"us": us, "GBps": nbytes / us / 1e3, "hbm_frac": nbytes / us / 1e3 / peak, "algorithmic_bytes": nbytes}
+    top = res["nq_rows_to_tiles"]
+    print(json.dumps({
+        "mode": "pack", "metric": "pack / layout kernels, GB/s of algorithmic bytes", "value": top["GBps"], "unit": "GB/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": 1, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "u8 / u32 bit operations", "data": "synthetic",
+        "config": {"workload": f"{rows} x {cols} +-1 matrix; {n_dense} dense / {n_packed} packed inputs in rotation (> 2 x L2)"},
+        "roofline": {"bound": "hbm", "achieved": top["GBps"], "peak": peak, "unit": "GB/s", "frac": top["hbm_frac"],
+                     "traffic": None, "kernel": "rows_to_tiles_kernel", "peak_source": peak_src},
+        "kernels": res, "gpu_launches": args.steps * (3 * n_packed + 2 * n_dense)}), flush=True)
+
+
 def head_arm(args):
     """`--mode head`: the dense GEMV of the un-quantised `lm_head` alone (`--vocab` rows, `--batch` tokens)."""
     import torch
@@ -953,9 +1137,10 @@ def main():
     ap.add_argument("--gemm-min-tokens", type=int, default=0,
                     help="decode batches of at least this many tokens run the group GEMM instead of the GEMV (0: library default)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-check", action="store_true", help="skip the output check of the launch structure against the oracle")
     ap.add_argument("--no-side-numbers", action="store_true",
                     help="skip the short batch-4 / batch-16 / prefill measurements added to the default line")
-    ap.add_argument("--mode", default="replica", choices=["replica", "tp", "prefill", "head", "linear"],
+    ap.add_argument("--mode", default="replica", choices=["replica", "tp", "prefill", "head", "linear", "pack"],
                     help="replica: the decode step (N > 1: independent replicas); tp: 70B-shaped TP decode step; "
                          "prefill: GEMM TFLOP/s on Llama-2-7B-shaped layers")
     ap.add_argument("--shape", default="config1", choices=sorted(GROUP_SHAPES), help="launch group of --mode linear")
@@ -963,6 +1148,8 @@ def main():
     ap.add_argument("--copies", type=int, default=0, help="--mode linear: cap on the weight sets (0: enough for 2 x L2)")
     ap.add_argument("--vocab", type=int, default=0, help="rows of the head in --mode head (0: the workload's vocabulary)")
     ap.add_argument("--tokens", type=int, default=2048, help="tokens per GEMM in --mode prefill")
+    ap.add_argument("--prefill-model", default="llama-2-7b", choices=sorted(PREFILL_SHAPES),
+                    help="layer shapes of --mode prefill")
     ap.add_argument("--layers", type=int, default=LAYERS, help="decoder layers resident (fewer only for profiling)")
     ap.add_argument("--tp-layers", type=int, default=TP_LAYERS, help="layers actually timed in --mode tp")
     ap.add_argument("--tp-collective", default="peer", choices=["peer", "nccl"],
@@ -983,6 +1170,8 @@ def main():
         head_arm(args)
     elif args.mode == "linear":
         linear_arm(args)
+    elif args.mode == "pack":
+        pack_arm(args)
     else:
         gpu_arm(args)
 

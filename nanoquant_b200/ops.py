@@ -20,7 +20,9 @@ Note the reference's argument naming: ``Ubits`` is the FIRST factor (module
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
+import threading
 from typing import Optional
 
 import torch
@@ -37,9 +39,9 @@ _SWEEP = {  # reference: cuda/gemv_kernel.cu:351-354
     "n_pipe": (1, 2, 4, 8, 16),
 }
 
-_scratch = {}   # (device index, stream) -> zero-initialised uint8 tensor
-_reserved = {}  # device index -> bytes every scratch of that device is allocated with
+_scratch = {}        # device index -> zero-initialised uint8 tensor
 _SCRATCH_MIN = 4 << 20
+_override = threading.local()   # .buf: a caller-provided scratch for this thread (see private_scratch)
 
 
 def _check_sweep(name: str, kind: str, value: int) -> None:
@@ -52,28 +54,44 @@ def _check_sweep(name: str, kind: str, value: int) -> None:
         raise ValueError(f"{name} should be one of [{', '.join(map(str, choices))}], but {value} was given")
 
 
-def reserve_scratch(device: torch.device, nbytes: int) -> None:
-    """Announce the scratch a layer on `device` will need (called when a layer is prepared), so that the
-    buffers of that device are allocated once, large enough for its largest layer, before any forward."""
+def reserve_scratch(device: torch.device, nbytes: int) -> torch.Tensor:
+    """Make sure the scratch of `device` holds `nbytes` (called when a layer is prepared, i.e. before any forward
+    and outside any stream capture or graph memory pool): the buffer is allocated once, for the device's largest
+    layer, and every later launch only reads its address."""
     idx = device.index if device.index is not None else torch.cuda.current_device()
-    _reserved[idx] = max(_reserved.get(idx, _SCRATCH_MIN), int(nbytes))
-
-
-def scratch_for(device: torch.device, nbytes: int) -> torch.Tensor:
-    """Per (device, stream) scratch of the kernels: zeroed once at allocation, as the C ABI asks.  Sized from
-    :func:`reserve_scratch`; growing it later is refused during a stream capture (a captured graph would keep
-    pointing at the buffer that the growth orphans, and the allocation itself would land inside the capture)."""
-    idx = device.index if device.index is not None else torch.cuda.current_device()
-    key = (idx, torch.cuda.current_stream(device).cuda_stream)
-    buf = _scratch.get(key)
+    buf = _scratch.get(idx)
     if buf is None or buf.numel() < nbytes:
         if torch.cuda.is_current_stream_capturing():
             raise RuntimeError("nanoquant_b200: the kernels' scratch buffer would have to be (re)allocated inside a "
-                               "stream capture; run the layer once before capturing, or call "
-                               "nanoquant_b200.ops.reserve_scratch() first")
-        buf = torch.zeros(max(nbytes, _reserved.get(idx, _SCRATCH_MIN)), dtype=torch.uint8, device=device)
-        _scratch[key] = buf
+                               "stream capture; prepare the layers (or call nanoquant_b200.ops.reserve_scratch) first")
+        buf = torch.zeros(max(int(nbytes), _SCRATCH_MIN), dtype=torch.uint8, device=torch.device("cuda", idx))
+        _scratch[idx] = buf
     return buf
+
+
+def scratch_for(device: torch.device, nbytes: int) -> torch.Tensor:
+    """The scratch the kernels of `device` run on: one buffer per device, zeroed once at allocation as the C ABI
+    asks.  Launches that share it must be ordered on one stream (what a model forward and its graph capture
+    are); code that runs layers on several streams at once gives each stream its own buffer with
+    :func:`private_scratch`."""
+    buf = getattr(_override, "buf", None)
+    if buf is not None:
+        if buf.numel() < nbytes:
+            raise RuntimeError(f"private scratch of {buf.numel()} bytes is too small: {nbytes} needed")
+        return buf
+    return reserve_scratch(device, nbytes)
+
+
+@contextlib.contextmanager
+def private_scratch(buf: torch.Tensor):
+    """Run the enclosed launches of this thread on `buf` (uint8, zeroed once by the caller, 16-byte aligned)
+    instead of the device's shared scratch: for concurrent streams."""
+    prev = getattr(_override, "buf", None)
+    _override.buf = buf
+    try:
+        yield buf
+    finally:
+        _override.buf = prev
 
 
 def _dtype_id(t: torch.Tensor) -> int:

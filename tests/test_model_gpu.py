@@ -189,10 +189,11 @@ def test_operators_under_torch_compile():
     x = torch.randn(1, m.H, generator=torch.Generator().manual_seed(2)).to(DT).cuda()
     with torch.no_grad():
         y_eager = m(x)
-        try:
-            fn = torch.compile(m, fullgraph=True, backend="cudagraphs")
-            y_c = fn(x)
-            y_c2 = fn(x)
-        except Exception as exc:   # no usable dynamo on this host
-            pytest.skip(f"torch.compile unavailable here: {type(exc).__name__}")
-    assert torch.equal(y_c, y_eager) and torch.equal(y_c2, y_eager)
+        # the reference's call (test_decode.py:396-402): inductor with CUDA graphs; the fake implementations of the
+        # operators make the module traceable as one graph, and nothing allocates inside the replayed region
+        fn = torch.compile(m, mode="reduce-overhead", fullgraph=True)
+        outs = [fn(x).clone() for _ in range(4)]        # warm-up, capture, replays
+        fn2 = torch.compile(m, fullgraph=True, backend="cudagraphs")
+        outs += [fn2(x).clone() for _ in range(3)]
+    for y in outs:
+        assert torch.equal(y, y_eager)
