@@ -88,6 +88,15 @@ __global__ void reorder_words_kernel(const uint32_t* __restrict__ in, uint32_t* 
          i += (int64_t)gridDim.x * blockDim.x)
         out[i] = convert_order(in[i], from, to);
 }
+// the same with 16-byte accesses (n4 groups of four words, both pointers 16-byte aligned)
+__global__ void reorder_words4_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, int64_t n4, int from, int to) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n4;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const uint4 v = __ldg(in + i);
+        out[i] = make_uint4(convert_order(v.x, from, to), convert_order(v.y, from, to), convert_order(v.z, from, to),
+                            convert_order(v.w, from, to));
+    }
+}
 
 // ---------------------------------------------------------------------------
 // marlin layout.  out = 64*to + 16*o16 + 8*o8 + o1, in = 16*tr + 8*r8 + 2*r2 + r1
@@ -117,6 +126,41 @@ __global__ void pack_marlin_kernel(const int8_t* __restrict__ w, uint32_t* __res
                 }
         B[i] = bits;
     }
+}
+
+// The same through shared memory: a CTA stages 64 output rows x 128 input columns with 16-byte row loads (a row
+// segment of 128 bytes is one coalesced request) and every thread assembles one word of the 8 x 32 words of the
+// tile from it.  The direct kernel above reads two single bytes per bit pair at a stride of in_f bytes.
+constexpr int kMarlinKT = 128;              // input columns per CTA
+constexpr int kMarlinPitch = kMarlinKT + 16;
+__global__ void __launch_bounds__(256) pack_marlin_staged_kernel(const int8_t* __restrict__ w, uint32_t* __restrict__ B,
+                                                                 int64_t out_f, int64_t in_f) {
+    __shared__ __align__(16) int8_t tile[64 * kMarlinPitch];
+    const int64_t to = blockIdx.x, k0 = (int64_t)blockIdx.y * kMarlinKT;
+    const int t = threadIdx.x;
+    for (int idx = t; idx < 64 * (kMarlinKT / 16); idx += 256) {
+        const int row = idx / (kMarlinKT / 16), seg = idx % (kMarlinKT / 16);
+        if (k0 + 16 * seg < in_f)      // in_f is a multiple of 16: a segment is inside the row or beyond it as a whole
+            *reinterpret_cast<uint4*>(tile + row * kMarlinPitch + 16 * seg) =
+                __ldg(reinterpret_cast<const uint4*>(w + (64 * to + row) * in_f + k0 + 16 * seg));
+    }
+    __syncthreads();
+    const int trl = t >> 5, colw = t & 31;
+    if (k0 + 16 * trl >= in_f) return;
+    const int o1 = colw >> 2, r2 = colw & 3;
+    uint32_t bits = 0;
+#pragma unroll
+    for (int o16 = 0; o16 < 4; ++o16)
+#pragma unroll
+        for (int o8 = 0; o8 < 2; ++o8)
+#pragma unroll
+            for (int r8 = 0; r8 < 2; ++r8) {
+                const int8_t* p = tile + (16 * o16 + 8 * o8 + o1) * kMarlinPitch + 16 * trl + 8 * r8 + 2 * r2;
+                const int pos = 15 - 4 * o16 - 2 * o8 - r8;
+                bits |= (uint32_t)(p[0] < 0) << pos;
+                bits |= (uint32_t)(p[1] < 0) << (pos + 16);
+            }
+    B[(k0 / 16 + trl) * (out_f / 2) + 32 * to + colw] = bits;
 }
 
 __global__ void marlin_to_rows_kernel(const uint32_t* __restrict__ B, uint32_t* __restrict__ packed,
@@ -272,8 +316,12 @@ int nq_reorder_words(const int32_t* in, int32_t* out, int64_t n_words, int order
     if (check_order(order_in) != NQ_OK || check_order(order_out) != NQ_OK) return NQ_ERR_DTYPE;
     if (n_words == 0) return NQ_OK;
     if (!in || !out) return NQ_ERR_NULL;
-    reorder_words_kernel<<<grid_for(n_words, kPackThreads), kPackThreads, 0, as_stream(stream)>>>(
-        reinterpret_cast<const uint32_t*>(in), reinterpret_cast<uint32_t*>(out), n_words, order_in, order_out);
+    if (n_words % 4 == 0 && aligned16(in) && aligned16(out))
+        reorder_words4_kernel<<<grid_for(n_words / 4, kPackThreads), kPackThreads, 0, as_stream(stream)>>>(
+            reinterpret_cast<const uint4*>(in), reinterpret_cast<uint4*>(out), n_words / 4, order_in, order_out);
+    else
+        reorder_words_kernel<<<grid_for(n_words, kPackThreads), kPackThreads, 0, as_stream(stream)>>>(
+            reinterpret_cast<const uint32_t*>(in), reinterpret_cast<uint32_t*>(out), n_words, order_in, order_out);
     NQ_LAUNCH_CHECK();
     return NQ_OK;
 }
@@ -282,8 +330,13 @@ int nq_pack_marlin(const int8_t* w, int32_t* B, int64_t out_f, int64_t in_f, nq_
     if (out_f < 0 || in_f < 0 || out_f % 64 || in_f % 16) return NQ_ERR_SHAPE;
     if (out_f == 0 || in_f == 0) return NQ_OK;
     if (!w || !B) return NQ_ERR_NULL;
-    pack_marlin_kernel<<<grid_for((in_f / 16) * (out_f / 2), kPackThreads), kPackThreads, 0, as_stream(stream)>>>(
-        w, reinterpret_cast<uint32_t*>(B), out_f, in_f);
+    const int64_t kblocks = (in_f + kMarlinKT - 1) / kMarlinKT;
+    if (aligned16(w) && out_f / 64 <= 0x7FFFFFFF && kblocks <= 65535)
+        pack_marlin_staged_kernel<<<dim3((unsigned)(out_f / 64), (unsigned)kblocks), 256, 0, as_stream(stream)>>>(
+            w, reinterpret_cast<uint32_t*>(B), out_f, in_f);
+    else
+        pack_marlin_kernel<<<grid_for((in_f / 16) * (out_f / 2), kPackThreads), kPackThreads, 0, as_stream(stream)>>>(
+            w, reinterpret_cast<uint32_t*>(B), out_f, in_f);
     NQ_LAUNCH_CHECK();
     return NQ_OK;
 }

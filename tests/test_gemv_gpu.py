@@ -7,7 +7,7 @@ import pytest
 import torch
 
 from oracle import nanoquant_oracle as oc
-from tests.util import TOL, exact_np, half2_bits, make_layer, np_to_torch
+from tests.util import parity_excess, TOL, exact_np, half2_bits, make_layer, np_to_torch
 
 pytestmark = pytest.mark.gpu
 
@@ -32,7 +32,7 @@ def test_golden_forward_fp64(op, golden_dir):
         y = op(np_to_torch(g[f"{name}_x"], torch.float16), np_to_torch(g[f"{name}_s_pre"], torch.float16),
                half2_bits(g[f"{name}_V"]), s_mid, half2_bits(g[f"{name}_U"]),
                np_to_torch(g[f"{name}_s_post"], torch.float16), **KW)
-        assert oc.rel_err(exact_np(y), g[f"{name}_y"]) <= TOL[torch.float16], name
+        assert parity_excess(exact_np(y), g[f"{name}_y"], torch.float16) <= 0, name
 
 
 SHAPES = [
@@ -54,13 +54,13 @@ def test_gemv_vs_oracle(op, shape, dtype):
     L = make_layer(N, R, M, T, dtype, seed=N + R + M + T)
     y = run(op, L)
     assert y.shape == (T, M) and y.dtype == dtype
-    assert oc.rel_err(exact_np(y), L["y64"]) <= TOL[dtype]
+    assert parity_excess(exact_np(y), L["y64"], dtype) <= 0
 
 
 @pytest.mark.parametrize("T", [5, 8, 16])
 def test_gemv_more_than_four_tokens(op, T):
     L = make_layer(1024, 320, 768, T, torch.float16, seed=T)
-    assert oc.rel_err(exact_np(run(op, L)), L["y64"]) <= TOL[torch.float16]
+    assert parity_excess(exact_np(run(op, L)), L["y64"], torch.float16) <= 0
 
 
 @pytest.mark.parametrize("T", [5, 9])
@@ -82,15 +82,25 @@ def test_c_abi_gemv_more_tokens_than_one_launch(T):
                               ut.data_ptr(), L["s_post"].data_ptr(), y.data_ptr(), scratch.data_ptr(), nbytes,
                               T, N, R, M, _lib.NQ_F16, st), "nq_gemv_fwd")
     assert Lb.nq_scratch_status(scratch.data_ptr(), st) == 0
-    assert oc.rel_err(exact_np(y), L["y64"]) <= TOL[torch.float16]
+    assert parity_excess(exact_np(y), L["y64"], torch.float16) <= 0
 
 
-@pytest.mark.parametrize("shape", [(8192, 5056, 3584, 2), (28672, 5056, 1024, 1)])
-def test_gemv_70b_shard_shapes(op, shape):
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(8192, 5056, 3584, 2), (28672, 5056, 1024, 1), (28672, 5056, 1024, 4)])
+def test_gemv_70b_shard_shapes(op, shape, dtype):
     # Llama-3-70B-shaped gate/up and down projections at 0.8 bpw with U split eight ways by output rows
     N, R, M, T = shape
-    L = make_layer(N, R, M, T, torch.float16, seed=N + M)
-    assert oc.rel_err(exact_np(run(op, L)), L["y64"]) <= TOL[torch.float16]
+    L = make_layer(N, R, M, T, dtype, seed=N + M)
+    assert parity_excess(exact_np(run(op, L)), L["y64"], dtype) <= 0
+
+
+@pytest.mark.parametrize("T", [1, 4])
+@pytest.mark.parametrize("shape", [(2048, 384, 512), (2048, 1600, 8192), (8192, 1600, 2048)])
+def test_gemv_llama_1b_shapes(op, shape, T):
+    # Llama-3.2-1B k/v, gate/up and down at 1.0 bpw in the type the decode workload runs in
+    N, R, M = shape
+    L = make_layer(N, R, M, T, torch.bfloat16, seed=N + R + T)
+    assert parity_excess(exact_np(run(op, L)), L["y64"], torch.bfloat16) <= 0
 
 
 def test_gemv_without_scale_mid_and_1d_input(op):
@@ -100,7 +110,7 @@ def test_gemv_without_scale_mid_and_1d_input(op):
     y1 = run(op, L1)
     assert y1.shape == (256,)
     assert torch.equal(y1, y2[0])
-    assert oc.rel_err(exact_np(y2), L["y64"]) <= TOL[torch.float16]
+    assert parity_excess(exact_np(y2), L["y64"], torch.float16) <= 0
 
 
 def test_gemv_is_deterministic_and_token_independent(op):

@@ -87,6 +87,8 @@ def test_reorder_words(ku):
     assert torch.equal(ku.reorder_packed(lsb, "lsb_first", "half2"), h2)
     assert torch.equal(ku.reorder_packed(h2, "half2", "lsb_first"), lsb)
     assert torch.equal(ku.reorder_packed(h2, "half2", "half2"), h2)
+    odd = lsb.reshape(-1)[:397].contiguous()          # a word count that is not a multiple of four: scalar kernel
+    assert torch.equal(ku.reorder_packed(odd[None], "lsb_first", "half2")[0], h2.reshape(-1)[:397])
 
 
 def test_pack_marlin_golden_and_oracle(ku, golden_dir):
@@ -110,6 +112,23 @@ def test_pack_marlin_golden_and_oracle(ku, golden_dir):
                                        torch.ones(4096, dtype=torch.float16, device="cuda"),
                                        torch.ones(1536, dtype=torch.float16, device="cuda"))
     assert np.array_equal(B.cpu().numpy(), oc.pack_marlin_bits(w))
+
+
+def test_pack_marlin_partial_blocks_and_unaligned_base(ku):
+    # in_f not a multiple of the 128 columns a CTA stages (partial last block), and a base pointer that is not
+    # 16-byte aligned (the byte-wise kernel takes over): both bit-exact with the oracle
+    from nanoquant_b200 import _lib
+    Lb = _lib.lib()
+    st = torch.cuda.current_stream().cuda_stream
+    for (o, i) in [(128, 208), (192, 16), (64, 400)]:
+        w = signs((o, i), o + i)
+        want = oc.pack_marlin_bits(w)
+        for offset in (0, 1):
+            buf = torch.zeros(o * i + 16, dtype=torch.int8, device="cuda")
+            buf[offset:offset + o * i] = torch.from_numpy(w).reshape(-1).cuda()
+            B = torch.empty(i // 16, o // 2, dtype=torch.int32, device="cuda")
+            _lib.check(Lb.nq_pack_marlin(buf.data_ptr() + offset, B.data_ptr(), o, i, st), "nq_pack_marlin")
+            assert np.array_equal(B.cpu().numpy(), want), (o, i, offset)
 
 
 def test_pack_marlin_fused_golden(ku, golden_dir):

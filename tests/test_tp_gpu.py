@@ -29,7 +29,7 @@ def _worker(rank, world, port, q):
     try:
         from nanoquant_b200 import ops, tp
         from nanoquant_b200.kernel import utils as ku
-        from tests.util import TOL, exact_np, half2_bits, make_layer
+        from tests.util import parity_excess, TOL, exact_np, half2_bits, make_layer
         out = []
         for (N, R, M, T) in ((1024, 288, 1024, 1), (2048, 512, 4096, 3), (1024, 256, 2048, 160)):
             L = make_layer(N, R, M, T, torch.bfloat16, seed=N + T, device=f"cuda:{rank}")
@@ -39,7 +39,7 @@ def _worker(rank, world, port, q):
             y = tp.tp_linear_forward(L["x"], shard)
             y1 = ops.linear_forward(L["x"], L["s_pre"], vt, L["s_mid"], ut, L["s_post"], R)
             torch.cuda.synchronize()
-            out.append((tuple(y.shape), bool(torch.equal(y, y1)), oc.rel_err(exact_np(y), L["y64"]) <= TOL[torch.bfloat16]))
+            out.append((tuple(y.shape), bool(torch.equal(y, y1)), parity_excess(exact_np(y), L["y64"], torch.bfloat16) <= 0))
         q.put((rank, out))
     finally:
         dist.destroy_process_group()

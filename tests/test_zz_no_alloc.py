@@ -10,7 +10,7 @@ import pytest
 import torch
 
 from oracle import nanoquant_oracle as oc
-from tests.util import TOL, exact_np, half2_bits, make_layer
+from tests.util import parity_excess, TOL, exact_np, half2_bits, make_layer
 
 pytestmark = pytest.mark.gpu
 
@@ -45,7 +45,7 @@ def test_static_scratch_entry_point_matches_regular_one(dtype):
         want = _run("regular", L, vt, ut, T, N, R, M, scratch)
         first = _run("static", L, vt, ut, T, N, R, M)
         second = _run("static", L, vt, ut, T, N, R, M)      # meets the first call's leftovers
-        assert oc.rel_err(exact_np(want), L["y64"]) <= TOL[dtype]
+        assert parity_excess(exact_np(want), L["y64"], dtype) <= 0
         # same kernel, exact integer accumulation: the results are identical, well inside the bar
         assert torch.equal(first, want) and torch.equal(second, want)
 

@@ -4,10 +4,11 @@ import torch
 
 from oracle import nanoquant_oracle as oc
 
-# Parity bar: max|y - y64| / max|y64| <= 2e-3 against the fp64 oracle.  A bf16
-# output cannot represent the result better than half a unit in the last place of
-# its 8-bit significand (2^-8 of the element), so for bf16 that representation
-# error is allowed on top; fp16 (2^-11) fits inside the bar.
+# Parity bar against the fp64 oracle, element by element:
+#     |y - y64| <= 2e-3 * max|y64| + half a unit in the last place of the output type at that element
+# (`parity_excess` / `assert_parity` below).  The representation error of a rounded output belongs to the
+# element (2^-9 of it for bf16, 2^-12 for fp16), not to the largest one, so a 2e-3 error before the final rounding
+# cannot hide behind it.  TOL is the older max-normalised bar, kept for comparisons between two rounded results.
 TOL = {torch.float16: 2e-3, torch.bfloat16: 2e-3 + 2.0 ** -8}
 
 
@@ -75,6 +76,12 @@ def elementwise_bound(y64, dtype, rel=2e-3, y=None):
         mag = np.maximum(mag, np.abs(np.asarray(y, np.float64)))
     half_ulp = 2.0 ** (np.floor(np.log2(mag)) - bits)
     return rel * np.max(np.abs(y64)) + half_ulp
+
+
+def parity_excess(y, y64, dtype, rel=2e-3):
+    """max over the elements of |y - y64| minus the element's bound; parity holds when this is <= 0."""
+    y = np.asarray(y, np.float64)
+    return float((np.abs(y - np.asarray(y64, np.float64)) - elementwise_bound(y64, dtype, rel, y)).max())
 
 
 def assert_parity(y, y64, dtype, rel=2e-3, what=""):
