@@ -1125,6 +1125,33 @@ def head_arm(args):
         "gpu_launches": args.steps, "clocks": clocks}), flush=True)
 
 
+def probe_arm(args):
+    """`--mode probe`: the library's measurement probes.  `chain_us` is the time per launch of a decode launch's
+    dependent chain with the arithmetic taken out (the floor of the launch structure) for several CTA counts;
+    `loop_gbs` is the rate of the GEMV's item loop fed from shared memory only, a cp.async ring, or registers."""
+    import ctypes
+    import torch
+    from nanoquant_b200 import _lib
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(device)
+    torch.zeros(1, device=device)   # primary context
+    L = _lib.lib()
+    sms = torch.cuda.get_device_properties(device).multi_processor_count
+    out = ctypes.c_float()
+    chain = {}
+    for ctas in sorted({sms, sms * 7 // 8, sms * 13 // 20, sms * 3 // 5, sms // 2, sms // 4}):
+        for rank in (1600, 2432):
+            _lib.check(L.nq_probe_chain(ctas, rank, 0, ctypes.byref(out)), "nq_probe_chain")
+            chain[f"{ctas} CTAs, rank {rank}"] = round(out.value, 3)
+    loop = {}
+    for mode, name in enumerate(("shared memory only", "cp.async ring", "registers")):
+        _lib.check(L.nq_probe_loop(mode, 256, ctypes.byref(out)), "nq_probe_loop")
+        loop[name] = round(out.value, 1)
+    peak, peak_src = hbm_peak()
+    print(json.dumps({"mode": "probe", "chain_us_per_launch": chain, "loop_gbs": loop, "hbm_peak_gbs": peak,
+                      "peak_source": peak_src, "n_gpus": 1}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -1140,7 +1167,7 @@ def main():
     ap.add_argument("--no-check", action="store_true", help="skip the output check of the launch structure against the oracle")
     ap.add_argument("--no-side-numbers", action="store_true",
                     help="skip the short batch-4 / batch-16 / prefill measurements added to the default line")
-    ap.add_argument("--mode", default="replica", choices=["replica", "tp", "prefill", "head", "linear", "pack"],
+    ap.add_argument("--mode", default="replica", choices=["replica", "tp", "prefill", "head", "linear", "pack", "probe"],
                     help="replica: the decode step (N > 1: independent replicas); tp: 70B-shaped TP decode step; "
                          "prefill: GEMM TFLOP/s on Llama-2-7B-shaped layers")
     ap.add_argument("--shape", default="config1", choices=sorted(GROUP_SHAPES), help="launch group of --mode linear")
@@ -1172,6 +1199,8 @@ def main():
         linear_arm(args)
     elif args.mode == "pack":
         pack_arm(args)
+    elif args.mode == "probe":
+        probe_arm(args)
     else:
         gpu_arm(args)
 

@@ -306,6 +306,22 @@ int nq_dense_gemv_max_tokens(void);
 int nq_dense_gemv_fwd(const void* x, const void* w, const void* bias, void* y, int T, int N, int V,
                       int64_t ldw, int64_t ldy, int dtype, nq_stream_t stream);
 
+/* ------------------------------------------------------------------------ *
+ * Measurement probes (no counterpart in the reference; nothing on the hot path calls them)
+ * ------------------------------------------------------------------------ */
+
+/* SYNCHRONOUS, allocate and free their own device memory, run on streams of their own: call them from a benchmark,
+ * not from serving code.
+ * nq_probe_chain: microseconds per launch of the dependent chain of a decode launch with the arithmetic taken out
+ * (dependency wait, broadcast load of an 8 KB input by every CTA, tagged hand-over of a rank-R vector between all
+ * CTAs, barriers, output store; 100 cooperative launches with programmatic stream serialization in a CUDA graph,
+ * replayed 10 times) for `ctas` CTAs; `pause_ns` > 0 sleeps that long before the first poll.
+ * nq_probe_loop: GB/s of packed factors through the GEMV's item loop fed from shared memory only (mode 0: the
+ * arithmetic ceiling), through a cp.async ring (mode 1) or through registers (mode 2); one CTA per SM,
+ * `items_per_warp` KB per warp (a multiple of 4, at most 1024). */
+int nq_probe_chain(int ctas, int R, int pause_ns, float* us_per_launch_host);
+int nq_probe_loop(int mode, int items_per_warp, float* gbs_host);
+
 #ifdef __cplusplus
 }
 #endif

@@ -69,6 +69,8 @@ SIGNATURES = {
     "nq_gemv_max_tokens": (c_int, []),
     "nq_linear_scratch_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "nq_linear_fwd": (c_int, [c_void_p] * 8 + [c_size_t, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "nq_probe_chain": (c_int, [c_int, c_int, c_int, ctypes.POINTER(ctypes.c_float)]),
+    "nq_probe_loop": (c_int, [c_int, c_int, ctypes.POINTER(ctypes.c_float)]),
 }
 
 _lib = None

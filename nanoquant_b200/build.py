@@ -17,7 +17,7 @@ CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libnanoquant_b200.so")
 INCLUDE = os.path.join(os.path.dirname(PKG_DIR), "include")
 
-SOURCES = ["nq_core.cu", "nq_pack.cu", "nq_gemv.cu", "nq_gemm.cu", "nq_comm.cu", "nq_dense.cu"]
+SOURCES = ["nq_core.cu", "nq_pack.cu", "nq_gemv.cu", "nq_gemm.cu", "nq_comm.cu", "nq_dense.cu", "nq_probe.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -651,7 +651,9 @@ constexpr size_t kMaxSlabBytes = (size_t)16 << 20;
 // The tile counters live in words 8..63 of the 256-byte scratch header, which no other kernel writes
 // (the decode kernel that may share the scratch uses words 0..2 and the bytes behind the header).
 constexpr int kCounterWord0 = 8, kMaxSplitTiles = 56;
-constexpr int kMaxSplitTokens = 64;   // beyond that the serial slab reduction of the last CTA costs more than the split saves
+// beyond 64 tokens the serial slab reduction of the last CTA costs more than the split saves
+// (128 tokens, Llama-2-7B shapes: 115 TFLOP/s with the split against 163 without)
+constexpr int kMaxSplitTokens = 64;
 
 // Tile shape (128*mh tokens x 128*nh weight rows) by a small cost model: a CTA needs a measured number of
 // cycles per 64-column step (bounded by the tensor pipe for the 256 x 256 tile, by the per-step waits and
