@@ -117,6 +117,13 @@ struct GemmParams {
     int T, t_pad;          // tokens; slab row length (tokens, multiple of 4)
     int is_bf16;
     int saturate;          // apply the reference's output saturation bounds
+    // Cluster split-K (more than 48 tokens, fewer output tiles than SMs): the `csplit` CTAs of a thread-block
+    // cluster along grid.z share an output tile, each over `chunks_per` 256-column chunks of every job.  After the
+    // main loops the accumulators are exchanged through distributed shared memory: 32-column blocks of the tile
+    // are dealt round-robin to the CTAs of the cluster, every CTA stores the blocks it does not own into the
+    // owner's (by then idle) pipeline buffers, and the owner adds the partial sums in rank order and runs the
+    // epilogue of its blocks.  1 = no cluster.
+    int csplit;
 };
 
 // ---------------------------------------------------------------------------
@@ -210,6 +217,23 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// Barrier of the thread-block cluster (every thread of every CTA of the cluster arrives): a hardware barrier
+// like __syncthreads(), with release/acquire ordering of the distributed-shared-memory stores before it.
+__device__ __forceinline__ void cluster_sync_all() {
+    __syncwarp();
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// address of this CTA's shared-memory location `local` in the CTA of rank `rank` of the cluster
+__device__ __forceinline__ uint32_t cluster_map(uint32_t local, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_store4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared::cluster.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
 // ---------------------------------------------------------------------------
 // the kernel: one 128 x 128 output tile per CTA
 // ---------------------------------------------------------------------------
@@ -230,7 +254,8 @@ __global__ void __launch_bounds__(GemmCfg<MH, NH>::kThreads) gemm_stage_kernel(c
     int ji = 0;
     while (ji + 1 < P.njobs && (int)blockIdx.x >= P.job[ji + 1].tile0) ++ji;
     const GemmJob& J = P.job[ji];
-    if ((int)blockIdx.z >= J.splits) return;   // grid.z is the largest split count of the launch
+    // grid.z is the largest split count of the launch; the CTAs of a cluster all stay (they meet at its barriers)
+    if (P.csplit == 1 && (int)blockIdx.z >= J.splits) return;
     const int tile = (int)blockIdx.x - J.tile0;
     const int n0 = tile * kBN;   // first weight row of the tile
     const int m0 = blockIdx.y * (kBM * MH);   // first token of the tile
@@ -299,6 +324,7 @@ __global__ void __launch_bounds__(GemmCfg<MH, NH>::kThreads) gemm_stage_kernel(c
     int nrg = J.row_groups - (n0 >> 4);          // row groups of this tile that exist
     nrg = nrg > kBN / 16 ? kBN / 16 : nrg;
 
+    bool expand_ok = true;   // expand warps: no wait of this thread has expired
     if (warp == 0) {
         // ------------------------------------------------------------ producer
         if (lane == 0) {
@@ -419,30 +445,89 @@ __global__ void __launch_bounds__(GemmCfg<MH, NH>::kThreads) gemm_stage_kernel(c
             // that a group without a block in a partial last chunk has nothing to release or to wait for)
             if (((kb + kGroups) >> 2) != c || kb + kGroups >= nkb) mbar_arrive(bar_bits_empty(b));
         }
-        // ------------------------------------------------------------ epilogue
-        if (ok) ok = mbar_wait(bar_accum, 0, abort_flag, P.status);
+        if (ok) ok = mbar_wait(bar_accum, 0, abort_flag, P.status);   // this CTA's MMAs are complete
+        expand_ok = ok;
+    }
+    // ---------------------------------------------------------------- epilogue (expand warps)
+    const bool is_expand = warp >= kFirstExpandWarp;
+    const int lq = warp & 3;                                   // tensor-memory lane quarter this warp may read
+    const int sub_w = (warp - kFirstExpandWarp) >> 2;          // index among the warps of that quarter
+    constexpr int kBlocks = MH * (kBN / 32);                   // 128-token x 32-column blocks of the tile
+    constexpr int kBlockBytes = 128 * 32 * 4;
+    // accumulator block `blk` of this CTA (both issuers' sums) into r; zeros if this CTA had no k block.
+    // Warp-collective: every lane of the warp takes part.
+    auto load_block = [&](int blk, uint32_t (&r)[32]) {
+        const int mh = blk / (kBN / 32), c0 = (blk % (kBN / 32)) * 32;
+        __syncwarp();
+        if (nkb <= 0) {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) r[e] = 0u;
+            return;
+        }
+        tmem_ld32(tmem_base + ((uint32_t)(32 * lq) << 16) + (uint32_t)(mh * kBN + c0), r);
+        if (C::kIssuers == 2 && nkb > 1) {   // the second issuer's accumulator
+            uint32_t r2[32];
+            tmem_ld32(tmem_base + ((uint32_t)(32 * lq) << 16) + (uint32_t)(MH * kBN + mh * kBN + c0), r2);
+#pragma unroll
+            for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) + __uint_as_float(r2[e]));
+        }
+    };
+    const int crank = P.csplit > 1 ? (int)blockIdx.z : 0;      // cluster dimensions are (1, 1, csplit)
+    const int max_owned = (kBlocks + P.csplit - 1) / P.csplit;
+    if (P.csplit > 1) {
+        // every CTA of the cluster has finished its main loop: the pipeline buffers (from kOffA) are free to
+        // receive the partial sums of the blocks this CTA owns, slot [source rank][block / csplit], each row of
+        // 128 bytes with its 16-byte pieces XOR-swizzled by the token (conflict-free stores and loads)
+        cluster_sync_all();
+        if (is_expand && expand_ok) {
+            tc_fence_after();
+            const int tok = 32 * lq + lane;
+#pragma unroll 1
+            for (int blk = sub_w; blk < kBlocks; blk += kExpandThreads / 128) {
+                const int owner = blk % P.csplit;
+                if (owner == crank) continue;
+                uint32_t r[32];
+                load_block(blk, r);
+                const uint32_t slot = sbase + kOffA + (uint32_t)((crank * max_owned + blk / P.csplit) * kBlockBytes + tok * 128);
+                const uint32_t dst = cluster_map(slot, (uint32_t)owner);
+#pragma unroll
+                for (int c = 0; c < 8; ++c)
+                    cluster_store4(dst + (uint32_t)((c ^ (tok & 7)) << 4), r[4 * c], r[4 * c + 1], r[4 * c + 2], r[4 * c + 3]);
+            }
+        }
+        cluster_sync_all();
+    }
+    if (is_expand) {
+        bool ok = expand_ok;
         // the output buffer may still be read by the kernel before the previous one (its input): the accumulator
         // is complete only after warp 0 passed its wait, but each thread has to order its own stores
         asm volatile("griddepcontrol.wait;" ::: "memory");
         // 32-column blocks of the MH accumulators, dealt round-robin to the warps that share a lane quarter
         if (ok) {
             tc_fence_after();
-            const int lq = warp & 3;                 // tensor-memory lane quarter this warp may read
-            const int sub_w = (warp - kFirstExpandWarp) >> 2;   // index among the warps of that quarter
             const float lim = P.saturate ? (P.is_bf16 ? 3.3895313892515355e+38f : 64504.0f) : 3.4e38f;
             const float4* post4 = reinterpret_cast<const float4*>(smem + kOffPost);
 #pragma unroll 1
-            for (int blk = sub_w; blk < MH * (kBN / 32); blk += kExpandThreads / 128) {
+            for (int blk = sub_w; blk < kBlocks; blk += kExpandThreads / 128) {
+                if (P.csplit > 1 && blk % P.csplit != crank) continue;   // another CTA of the cluster finishes this block
                 const int mh = blk / (kBN / 32), c0 = (blk % (kBN / 32)) * 32;
                 const int row = m0 + kBM * mh + 32 * lq + lane;     // token
-                __syncwarp();   // the tensor-memory loads are warp-collective: all lanes arrive here together
                 uint32_t r[32];
-                tmem_ld32(tmem_base + ((uint32_t)(32 * lq) << 16) + (uint32_t)(mh * kBN + c0), r);
-                if (C::kIssuers == 2 && nkb > 1) {   // the second issuer's accumulator
-                    uint32_t r2[32];
-                    tmem_ld32(tmem_base + ((uint32_t)(32 * lq) << 16) + (uint32_t)(MH * kBN + mh * kBN + c0), r2);
+                load_block(blk, r);
+                if (P.csplit > 1) {   // the other ranks' partial sums, in rank order
+                    const int tok = 32 * lq + lane;
+                    for (int rk = 0; rk < P.csplit; ++rk) {
+                        if (rk == crank) continue;
+                        const unsigned char* src = smem + kOffA + (size_t)(rk * max_owned + blk / P.csplit) * kBlockBytes + tok * 128;
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) + __uint_as_float(r2[e]));
+                        for (int c = 0; c < 8; ++c) {
+                            const float4 v = *reinterpret_cast<const float4*>(src + ((c ^ (tok & 7)) << 4));
+                            r[4 * c] = __float_as_uint(__uint_as_float(r[4 * c]) + v.x);
+                            r[4 * c + 1] = __float_as_uint(__uint_as_float(r[4 * c + 1]) + v.y);
+                            r[4 * c + 2] = __float_as_uint(__uint_as_float(r[4 * c + 2]) + v.z);
+                            r[4 * c + 3] = __float_as_uint(__uint_as_float(r[4 * c + 3]) + v.w);
+                        }
+                    }
                 }
                 // The tensor-memory loads above are warp-collective: every lane takes part in every round, and a
                 // lane without a valid output only skips the stores.
@@ -640,6 +725,7 @@ struct GroupPlan {
     int t_pad;                        // slab row length (tokens, multiple of 4)
     int tiles_total;                  // grid.x
     int max_splits;                   // grid.z
+    int csplit;                       // CTAs per cluster along grid.z that share an output tile (1: no cluster)
     int tile0[kMaxGemmJobs];          // first grid.x index of each job
     int splits[kMaxGemmJobs];         // CTAs per output tile along K (1 = no split)
     int chunks_per[kMaxGemmJobs];     // 256-column chunks per split
@@ -651,34 +737,116 @@ constexpr size_t kMaxSlabBytes = (size_t)16 << 20;
 // The tile counters live in words 8..63 of the 256-byte scratch header, which no other kernel writes
 // (the decode kernel that may share the scratch uses words 0..2 and the bytes behind the header).
 constexpr int kCounterWord0 = 8, kMaxSplitTiles = 56;
-// beyond 64 tokens the serial slab reduction of the last CTA costs more than the split saves
-// (128 tokens, Llama-2-7B shapes: 115 TFLOP/s with the split against 163 without)
-constexpr int kMaxSplitTokens = 64;
+// Up to 48 tokens the k split goes over independent CTAs with slabs in global memory (any number of splits, as
+// many as there are idle SMs); beyond, the serial slab reduction of the last CTA costs more than the split saves
+// and the split goes over the CTAs of a cluster instead.  Qwen3-8B decode step, slabs against clusters: 32 tokens
+// 3.84 against 4.50 ms, 64 tokens 4.89 against 4.54 ms.
+constexpr int kMaxSplitTokens = 48;
+
+// The four tile configurations as the host sees them.
+struct KernelInfo {
+    const void* fn;
+    size_t smem;
+    int threads;
+    int pipe_bytes;   // pipeline buffers (activation + weight stages): receive space of a cluster split
+    int blocks;       // 128-token x 32-column accumulator blocks of a tile
+};
+template <int MH, int NH>
+static KernelInfo kernel_info_of() {
+    using C = GemmCfg<MH, NH>;
+    return {(const void*)gemm_stage_kernel<MH, NH>, (size_t)C::kSmemBytes, C::kThreads, C::kStages * (C::kABytes + C::kWBytes),
+            MH * (C::kBN / 32)};
+}
+static KernelInfo kernel_info(int mh, int nh) {
+    if (mh == 1 && nh == 1) return kernel_info_of<1, 1>();
+    if (mh == 1) return kernel_info_of<1, 2>();
+    if (nh == 1) return kernel_info_of<2, 1>();
+    return kernel_info_of<2, 2>();
+}
+
+static int set_kernel_attributes() {
+    static bool attr_set[64];
+    int dev = 0;
+    NQ_CUDA_TRY(cudaGetDevice(&dev));
+    if (!attr_set[dev & 63]) {
+        for (int mh = 1; mh <= 2; ++mh)
+            for (int nh = 1; nh <= 2; ++nh) {
+                const KernelInfo ki = kernel_info(mh, nh);
+                NQ_CUDA_TRY(cudaFuncSetAttribute(ki.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ki.smem));
+            }
+        attr_set[dev & 63] = true;
+    }
+    return NQ_OK;
+}
+
+// CTAs of configuration (mh, nh) that can be resident at once when they are launched as clusters of `s`
+// (clusters are placed inside one GPC, so this is less than the SM count for most sizes).
+static int cluster_capacity(int mh, int nh, int s) {
+    static int cached[2][2][9];
+    int& c = cached[mh - 1][nh - 1][s];
+    if (c == 0) {
+        const KernelInfo ki = kernel_info(mh, nh);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(1, 1, s);
+        cfg.blockDim = dim3(ki.threads);
+        cfg.dynamicSmemBytes = ki.smem;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 1; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = (unsigned)s;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        int clusters = 0;
+        if (set_kernel_attributes() != NQ_OK || cudaOccupancyMaxActiveClusters(&clusters, ki.fn, &cfg) != cudaSuccess ||
+            clusters <= 0) {
+            (void)cudaGetLastError();
+            clusters = sm_count() * 7 / 8 / s;   // a guess on the safe side
+        }
+        c = clusters * s;
+    }
+    return c;
+}
 
 // Tile shape (128*mh tokens x 128*nh weight rows) by a small cost model: a CTA needs a measured number of
-// cycles per 64-column step (bounded by the tensor pipe for the 256 x 256 tile, by the per-step waits and
-// MMA issue of the issuing threads for the smaller ones); the grid runs in ceil(tiles/SMs) waves, each
-// with a fixed prologue/epilogue cost.  With at most 64 tokens and few output tiles the k dimension of every
-// job is split over the idle SMs (whole 256-column chunks per CTA), as far as counters and slab budget allow.
-static GroupPlan plan_group(int T, int n, const int* K, const int* Nout, bool allow_split) {
+// cycles per 64-column step (bounded by the tensor pipe for the 256 x 256 tile, by shared-memory traffic and the
+// per-step waits of the issuing threads for the smaller ones); the grid runs in ceil(CTAs/resident CTAs) waves, each
+// with a fixed prologue/epilogue cost.  Launches that would leave SMs idle split the k dimension of every job
+// (whole 256-column chunks per CTA): above 48 tokens over the CTAs of a cluster, which add their partial sums
+// through distributed shared memory; up to 48 tokens over independent CTAs with fp32 slabs in global memory, as
+// far as counters and slab budget allow.
+static GroupPlan plan_group(int T, int n, const int* K, const int* Nout, bool allow_split, bool allow_cluster) {
     GroupPlan pl;
     memset(&pl, 0, sizeof(pl));
-    pl.mh = 1; pl.nh = 1;
+    pl.mh = 1; pl.nh = 1; pl.csplit = 1;
     static const int cand[4][2] = {{1, 1}, {2, 1}, {1, 2}, {2, 2}};
     const long long sms = sm_count();
-    long long steps = 0;
-    for (int j = 0; j < n; ++j) steps = steps > (K[j] + kBK - 1) / kBK ? steps : (K[j] + kBK - 1) / kBK;
+    int min_chunks = 1 << 30, max_chunks = 0;
+    for (int j = 0; j < n; ++j) {
+        const int c = (K[j] + 255) / 256;
+        min_chunks = c < min_chunks ? c : min_chunks;
+        max_chunks = c > max_chunks ? c : max_chunks;
+    }
+    const bool cluster_ok = allow_cluster && T > kMaxSplitTokens;
     long long best = -1;
     for (const auto& c : cand) {
         if (c[0] == 2 && T <= kBM) continue;
         long long tiles = 0;
         for (int j = 0; j < n; ++j)
             tiles += (long long)((T + kBM * c[0] - 1) / (kBM * c[0])) * ((Nout[j] + 128 * c[1] - 1) / (128 * c[1]));
-        const long long waves = (tiles + sms - 1) / sms;
         // measured cycles of the MMA thread per 64-column step (wait + issue, tensor pipe busy)
         const long long per_step = c[0] * c[1] == 4 ? 990 : (c[0] == 2 ? 580 : (c[1] == 2 ? 830 : 485));
-        const long long cost = waves * (steps * per_step + 6000 + 2000LL * c[0] * c[1]);
-        if (best < 0 || cost < best) { best = cost; pl.mh = c[0]; pl.nh = c[1]; }
+        const long long fixed = 6000 + 2000LL * c[0] * c[1];
+        const KernelInfo ki = kernel_info(c[0], c[1]);
+        for (int s = 1; s <= (cluster_ok && c[0] * c[1] < 4 ? 8 : 1); ++s) {
+            if (s > 1) {
+                if (s > min_chunks) break;
+                if ((long long)s * ((ki.blocks + s - 1) / s) * (128 * 32 * 4) > ki.pipe_bytes) continue;
+            }
+            const long long resident = s == 1 ? sms : cluster_capacity(c[0], c[1], s);
+            const long long waves = (tiles * s + resident - 1) / resident;
+            const long long steps = 4LL * ((max_chunks + s - 1) / s);
+            const long long cost = waves * (steps * per_step + fixed + (s > 1 ? 2500 + 300LL * s : 0));
+            if (best < 0 || cost < best) { best = cost; pl.mh = c[0]; pl.nh = c[1]; pl.csplit = s; }
+        }
     }
     pl.t_pad = (T + 3) / 4 * 4;
     pl.max_splits = 1;
@@ -689,6 +857,10 @@ static GroupPlan plan_group(int T, int n, const int* K, const int* Nout, bool al
         pl.tiles_total += tiles_n[j];
         pl.splits[j] = 1;
         pl.chunks_per[j] = (K[j] + 255) / 256;
+    }
+    if (pl.csplit > 1) {
+        pl.max_splits = pl.csplit;
+        for (int j = 0; j < n; ++j) pl.chunks_per[j] = ((K[j] + 255) / 256 + pl.csplit - 1) / pl.csplit;
     }
     if (allow_split && T <= kMaxSplitTokens) {
         long long want_all = sms / pl.tiles_total;   // CTAs per tile that the idle SMs allow
@@ -728,7 +900,8 @@ static int launch_stage(const StageJob* jobs, int n, int T, int dtype, int satur
         if (S.pre && !aligned16(S.pre)) return NQ_ERR_ALIGN;
         Ks[j] = S.K; Ns[j] = S.Nout;
     }
-    const GroupPlan pl = plan_group(T, n, Ks, Ns, counters != nullptr && slabs != nullptr);
+    { const int st_attr = set_kernel_attributes(); if (st_attr != NQ_OK) return st_attr; }
+    const GroupPlan pl = plan_group(T, n, Ks, Ns, counters != nullptr && slabs != nullptr, true);
     const int mh = pl.mh, nh = pl.nh;
     const int m_tiles = (T + kBM * mh - 1) / (kBM * mh);
     GemmParams P;
@@ -739,6 +912,7 @@ static int launch_stage(const StageJob* jobs, int n, int T, int dtype, int satur
     P.t_pad = pl.t_pad;
     P.is_bf16 = dtype == NQ_BF16;
     P.saturate = saturate;
+    P.csplit = pl.csplit;
     for (int j = 0; j < n; ++j) {
         const StageJob& S = jobs[j];
         GemmJob& J = P.job[j];
@@ -768,27 +942,10 @@ static int launch_stage(const StageJob* jobs, int n, int T, int dtype, int satur
         J.counters = counters ? counters + pl.counter0[j] : nullptr;
         J.slabs = slabs ? slabs + pl.slab0[j] : nullptr;
     }
-    static bool attr_set[64];
-    int dev = 0;
-    NQ_CUDA_TRY(cudaGetDevice(&dev));
-    if (!attr_set[dev & 63]) {
-        NQ_CUDA_TRY(cudaFuncSetAttribute(gemm_stage_kernel<1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         GemmCfg<1, 1>::kSmemBytes));
-        NQ_CUDA_TRY(cudaFuncSetAttribute(gemm_stage_kernel<2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         GemmCfg<2, 1>::kSmemBytes));
-        NQ_CUDA_TRY(cudaFuncSetAttribute(gemm_stage_kernel<1, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         GemmCfg<1, 2>::kSmemBytes));
-        NQ_CUDA_TRY(cudaFuncSetAttribute(gemm_stage_kernel<2, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         GemmCfg<2, 2>::kSmemBytes));
-        attr_set[dev & 63] = true;
-    }
-    const void* fn;
-    size_t smem_bytes;
-    int threads;
-    if (mh == 1 && nh == 1) { fn = (const void*)gemm_stage_kernel<1, 1>; smem_bytes = GemmCfg<1, 1>::kSmemBytes; threads = GemmCfg<1, 1>::kThreads; }
-    else if (mh == 1) { fn = (const void*)gemm_stage_kernel<1, 2>; smem_bytes = GemmCfg<1, 2>::kSmemBytes; threads = GemmCfg<1, 2>::kThreads; }
-    else if (nh == 1) { fn = (const void*)gemm_stage_kernel<2, 1>; smem_bytes = GemmCfg<2, 1>::kSmemBytes; threads = GemmCfg<2, 1>::kThreads; }
-    else { fn = (const void*)gemm_stage_kernel<2, 2>; smem_bytes = GemmCfg<2, 2>::kSmemBytes; threads = GemmCfg<2, 2>::kThreads; }
+    const KernelInfo ki = kernel_info(mh, nh);
+    const void* fn = ki.fn;
+    const size_t smem_bytes = ki.smem;
+    const int threads = ki.threads;
     // Programmatic stream serialization lets this grid start while the previous kernel of the stream drains
     // (see the kernel's griddepcontrol instructions).  If the driver refuses the attribute once, plain
     // launches are used from then on.
@@ -798,17 +955,23 @@ static int launch_stage(const StageJob* jobs, int n, int T, int dtype, int satur
     cfg.blockDim = dim3(threads);
     cfg.dynamicSmemBytes = smem_bytes;
     cfg.stream = stream;
-    cudaLaunchAttribute attr;
-    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr.val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = &attr;
-    cfg.numAttrs = pdl_ok ? 1 : 0;
+    cudaLaunchAttribute attrs[2];
+    int na = 0;
+    if (pl.csplit > 1) {
+        attrs[na].id = cudaLaunchAttributeClusterDimension;
+        attrs[na].val.clusterDim.x = 1; attrs[na].val.clusterDim.y = 1; attrs[na].val.clusterDim.z = (unsigned)pl.csplit;
+        ++na;
+    }
+    attrs[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[na].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attrs;
+    cfg.numAttrs = pdl_ok ? na + 1 : na;
     void* args[] = {&P};
     cudaError_t e = cudaLaunchKernelExC(&cfg, fn, args);
     if (e != cudaSuccess && pdl_ok) {
         (void)cudaGetLastError();
         pdl_ok = false;
-        cfg.numAttrs = 0;
+        cfg.numAttrs = na;
         e = cudaLaunchKernelExC(&cfg, fn, args);
     }
     NQ_CUDA_TRY(e);
@@ -832,7 +995,7 @@ static size_t gemm_group_layout(const nq_linear_desc* d, int n, int T, size_t* t
         K1[j] = d[j].N; N1[j] = d[j].R; K2[j] = d[j].R; N2[j] = d[j].M;
     }
     if (slab_off) *slab_off = off;
-    const size_t a = plan_group(T, n, K1, N1, true).slab_floats, b = plan_group(T, n, K2, N2, true).slab_floats;
+    const size_t a = plan_group(T, n, K1, N1, true, false).slab_floats, b = plan_group(T, n, K2, N2, true, false).slab_floats;
     return off + (a > b ? a : b) * sizeof(float);
 }
 

@@ -220,6 +220,43 @@ def test_c_abi_gemm_group_matches_single_linears(T):
         col += m
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("T", [49, 100, 128, 200, 300])
+def test_c_abi_gemm_cluster_split(T, dtype):
+    # Few output tiles above 48 tokens: the k dimension is split over the CTAs of a thread-block cluster, which add
+    # their partial sums through distributed shared memory.  Two linears with different ranks in one launch, so the
+    # chunks per CTA differ per job and the last CTA of a cluster has no chunk of the smaller job (it contributes
+    # zeros); ragged token counts; the result must not change from run to run (fixed summation order).
+    from nanoquant_b200 import _lib
+    from tests.util import make_group, tiles_on_gpu, assert_parity
+    Lb = _lib.lib()
+    code = _lib.NQ_BF16 if dtype == torch.bfloat16 else _lib.NQ_F16
+    shapes = [(1024, 1288, 256), (1024, 2048, 200)]
+    layers = make_group(shapes, T, dtype, seed=300 + T)
+    width = 512
+    ybuf = torch.zeros(T, width, dtype=dtype, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    keep, descs = [], []
+    for i, (L, (n, r, m)) in enumerate(zip(layers, shapes)):
+        vt, ut = tiles_on_gpu(L["V"]), tiles_on_gpu(L["U"])
+        keep += [vt, ut]
+        descs.append(_lib.LinearDesc(L["x"].data_ptr(), L["s_pre"].data_ptr(), vt.data_ptr(), L["s_mid"].data_ptr(), ut.data_ptr(),
+                                     L["s_post"].data_ptr(), ybuf.data_ptr() + 2 * 256 * i, n, r, m, n, width))
+    arr = (_lib.LinearDesc * len(descs))(*descs)
+    nbytes = Lb.nq_gemm_group_scratch_bytes(arr, len(descs), T)
+    scratch = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+    outs = []
+    for _ in range(3):
+        ybuf.fill_(7.0)
+        _lib.check(Lb.nq_gemm_group_fwd(arr, len(descs), T, code, scratch.data_ptr(), nbytes, st), "group")
+        outs.append(ybuf.clone())
+    assert Lb.nq_scratch_status(scratch.data_ptr(), st) == 0
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    for i, (L, (n, r, m)) in enumerate(zip(layers, shapes)):
+        assert_parity(exact_np(ybuf[:, 256 * i:256 * i + m]), L["y64"], dtype)
+    assert torch.all(ybuf[:, 256 + 200:] == 7.0)   # columns beyond the second linear's width are untouched
+
+
 def test_gemm_linearity_full_size(ops):
     # size-independent property at a full-size shape: the op is linear in x.  Doubling x doubles every
     # fp32 partial sum exactly; only intermediate values that fall into the fp16 subnormal range may
