@@ -216,7 +216,7 @@ unsigned nq_gemv_set_wait_limit(unsigned polls);
 /* Bytes of scratch nq_gemm_fwd needs: a 256-byte header (status word at byte 8,
  * the same place as in the GEMV scratch; tile counters of the split-K path in
  * bytes 32..255) followed by the rank-R intermediate t[T, R] in the I/O dtype
- * and, for up to 48 tokens, the fp32 partial sums of the k splits (above that
+ * and, for up to 24 tokens, the fp32 partial sums of the k splits (above that
  * a k split runs over the CTAs of a thread-block cluster and needs no scratch). */
 size_t nq_gemm_scratch_bytes(int T, int N, int R, int M);
 

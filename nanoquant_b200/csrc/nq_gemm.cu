@@ -117,7 +117,7 @@ struct GemmParams {
     int T, t_pad;          // tokens; slab row length (tokens, multiple of 4)
     int is_bf16;
     int saturate;          // apply the reference's output saturation bounds
-    // Cluster split-K (more than 48 tokens, fewer output tiles than SMs): the `csplit` CTAs of a thread-block
+    // Cluster split-K (more than 24 tokens, fewer output tiles than SMs): the `csplit` CTAs of a thread-block
     // cluster along grid.z share an output tile, each over `chunks_per` 256-column chunks of every job.  After the
     // main loops the accumulators are exchanged through distributed shared memory: 32-column blocks of the tile
     // are dealt round-robin to the CTAs of the cluster, every CTA stores the blocks it does not own into the
@@ -283,6 +283,8 @@ __global__ void __launch_bounds__(GemmCfg<MH, NH>::kThreads) gemm_stage_kernel(c
     // may still use only behind griddepcontrol.wait: the activation loads (warp 0) and the output stores.
     // Weights and scales are constants of the layer.  Both instructions are no-ops without the launch attribute.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (threadIdx.x == 32)   // the activation tile's descriptor on its way while the barriers are set up
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&J.map_a)) : "memory");
     if (threadIdx.x == 0) {
         for (int s = 0; s < kGemmStages; ++s) {
             mbar_init(bar_ready(s), 1 + kGroupThreads);
@@ -299,17 +301,15 @@ __global__ void __launch_bounds__(GemmCfg<MH, NH>::kThreads) gemm_stage_kernel(c
     // input-scale slots start finite: a partial last k block leaves older (finite) values behind
     for (int i = threadIdx.x; i < kBitsSlots * kPreBytes / 4; i += kGemmThreads)
         reinterpret_cast<uint32_t*>(smem + kOffPre)[i] = 0;
-    for (int i = threadIdx.x; i < kBN; i += kGemmThreads) {   // output scales of this tile, once, as fp32
-        float f = 1.f;
-        if (J.post && n0 + i < J.Nout)
-            f = P.is_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(J.post)[n0 + i])
-                          : __half2float(static_cast<const __half*>(J.post)[n0 + i]);
-        reinterpret_cast<float*>(smem + kOffPost)[i] = f;
-        float bv = 0.f;
-        if (J.bias && n0 + i < J.Nout)
-            bv = P.is_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(J.bias)[n0 + i])
-                           : __half2float(static_cast<const __half*>(J.bias)[n0 + i]);
-        reinterpret_cast<float*>(smem + kOffBias)[i] = bv;
+    // Output scales and bias of this tile: expand thread i loads those of column i now (the values are needed
+    // only in the epilogue, and nothing here waits for them) and puts them into shared memory behind its main loop.
+    uint32_t raw_post = 0, raw_bias = 0;
+    {
+        const int i = (int)threadIdx.x - 32 * kFirstExpandWarp;
+        if (i >= 0 && i < kBN && n0 + i < J.Nout) {
+            if (J.post) raw_post = 0x10000u | static_cast<const uint16_t*>(J.post)[n0 + i];
+            if (J.bias) raw_bias = 0x10000u | static_cast<const uint16_t*>(J.bias)[n0 + i];
+        }
     }
     if (warp == 1) {  // tensor-memory allocation: 128 fp32 columns per accumulator, by one whole warp
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
@@ -445,6 +445,15 @@ __global__ void __launch_bounds__(GemmCfg<MH, NH>::kThreads) gemm_stage_kernel(c
             // that a group without a block in a partial last chunk has nothing to release or to wait for)
             if (((kb + kGroups) >> 2) != c || kb + kGroups >= nkb) mbar_arrive(bar_bits_empty(b));
         }
+        if (tu < kBN) {
+            auto as_float = [&](uint32_t raw, float dflt) {
+                if (!(raw & 0x10000u)) return dflt;
+                return P.is_bf16 ? __uint_as_float(raw << 16) : __half2float(__ushort_as_half((unsigned short)raw));
+            };
+            reinterpret_cast<float*>(smem + kOffPost)[tu] = as_float(raw_post, 1.f);
+            reinterpret_cast<float*>(smem + kOffBias)[tu] = as_float(raw_bias, 0.f);
+        }
+        asm volatile("bar.sync 2, %0;" ::"n"(kExpandThreads) : "memory");   // scales visible to every expand thread
         if (ok) ok = mbar_wait(bar_accum, 0, abort_flag, P.status);   // this CTA's MMAs are complete
         expand_ok = ok;
     }
@@ -476,23 +485,24 @@ __global__ void __launch_bounds__(GemmCfg<MH, NH>::kThreads) gemm_stage_kernel(c
     const int max_owned = (kBlocks + P.csplit - 1) / P.csplit;
     if (P.csplit > 1) {
         // every CTA of the cluster has finished its main loop: the pipeline buffers (from kOffA) are free to
-        // receive the partial sums of the blocks this CTA owns, slot [source rank][block / csplit], each row of
-        // 128 bytes with its 16-byte pieces XOR-swizzled by the token (conflict-free stores and loads)
+        // receive the partial sums of the blocks this CTA owns, slot [source rank][block / csplit]; inside a slot
+        // [lane quarter][16-byte piece of the 32 columns][lane], so that a warp's store covers 512 contiguous bytes
+        // (stores that scatter over 32 rows took 5 us per exchange: the cluster network moves whole lines)
         cluster_sync_all();
         if (is_expand && expand_ok) {
             tc_fence_after();
-            const int tok = 32 * lq + lane;
 #pragma unroll 1
             for (int blk = sub_w; blk < kBlocks; blk += kExpandThreads / 128) {
                 const int owner = blk % P.csplit;
                 if (owner == crank) continue;
+                if (m0 + kBM * (blk / (kBN / 32)) + 32 * lq >= P.T) continue;   // none of this warp's 32 tokens exists
                 uint32_t r[32];
                 load_block(blk, r);
-                const uint32_t slot = sbase + kOffA + (uint32_t)((crank * max_owned + blk / P.csplit) * kBlockBytes + tok * 128);
+                const uint32_t slot = sbase + kOffA + (uint32_t)((crank * max_owned + blk / P.csplit) * kBlockBytes + lq * 4096 + lane * 16);
                 const uint32_t dst = cluster_map(slot, (uint32_t)owner);
 #pragma unroll
-                for (int c = 0; c < 8; ++c)
-                    cluster_store4(dst + (uint32_t)((c ^ (tok & 7)) << 4), r[4 * c], r[4 * c + 1], r[4 * c + 2], r[4 * c + 3]);
+                for (int c = 0; c < 8; ++c)   // a warp stores 512 contiguous bytes per instruction
+                    cluster_store4(dst + (uint32_t)(c * 512), r[4 * c], r[4 * c + 1], r[4 * c + 2], r[4 * c + 3]);
             }
         }
         cluster_sync_all();
@@ -512,16 +522,16 @@ __global__ void __launch_bounds__(GemmCfg<MH, NH>::kThreads) gemm_stage_kernel(c
                 if (P.csplit > 1 && blk % P.csplit != crank) continue;   // another CTA of the cluster finishes this block
                 const int mh = blk / (kBN / 32), c0 = (blk % (kBN / 32)) * 32;
                 const int row = m0 + kBM * mh + 32 * lq + lane;     // token
+                if (row - lane >= P.T) continue;                     // none of this warp's 32 tokens exists
                 uint32_t r[32];
                 load_block(blk, r);
                 if (P.csplit > 1) {   // the other ranks' partial sums, in rank order
-                    const int tok = 32 * lq + lane;
                     for (int rk = 0; rk < P.csplit; ++rk) {
                         if (rk == crank) continue;
-                        const unsigned char* src = smem + kOffA + (size_t)(rk * max_owned + blk / P.csplit) * kBlockBytes + tok * 128;
+                        const unsigned char* src = smem + kOffA + (size_t)(rk * max_owned + blk / P.csplit) * kBlockBytes + lq * 4096 + lane * 16;
 #pragma unroll
                         for (int c = 0; c < 8; ++c) {
-                            const float4 v = *reinterpret_cast<const float4*>(src + ((c ^ (tok & 7)) << 4));
+                            const float4 v = *reinterpret_cast<const float4*>(src + c * 512);
                             r[4 * c] = __float_as_uint(__uint_as_float(r[4 * c]) + v.x);
                             r[4 * c + 1] = __float_as_uint(__uint_as_float(r[4 * c + 1]) + v.y);
                             r[4 * c + 2] = __float_as_uint(__uint_as_float(r[4 * c + 2]) + v.z);
@@ -737,11 +747,11 @@ constexpr size_t kMaxSlabBytes = (size_t)16 << 20;
 // The tile counters live in words 8..63 of the 256-byte scratch header, which no other kernel writes
 // (the decode kernel that may share the scratch uses words 0..2 and the bytes behind the header).
 constexpr int kCounterWord0 = 8, kMaxSplitTiles = 56;
-// Up to 48 tokens the k split goes over independent CTAs with slabs in global memory (any number of splits, as
+// Up to 24 tokens the k split goes over independent CTAs with slabs in global memory (any number of splits, as
 // many as there are idle SMs); beyond, the serial slab reduction of the last CTA costs more than the split saves
-// and the split goes over the CTAs of a cluster instead.  Qwen3-8B decode step, slabs against clusters: 32 tokens
-// 3.84 against 4.50 ms, 64 tokens 4.89 against 4.54 ms.
-constexpr int kMaxSplitTokens = 48;
+// and the split goes over the CTAs of a cluster instead.  Qwen3-8B decode step, slabs against clusters: 16 tokens
+// 3.59 against 3.76 ms, 32 tokens 3.79 against 3.73 ms, 48 tokens 4.38 against 3.83 ms.
+constexpr int kMaxSplitTokens = 24;
 
 // The four tile configurations as the host sees them.
 struct KernelInfo {
@@ -810,8 +820,8 @@ static int cluster_capacity(int mh, int nh, int s) {
 // cycles per 64-column step (bounded by the tensor pipe for the 256 x 256 tile, by shared-memory traffic and the
 // per-step waits of the issuing threads for the smaller ones); the grid runs in ceil(CTAs/resident CTAs) waves, each
 // with a fixed prologue/epilogue cost.  Launches that would leave SMs idle split the k dimension of every job
-// (whole 256-column chunks per CTA): above 48 tokens over the CTAs of a cluster, which add their partial sums
-// through distributed shared memory; up to 48 tokens over independent CTAs with fp32 slabs in global memory, as
+// (whole 256-column chunks per CTA): above 24 tokens over the CTAs of a cluster, which add their partial sums
+// through distributed shared memory; up to 24 tokens over independent CTAs with fp32 slabs in global memory, as
 // far as counters and slab budget allow.
 static GroupPlan plan_group(int T, int n, const int* K, const int* Nout, bool allow_split, bool allow_cluster) {
     GroupPlan pl;

@@ -221,9 +221,9 @@ def test_c_abi_gemm_group_matches_single_linears(T):
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-@pytest.mark.parametrize("T", [49, 100, 128, 200, 300])
+@pytest.mark.parametrize("T", [25, 40, 100, 128, 200, 300])
 def test_c_abi_gemm_cluster_split(T, dtype):
-    # Few output tiles above 48 tokens: the k dimension is split over the CTAs of a thread-block cluster, which add
+    # Few output tiles above 24 tokens: the k dimension is split over the CTAs of a thread-block cluster, which add
     # their partial sums through distributed shared memory.  Two linears with different ranks in one launch, so the
     # chunks per CTA differ per job and the last CTA of a cluster has no chunk of the smaller job (it contributes
     # zeros); ragged token counts; the result must not change from run to run (fixed summation order).
