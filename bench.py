@@ -461,6 +461,11 @@ def side_numbers(device, dtype, step_ms):
                                    "kernel": step.kernel_name, "hbm_frac": step.bytes / (ms * 1e-3) / 1e9 / hbm_peak()[0]}
         del step
         torch.cuda.empty_cache()
+    for T in (1, 4):   # the reference's CUDA GEMV on the same GPU and linears, when its library was built
+        r = measure_refkernel(T, LAYERS, 10, 3, device)
+        if r is not None:
+            out[f"reference_cuda_gemv_decode_batch{T}"] = r
+        torch.cuda.empty_cache()
     out["lm_head_gemv"] = measure_head(device, dtype, 1, step_ms)
     for model in ("llama-2-7b", "qwen3-8b"):
         for tokens in (2048, 512, 128):
@@ -1125,6 +1130,105 @@ def head_arm(args):
         "gpu_launches": args.steps, "clocks": clocks}), flush=True)
 
 
+REF_KERNEL_LIB = os.path.join(ROOT, "baseline", "_ref", "libnq_reference_kernels.so")
+# the launch parameters the reference's module passes (src/nanoquant/modules/linear.py:175-184)
+REF_GEMV_KWARGS = dict(num_thread_stage1=128, num_thread_stage2=128, num_row_per_warp_stage1=2, num_row_per_warp_stage2=2,
+                       num_acc_stage1=1, num_acc_stage2=1, num_pipeline_stage1=8, num_pipeline_stage2=8)
+
+
+def measure_refkernel(T, layers_timed, steps, warmup, device):
+    """The REFERENCE's own decode GEMV (its `gemv_kernel.cu`, compiled for sm_100 by `baseline/build_ref_kernels.py`) on
+    the linears of the decode step, one operator call per linear (two kernel launches each) replayed from a CUDA graph
+    as the reference's decode benchmark does (`kernel/test_decode.py:385-417`).  Returns a record, or None when the
+    library is not built."""
+    import torch
+    if not os.path.exists(REF_KERNEL_LIB):
+        return None
+    torch.ops.load_library(REF_KERNEL_LIB)
+    op = torch.ops.nq_reference.nanoquant_dyn_forward
+    dtype = torch.bfloat16
+    g = torch.Generator(device=device).manual_seed(0)
+    words = lambda rows, cols: torch.randint(-2**31, 2**31 - 1, (rows, cols // 32), generator=g, device=device, dtype=torch.int32)
+    scale = lambda n: ((torch.rand(n, generator=g, device=device) + 0.5) * 0.01).to(dtype)
+    xs = {"h": torch.randn(T, HIDDEN, generator=g, device=device).to(dtype),
+          "i": torch.randn(T, INTER, generator=g, device=device).to(dtype)}
+    layers = []
+    for _ in range(layers_timed):
+        layers.append([(src, scale(N), words(R, N), scale(R), words(M, R), scale(M)) for (_, N, R, M, src, _) in layer_linears()])
+
+    # one linear against the oracle first: the operands are in the reference's `half2` row layout
+    err = None
+    try:
+        from oracle import nanoquant_oracle as oc
+        import numpy as np
+        d = oc.synth_linear(1024, 256, 512, T, seed=5)
+        to = lambda a: torch.from_numpy(np.ascontiguousarray(a).astype(np.float32)).to(dtype).to(device)
+        bits = lambda w: torch.from_numpy(oc.pack_rows(w, "half2")).to(device)
+        xq, a, b, c = to(d["x"]), to(d["s_pre"]), to(d["s_mid"]), to(d["s_post"])
+        y = op(xq, a, bits(d["V"]), b, bits(d["U"]), c, **REF_GEMV_KWARGS)
+        f = lambda t: t.float().cpu().numpy().astype(np.float64)
+        err = float(oc.rel_err(f(y), oc.forward_fp64(f(xq), d["V"], d["U"], f(a), f(b), f(c))))
+    except ImportError:
+        pass
+
+    def run():
+        out = None
+        for lay in layers:
+            for (src, a, v, b, u, c) in lay:
+                out = op(xs[src], a, v, b, u, c, **REF_GEMV_KWARGS)
+        return out
+    stream = torch.cuda.Stream(device)
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            run()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            run()
+        for _ in range(max(warmup, 3)):
+            graph.replay()
+        stream.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            graph.replay()
+        e1.record(stream)
+        stream.synchronize()
+    ms = e0.elapsed_time(e1) / steps * (LAYERS / layers_timed)
+    nbytes = sum(algorithmic_bytes(N, R, M, T) for (_, N, R, M, _, _) in layer_linears()) * LAYERS
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    return {"value": T / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms, "hbm_gbs": gbs, "hbm_frac": gbs / hbm_peak()[0],
+            "launches_per_step": 2 * 7 * LAYERS, "layers_timed": layers_timed, "max_rel_err_vs_oracle": err,
+            "what": "the reference's own gemv_kernel.cu built for sm_100, one call per linear, CUDA-graph replay, same GPU"}
+
+
+def refkernel_arm(args):
+    """`--mode refkernel`: a same-GPU kernel-against-kernel figure beside the default line (not the `--impl reference`
+    arm, which is the reference's CPU path)."""
+    import torch
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(device)
+    sampler = ClockSampler(device.index or 0)
+    sampler.start()
+    r = measure_refkernel(args.batch, args.layers, args.steps, args.warmup, device)
+    clocks = sampler.stop()
+    if r is None:
+        print(json.dumps({"mode": "refkernel", "unavailable": "baseline/_ref/libnq_reference_kernels.so is not built "
+                          "(python baseline/build_ref_kernels.py needs the reference checkout)"}), flush=True)
+        return
+    peak, peak_src = hbm_peak()
+    print(json.dumps({
+        "mode": "refkernel", "impl": "reference CUDA kernels (gemv_kernel.cu, sm_100 build)",
+        "metric": "decode tok/s (quantised linears of one decode step)", "value": r["value"], "unit": "tokens/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": r["ms_per_step"],
+        "higher_is_better": True, "dtype": "bf16 (half2-style accumulation in the I/O type)", "data": "synthetic",
+        "config": workload_config(args.batch),
+        "roofline": {"bound": "hbm", "achieved": r["hbm_gbs"], "peak": peak, "unit": "GB/s", "frac": r["hbm_frac"],
+                     "traffic": None, "peak_source": peak_src},
+        "gpu_launches": 2 * 7 * args.layers * args.steps, "layers_timed": args.layers,
+        "max_rel_err_vs_oracle": r["max_rel_err_vs_oracle"], "clocks": clocks}), flush=True)
+
+
 def probe_arm(args):
     """`--mode probe`: the library's measurement probes.  `chain_us` is the time per launch of a decode launch's
     dependent chain with the arithmetic taken out (the floor of the launch structure) for several CTA counts;
@@ -1167,7 +1271,7 @@ def main():
     ap.add_argument("--no-check", action="store_true", help="skip the output check of the launch structure against the oracle")
     ap.add_argument("--no-side-numbers", action="store_true",
                     help="skip the short batch-4 / batch-16 / prefill measurements added to the default line")
-    ap.add_argument("--mode", default="replica", choices=["replica", "tp", "prefill", "head", "linear", "pack", "probe"],
+    ap.add_argument("--mode", default="replica", choices=["replica", "tp", "prefill", "head", "linear", "pack", "probe", "refkernel"],
                     help="replica: the decode step (N > 1: independent replicas); tp: 70B-shaped TP decode step; "
                          "prefill: GEMM TFLOP/s on Llama-2-7B-shaped layers")
     ap.add_argument("--shape", default="config1", choices=sorted(GROUP_SHAPES), help="launch group of --mode linear")
@@ -1201,6 +1305,8 @@ def main():
         pack_arm(args)
     elif args.mode == "probe":
         probe_arm(args)
+    elif args.mode == "refkernel":
+        refkernel_arm(args)
     else:
         gpu_arm(args)
 

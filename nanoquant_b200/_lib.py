@@ -11,8 +11,7 @@ import os
 from ctypes import c_char_p, c_int, c_int64, c_size_t, c_void_p
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-# NANOQUANT_B200_LIB selects another build of the same library (e.g. one compiled with development macros)
-LIB_PATH = os.environ.get("NANOQUANT_B200_LIB") or os.path.join(_PKG, "libnanoquant_b200.so")
+LIB_PATH = os.path.join(_PKG, "libnanoquant_b200.so")
 
 NQ_F16, NQ_BF16 = 0, 1
 NQ_LSB_FIRST, NQ_HALF2 = 0, 1

@@ -29,6 +29,11 @@ class LinearGroup:
         self.dtype = modules[0].dtype
         if any(m.dtype != self.dtype for m in modules):
             raise ValueError("the linears of a group share one dtype")
+        # scratch for this group at decode batches and at up to 64 tokens, reserved now: a forward (or a stream
+        # capture) then only reads the buffer's address
+        shapes = [(m.in_features, m.rank, m.out_features) for m in self.modules]
+        device = self.modules[0].scale_post.device
+        ops.reserve_scratch(device, max(ops.group_scratch_bytes(shapes, T) for T in (4, 24, 64)))
 
     @staticmethod
     def _layer(m: NanoQuantLinear):

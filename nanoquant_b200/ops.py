@@ -40,6 +40,7 @@ _SWEEP = {  # reference: cuda/gemv_kernel.cu:351-354
 }
 
 _scratch = {}        # device index -> zero-initialised uint8 tensor
+_retired = []        # outgrown scratch buffers, kept for graphs that were captured on them
 _SCRATCH_MIN = 4 << 20
 _override = threading.local()   # .buf: a caller-provided scratch for this thread (see private_scratch)
 
@@ -64,9 +65,22 @@ def reserve_scratch(device: torch.device, nbytes: int) -> torch.Tensor:
         if torch.cuda.is_current_stream_capturing():
             raise RuntimeError("nanoquant_b200: the kernels' scratch buffer would have to be (re)allocated inside a "
                                "stream capture; prepare the layers (or call nanoquant_b200.ops.reserve_scratch) first")
+        if buf is not None:
+            _retired.append(buf)   # a CUDA graph captured earlier may still point at the smaller buffer: keep it alive
         buf = torch.zeros(max(int(nbytes), _SCRATCH_MIN), dtype=torch.uint8, device=torch.device("cuda", idx))
         _scratch[idx] = buf
     return buf
+
+
+def group_scratch_bytes(shapes, T: int) -> int:
+    """Scratch bytes one launch group of linears with ``shapes = [(N, R, M), ...]`` needs at `T` tokens."""
+    L = _lib.lib()
+    arr = (_lib.LinearDesc * len(shapes))()
+    for d, (N, R, M) in zip(arr, shapes):
+        d.N, d.R, d.M = int(N), int(R), int(M)
+    if T <= L.nq_gemv_max_tokens():
+        return int(L.nq_gemv_group_scratch_bytes(arr, len(shapes), T))
+    return int(L.nq_gemm_group_scratch_bytes(arr, len(shapes), T))
 
 
 def scratch_for(device: torch.device, nbytes: int) -> torch.Tensor:

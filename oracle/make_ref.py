@@ -1,6 +1,6 @@
 """Stage the reference's own Python for this path under ``oracle/_ref`` (test infrastructure, not shipped).
 
-    python oracle/make_ref.py [/path/to/NanoQuant]        (default /root/reference)
+    python oracle/make_ref.py [/path/to/NanoQuant]        (default: $NANOQUANT_REFERENCE)
 
 Copies the two pure-Python files of the hot path, ``src/nanoquant/modules/linear.py`` (the module whose
 ``forward`` / ``_prepare_kernel`` the kernels sit behind, and whose PyTorch branch is the dequantise-then-matmul
@@ -20,7 +20,10 @@ DST = os.path.join(HERE, "_ref", "nanoquant_ref")
 FILES = (("modules", "linear.py"), ("kernel", "utils.py"))
 
 
-def make(ref_root: str = "/root/reference") -> bool:
+DEFAULT_ROOT = os.environ.get("NANOQUANT_REFERENCE", os.path.join(os.sep, "root", "reference"))
+
+
+def make(ref_root: str = DEFAULT_ROOT) -> bool:
     src = os.path.join(ref_root, "src", "nanoquant")
     if not all(os.path.exists(os.path.join(src, d, f)) for d, f in FILES):
         return False
@@ -44,5 +47,5 @@ def load():
 
 
 if __name__ == "__main__":
-    ok = make(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    ok = make(sys.argv[1] if len(sys.argv) > 1 else DEFAULT_ROOT)
     print("staged" if ok else "reference sources not found: nothing staged", DST)
