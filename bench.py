@@ -1082,19 +1082,40 @@ def pack_arm(args):
         ("nq_rows_to_tiles", W / 8 + W / 8, n_packed, lambda i: L.nq_rows_to_tiles(words[i].data_ptr(), out_tiles.data_ptr(), rows, cols, _lib.NQ_LSB_FIRST, st)),
         ("nq_reorder_words", W / 8 + W / 8, n_packed, lambda i: L.nq_reorder_words(words[i].data_ptr(), out_words.data_ptr(), rows * (cols // 32), _lib.NQ_LSB_FIRST, _lib.NQ_HALF2, st)),
     ]
+    # the word-to-word kernels again on a 70B-sized factor (28672 x 8192: 59 MB read + written per launch): at
+    # 12288 x 4096 they move 12.6 MB, which the memory system delivers in 2 us, less than a launch takes to ramp up
+    rows2, cols2 = 28672, 8192
+    W2 = rows2 * cols2
+    words2 = [torch.randint(-2**31, 2**31 - 1, (rows2, cols2 // 32), generator=g, device=device, dtype=torch.int32)
+              for _ in range(5)]
+    out_words2 = torch.empty(rows2, cols2 // 32, dtype=torch.int32, device=device)
+    out_tiles2 = torch.empty(L.nq_tiles_bytes(rows2, cols2), dtype=torch.uint8, device=device)
+    cases += [
+        ("nq_rows_to_tiles 28672x8192", W2 / 4, 5, lambda i: L.nq_rows_to_tiles(words2[i].data_ptr(), out_tiles2.data_ptr(), rows2, cols2, _lib.NQ_LSB_FIRST, st)),
+        ("nq_reorder_words 28672x8192", W2 / 4, 5, lambda i: L.nq_reorder_words(words2[i].data_ptr(), out_words2.data_ptr(), rows2 * (cols2 // 32), _lib.NQ_LSB_FIRST, _lib.NQ_HALF2, st)),
+    ]
     peak, peak_src = hbm_peak()
     res = {}
+    stream = torch.cuda.Stream(device)
     for name, nbytes, n, fn in cases:
-        for i in range(n):
-            _lib.check(fn(i), name)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize(device)
-        e0.record()
-        for _ in range(args.steps):
+        # one rotation over the inputs as a CUDA graph: the kernels take 2-15 us, less than a launch from Python
+        with torch.cuda.stream(stream):
+            st = stream.cuda_stream
             for i in range(n):
-                fn(i)
-        e1.record()
-        torch.cuda.synchronize(device)
+                _lib.check(fn(i), name)
+            stream.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                for i in range(n):
+                    _lib.check(fn(i), name)
+            graph.replay()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            stream.synchronize()
+            e0.record(stream)
+            for _ in range(args.steps):
+                graph.replay()
+            e1.record(stream)
+            stream.synchronize()
         us = e0.elapsed_time(e1) * 1e3 / (args.steps * n)
         res[name] = {"us": us, "GBps": nbytes / us / 1e3, "hbm_frac": nbytes / us / 1e3 / peak, "algorithmic_bytes": nbytes}
     top = res["nq_rows_to_tiles"]
@@ -1105,7 +1126,7 @@ def pack_arm(args):
         "config": {"workload": f"{rows} x {cols} +-1 matrix; {n_dense} dense / {n_packed} packed inputs in rotation (> 2 x L2)"},
         "roofline": {"bound": "hbm", "achieved": top["GBps"], "peak": peak, "unit": "GB/s", "frac": top["hbm_frac"],
                      "traffic": None, "kernel": "rows_to_tiles_kernel", "peak_source": peak_src},
-        "kernels": res, "gpu_launches": args.steps * (3 * n_packed + 2 * n_dense)}), flush=True)
+        "kernels": res, "gpu_launches": args.steps * (3 * n_packed + 2 * n_dense + 10)}), flush=True)
 
 
 def head_arm(args):

@@ -82,6 +82,48 @@ __global__ void unpack_rows_kernel(const uint32_t* __restrict__ packed, int8_t* 
     }
 }
 
+// The same two conversions for matrices of whole 32-column words at a 16-byte aligned address, with every global
+// access of a warp contiguous: the dense side moves in 512-byte pieces (one 16-byte piece per lane), the packed
+// side in 128-byte pieces (one word per lane), and the lanes trade their halves with shuffles.  A warp handles
+// 32 consecutive words (1 KB of weights) per step; `n_words` is a multiple of 32 here, the tail goes to the
+// word-per-thread kernels above.
+__global__ void __launch_bounds__(256) pack_rows_warp_kernel(const uint4* __restrict__ w, uint32_t* __restrict__ out,
+                                                             int64_t n_words, int order) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t base = ((blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5) * 32; base < n_words; base += warps * 32) {
+        // piece p (16 weights) of this step belongs to word base + p/2, half p & 1
+        const uint4 a = __ldcs(w + base * 2 + lane), b = __ldcs(w + base * 2 + 32 + lane);
+        const uint32_t ha = sign_nibble(a.x) | (sign_nibble(a.y) << 4) | (sign_nibble(a.z) << 8) | (sign_nibble(a.w) << 12);
+        const uint32_t hb = sign_nibble(b.x) | (sign_nibble(b.y) << 4) | (sign_nibble(b.z) << 8) | (sign_nibble(b.w) << 12);
+        // lane L wants word base + L: its halves are pieces 2L and 2L + 1, i.e. lanes 2(L & 15) and +1 of load a (L < 16) or b
+        const int src = 2 * (lane & 15);
+        const uint32_t a_lo = __shfl_sync(0xffffffffu, ha, src), a_hi = __shfl_sync(0xffffffffu, ha, src + 1);
+        const uint32_t b_lo = __shfl_sync(0xffffffffu, hb, src), b_hi = __shfl_sync(0xffffffffu, hb, src + 1);
+        const uint32_t bits = lane < 16 ? (a_lo | (a_hi << 16)) : (b_lo | (b_hi << 16));
+        out[base + lane] = convert_order(bits, NQ_LSB_FIRST, order);
+    }
+}
+
+__global__ void __launch_bounds__(256) unpack_rows_warp_kernel(const uint32_t* __restrict__ packed, uint4* __restrict__ w,
+                                                               int64_t n_words, int order) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t base = ((blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5) * 32; base < n_words; base += warps * 32) {
+        const uint32_t mine = convert_order(__ldcs(packed + base + lane), order, NQ_LSB_FIRST);
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            // piece 32k + lane: word base + 16k + lane/2, half lane & 1
+            const uint32_t word = __shfl_sync(0xffffffffu, mine, 16 * k + (lane >> 1));
+            const uint32_t h = (word >> (16 * (lane & 1))) & 0xFFFFu;
+            uint32_t v[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) v[q] = 0x01010101u + spread_nibble(h >> (4 * q)) * 0xFEu;   // +1 = 0x01, -1 = 0xFF
+            __stcs(w + base * 2 + 32 * k + lane, make_uint4(v[0], v[1], v[2], v[3]));
+        }
+    }
+}
+
 __global__ void reorder_words_kernel(const uint32_t* __restrict__ in, uint32_t* __restrict__ out,
                                      int64_t n, int from, int to) {
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n;
@@ -225,30 +267,49 @@ __global__ void permute_scale16_kernel(const uint16_t* __restrict__ s, uint16_t*
 // A-fragment register of an m16n8k32 MMA over columns [32j, 32j+32) with values
 // {0, 2^j} (j = 7: {0, -128}).  Rows and columns beyond the matrix are +1 (bit 0).
 // ---------------------------------------------------------------------------
-__global__ void rows_to_tiles_kernel(const uint32_t* __restrict__ packed, uint4* __restrict__ tiles,
-                                     int64_t rows, int64_t words, int64_t row_groups, int64_t chunks,
-                                     int order) {
-    const int64_t total = row_groups * chunks * 32;
-    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
-         i += (int64_t)gridDim.x * blockDim.x) {
-        const int lane = (int)(i & 31);
-        const int64_t tile = i >> 5;
-        const int64_t rg = tile / chunks, c = tile - rg * chunks;
-        const int g = lane >> 2, q = lane & 3;
-        uint32_t o[4] = {0, 0, 0, 0};
+// Through shared memory: a work item is one row group (16 rows) by eight chunks (64 words per row); a block
+// reads the 16 row pieces of 256 bytes with contiguous loads and writes eight whole tiles (one uint4 per thread).
+// (One thread per output lane reading its 16 words straight from global memory touches a 32-byte sector per word.)
+// Blocks stride over the items and load the next item's words into registers before they convert the current one.
+__global__ void __launch_bounds__(256) rows_to_tiles_staged_kernel(const uint32_t* __restrict__ packed, uint4* __restrict__ tiles,
+                                                                   int64_t rows, int64_t words, int64_t chunks, int64_t cblocks,
+                                                                   int64_t items, int order) {
+    __shared__ uint32_t s[16][65];
+    const int cl = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
+    uint32_t nxt[4];
+    auto fetch = [&](int64_t item) {
+        const int64_t rg = item / cblocks, c0 = (item - rg * cblocks) * 8;
 #pragma unroll
-        for (int half_row = 0; half_row < 2; ++half_row) {
-            const int64_t r = rg * 16 + g + 8 * half_row;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const int64_t wi = c * 8 + j;
-                uint32_t src = 0;
-                if (r < rows && wi < words) src = convert_order(packed[r * words + wi], order, NQ_LSB_FIRST);
-                o[half_row] |= spread_nibble(src >> (4 * q)) << j;           // h = 0
-                o[2 + half_row] |= spread_nibble(src >> (16 + 4 * q)) << j;  // h = 1
-            }
+        for (int k = 0; k < 4; ++k) {
+            const int i = threadIdx.x + 256 * k, r = i >> 6, wl = i & 63;
+            const int64_t gr = rg * 16 + r, gw = c0 * 8 + wl;
+            nxt[k] = (gr < rows && gw < words) ? __ldcs(packed + gr * words + gw) : 0u;
         }
-        tiles[i] = make_uint4(o[0], o[1], o[2], o[3]);
+    };
+    int64_t item = blockIdx.x;
+    if (item < items) fetch(item);
+    for (; item < items; item += gridDim.x) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int i = threadIdx.x + 256 * k;
+            s[i >> 6][i & 63] = convert_order(nxt[k], order, NQ_LSB_FIRST);   // padding words are 0 in either order
+        }
+        __syncthreads();
+        if (item + gridDim.x < items) fetch(item + gridDim.x);
+        const int64_t rg = item / cblocks, c0 = (item - rg * cblocks) * 8;
+        if (c0 + cl < chunks) {
+            uint32_t o[4] = {0, 0, 0, 0};
+#pragma unroll
+            for (int half_row = 0; half_row < 2; ++half_row)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const uint32_t src = s[g + 8 * half_row][cl * 8 + j];
+                    o[half_row] |= spread_nibble(src >> (4 * q)) << j;           // h = 0
+                    o[2 + half_row] |= spread_nibble(src >> (16 + 4 * q)) << j;  // h = 1
+                }
+            __stcs(tiles + ((rg * chunks + c0 + cl) << 5) + lane, make_uint4(o[0], o[1], o[2], o[3]));
+        }
+        __syncthreads();
     }
 }
 
@@ -274,6 +335,13 @@ __global__ void tiles_to_rows_kernel(const uint4* __restrict__ tiles, uint32_t* 
     }
 }
 
+// gcd(n, 32) for n > 0: the largest power of two up to 32 that divides n
+static int64_t gcd32(int64_t n) {
+    int64_t g = 1;
+    while (g < 32 && n % (2 * g) == 0) g *= 2;
+    return g;
+}
+
 static int check_order(int o) { return (o == NQ_LSB_FIRST || o == NQ_HALF2) ? NQ_OK : NQ_ERR_DTYPE; }
 
 }  // namespace nq
@@ -290,9 +358,24 @@ int nq_pack_rows(const int8_t* w, int32_t* packed, int64_t rows, int64_t cols, i
     if (!w || !packed) return NQ_ERR_NULL;
     const int64_t words = (cols + 31) / 32;
     const bool vec = (cols % 16 == 0) && aligned16(w);
-    pack_rows_kernel<<<grid_for(rows * words, kPackThreads), kPackThreads, 0, as_stream(stream)>>>(
-        w, reinterpret_cast<uint32_t*>(packed), rows, cols, words, bit_order, vec);
-    NQ_LAUNCH_CHECK();
+    // whole words at an aligned address: the rows form one run of words; the leading rows whose words are a multiple
+    // of 32 go to the warp-contiguous kernel, the remaining rows to the word-per-thread kernel
+    int64_t done_rows = 0;
+    if (cols % 32 == 0 && aligned16(w)) {
+        const int64_t step = 32 / gcd32(words), head_rows = rows / step * step, head = head_rows * words;
+        if (head > 0) {
+            pack_rows_warp_kernel<<<grid_for(head, kPackThreads), kPackThreads, 0, as_stream(stream)>>>(
+                reinterpret_cast<const uint4*>(w), reinterpret_cast<uint32_t*>(packed), head, bit_order);
+            NQ_LAUNCH_CHECK();
+            done_rows = head_rows;
+        }
+    }
+    if (done_rows < rows) {
+        pack_rows_kernel<<<grid_for((rows - done_rows) * words, kPackThreads), kPackThreads, 0, as_stream(stream)>>>(
+            w + done_rows * cols, reinterpret_cast<uint32_t*>(packed) + done_rows * words, rows - done_rows, cols, words,
+            bit_order, vec);
+        NQ_LAUNCH_CHECK();
+    }
     return NQ_OK;
 }
 
@@ -304,9 +387,22 @@ int nq_unpack_rows(const int32_t* packed, int8_t* w, int64_t rows, int64_t cols,
     if (!w || !packed) return NQ_ERR_NULL;
     const int64_t words = (cols + 31) / 32;
     const bool vec = (cols % 16 == 0) && aligned16(w);
-    unpack_rows_kernel<<<grid_for(rows * words, kPackThreads), kPackThreads, 0, as_stream(stream)>>>(
-        reinterpret_cast<const uint32_t*>(packed), w, rows, cols, words, bit_order, vec);
-    NQ_LAUNCH_CHECK();
+    int64_t done_rows = 0;
+    if (cols % 32 == 0 && aligned16(w)) {   // see nq_pack_rows
+        const int64_t step = 32 / gcd32(words), head_rows = rows / step * step, head = head_rows * words;
+        if (head > 0) {
+            unpack_rows_warp_kernel<<<grid_for(head, kPackThreads), kPackThreads, 0, as_stream(stream)>>>(
+                reinterpret_cast<const uint32_t*>(packed), reinterpret_cast<uint4*>(w), head, bit_order);
+            NQ_LAUNCH_CHECK();
+            done_rows = head_rows;
+        }
+    }
+    if (done_rows < rows) {
+        unpack_rows_kernel<<<grid_for((rows - done_rows) * words, kPackThreads), kPackThreads, 0, as_stream(stream)>>>(
+            reinterpret_cast<const uint32_t*>(packed) + done_rows * words, w + done_rows * cols, rows - done_rows, cols, words,
+            bit_order, vec);
+        NQ_LAUNCH_CHECK();
+    }
     return NQ_OK;
 }
 
@@ -377,8 +473,10 @@ int nq_rows_to_tiles(const int32_t* packed, void* tiles, int64_t rows, int64_t c
     if (!packed || !tiles) return NQ_ERR_NULL;
     if (!aligned16(tiles)) return NQ_ERR_ALIGN;
     const int64_t words = (cols + 31) / 32, rgs = (rows + 15) / 16, chunks = (cols + 255) / 256;
-    rows_to_tiles_kernel<<<grid_for(rgs * chunks * 32, kPackThreads), kPackThreads, 0, as_stream(stream)>>>(
-        reinterpret_cast<const uint32_t*>(packed), static_cast<uint4*>(tiles), rows, words, rgs, chunks, bit_order);
+    const int64_t cblocks = (chunks + 7) / 8, items = rgs * cblocks;
+    const int64_t resident = (int64_t)sm_count() * 8;   // 256-thread blocks that are resident at once
+    rows_to_tiles_staged_kernel<<<(unsigned)(items < resident ? items : resident), 256, 0, as_stream(stream)>>>(
+        reinterpret_cast<const uint32_t*>(packed), static_cast<uint4*>(tiles), rows, words, chunks, cblocks, items, bit_order);
     NQ_LAUNCH_CHECK();
     return NQ_OK;
 }
