@@ -828,10 +828,13 @@ PREFILL_SHAPES = {   # name -> (hidden, intermediate, kv width, bits per weight)
 }
 
 
-def measure_prefill(T, layers, steps, warmup, device, profile=False, min_seconds=0.0, e2e=False, model="llama-2-7b"):
-    """TFLOP/s of nq_gemm_fwd on the 7 linears of `layers` decoder layers of `model`'s shape (ranks from the rank
-    formula at its bit budget), T tokens per GEMM.  Returns (TFLOP/s, ms per step, launches per step, clock record
-    or None, end-to-end record or None)."""
+def measure_prefill(T, layers, steps, warmup, device, profile=False, min_seconds=0.0, e2e=False, model="llama-2-7b",
+                    grouped=True):
+    """TFLOP/s of the GEMM path on the 7 linears of `layers` decoder layers of `model`'s shape (ranks from the rank
+    formula at its bit budget), T tokens per GEMM.  `grouped`: q/k/v and gate/up go through nq_gemm_group_fwd as one
+    launch group each (what `LinearGroup` issues for a decoder layer, as in the decode step); otherwise one
+    nq_gemm_fwd per linear.  Returns (TFLOP/s, ms per step, launches per step, clock record or None, end-to-end
+    record or None)."""
     import torch
     from nanoquant_b200 import _lib
     L = _lib.lib()
@@ -844,22 +847,28 @@ def measure_prefill(T, layers, steps, warmup, device, profile=False, min_seconds
     scale = lambda n: ((torch.rand(n, generator=g, device=device) + 0.5) * 0.01).to(dtype)
     xs = {H: torch.randn(T, H, generator=g, device=device).to(dtype), I: torch.randn(T, I, generator=g, device=device).to(dtype)}
     calls, flops, scratch_bytes = [], 0.0, 0
+    group_of = [0, 0, 0, 1, 2, 2, 3] if grouped else list(range(7))
     for _ in range(layers):
-        for (N, M) in shapes:
+        members = {}
+        for (N, M), gi in zip(shapes, group_of):
             R = rank_for_bits(N, M, bpw)
             t = dict(v=rnd_bits(R, N), u=rnd_bits(M, R), a=scale(N), b=scale(R), c=scale(M),
                      y=torch.empty(T, M, device=device, dtype=dtype))
-            calls.append((t, N, R, M))
+            members.setdefault(gi, []).append((t, N, R, M))
             flops += 2.0 * T * R * (N + M)
-            scratch_bytes = max(scratch_bytes, L.nq_gemm_scratch_bytes(T, N, R, M))
+        for gi in sorted(members):
+            descs = [_lib.LinearDesc(xs[N].data_ptr(), t["a"].data_ptr(), t["v"].data_ptr(), t["b"].data_ptr(), t["u"].data_ptr(),
+                                     t["c"].data_ptr(), t["y"].data_ptr(), N, R, M, N, M) for (t, N, R, M) in members[gi]]
+            arr = (_lib.LinearDesc * len(descs))(*descs)
+            calls.append((arr, len(descs), members[gi]))
+            scratch_bytes = max(scratch_bytes, L.nq_gemm_group_scratch_bytes(arr, len(descs), T))
     scratch = torch.zeros(scratch_bytes, dtype=torch.uint8, device=device)
     st = torch.cuda.current_stream(device).cuda_stream
 
     def run():
-        for (t, N, R, M) in calls:
-            _lib.check(L.nq_gemm_fwd(xs[N].data_ptr(), t["a"].data_ptr(), t["v"].data_ptr(), t["b"].data_ptr(),
-                                     t["u"].data_ptr(), t["c"].data_ptr(), t["y"].data_ptr(), scratch.data_ptr(),
-                                     scratch.numel(), T, N, R, M, _lib.NQ_BF16, st), "nq_gemm_fwd")
+        for (arr, n, _) in calls:
+            _lib.check(L.nq_gemm_group_fwd(arr, n, T, _lib.NQ_BF16, scratch.data_ptr(), scratch.numel(), st),
+                       "nq_gemm_group_fwd")
     for _ in range(max(warmup, 3)):
         run()
     torch.cuda.synchronize(device)
@@ -887,7 +896,7 @@ def measure_prefill(T, layers, steps, warmup, device, profile=False, min_seconds
     e2e_info = None
     if e2e:   # the same step with the activations copied from pinned host memory and the last output read back
         hx = {k: v.cpu().pin_memory() for k, v in xs.items()}
-        last_y = calls[-1][0]["y"]
+        last_y = calls[-1][2][-1][0]["y"]
         hy = torch.empty_like(last_y, device="cpu").pin_memory()
 
         def e2e_step():
@@ -922,7 +931,7 @@ def prefill_arm(args):
     layers = args.layers if args.layers != LAYERS else 4
     model = args.prefill_model
     tf, ms, launches, clocks, e2e = measure_prefill(T, layers, args.steps, args.warmup, device, profile=True,
-                                                    min_seconds=1.0, e2e=True, model=model)
+                                                    min_seconds=1.0, e2e=True, model=model, grouped=not args.no_groups)
     peak, peak_src = tensor_peak()
     print(json.dumps({
         "mode": "prefill", "metric": "prefill TFLOP/s (quantised linears, 2*T*R*(N+M) flops)", "value": tf,
@@ -930,7 +939,9 @@ def prefill_arm(args):
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 (fp32 accumulate)",
         "data": "synthetic",
         "config": {"workload": f"{model}-shaped layer GEMMs at {PREFILL_SHAPES[model][3]} bpw, {T} tokens per GEMM, "
-                               f"{layers} layers", "tokens": T},
+                               f"{layers} layers; " + ("one launch per linear and stage" if args.no_groups else
+                                                       "q/k/v and gate/up as launch groups (8 launches per layer)"),
+                   "tokens": T},
         "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak,
                      "traffic": None, "kernel": "gemm_stage_kernel", "peak_source": peak_src},
         "e2e": e2e,
@@ -1302,6 +1313,8 @@ def main():
     ap.add_argument("--tokens", type=int, default=2048, help="tokens per GEMM in --mode prefill")
     ap.add_argument("--prefill-model", default="llama-2-7b", choices=sorted(PREFILL_SHAPES),
                     help="layer shapes of --mode prefill")
+    ap.add_argument("--no-groups", action="store_true",
+                    help="--mode prefill: one GEMM call per linear instead of launch groups for q/k/v and gate/up")
     ap.add_argument("--layers", type=int, default=LAYERS, help="decoder layers resident (fewer only for profiling)")
     ap.add_argument("--tp-layers", type=int, default=TP_LAYERS, help="layers actually timed in --mode tp")
     ap.add_argument("--tp-collective", default="peer", choices=["peer", "nccl"],

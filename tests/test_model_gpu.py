@@ -197,3 +197,33 @@ def test_operators_under_torch_compile():
         outs += [fn2(x).clone() for _ in range(3)]
     for y in outs:
         assert torch.equal(y, y_eager)
+
+
+def test_private_scratch_on_a_second_stream():
+    # Two streams run layers at the same time: the second one brings its own scratch (the shared per-device buffer
+    # holds one launch's intermediate at a time); results equal the single-stream ones bit for bit.
+    from nanoquant_b200 import ops
+    from nanoquant_b200.modules.linear import NanoQuantLinear
+    mods = []
+    for i, (n, r, m) in enumerate([(512, 160, 384), (512, 96, 256)]):
+        d = oc.synth_linear(n, r, m, 2, seed=70 + i)
+        lin = NanoQuantLinear(n, m, r, has_scale_mid=True)
+        fill(lin, d)
+        lin = lin.cuda()
+        lin._prepare_kernel("gemv", DT)
+        mods.append(lin)
+    x = torch.randn(2, 512, device="cuda").to(DT)
+    ref = [m(x).clone() for m in mods]
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    mine = torch.zeros(1 << 20, dtype=torch.uint8, device="cuda")
+    outs = [None, None]
+    for _ in range(20):
+        with torch.cuda.stream(side), ops.private_scratch(mine):
+            outs[1] = mods[1](x)
+        outs[0] = mods[0](x)
+    torch.cuda.synchronize()
+    assert torch.equal(outs[0], ref[0]) and torch.equal(outs[1], ref[1])
+    with pytest.raises(RuntimeError, match="too small"):
+        with ops.private_scratch(torch.zeros(64, dtype=torch.uint8, device="cuda")):
+            mods[0](x)
