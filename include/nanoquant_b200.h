@@ -184,8 +184,10 @@ int nq_gemv_group_fwd(const nq_linear_desc* linears_host, int n_linears, int T, 
  * every GPU that loads the library until the process exits); nothing is allocated or freed,
  * here or in any library it calls.  Limits: rank R <= nq_gemv_static_max_rank() (8192),
  * otherwise NQ_ERR_TOO_LARGE; T > 4 runs as several launches like nq_gemv_fwd.
- * The first call on a device looks the array's device address up (cudaGetSymbolAddress);
- * make that first call outside any stream capture.  Nothing has to start at zero between
+ * The first call on a device looks the array's device address up (cudaGetSymbolAddress)
+ * and keeps it for the life of the process: make that first call outside any stream
+ * capture, and do not reset the device's primary context afterwards (the kept address
+ * would be stale).  Nothing has to start at zero between
  * calls (the array is zero when the library is loaded; every launch tags its intermediate
  * with a fresh value of the counter), but every call reuses the same array, so two calls
  * that can overlap on the GPU (different streams, or threads, without ordering) race on

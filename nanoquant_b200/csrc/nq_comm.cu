@@ -34,6 +34,12 @@ struct PushParams {
 
 __global__ void __launch_bounds__(kPushThreads) allgather_push_kernel(const __grid_constant__ PushParams P) {
     __shared__ int is_last;
+    // Programmatic dependent launch on both sides (no-ops without the launch attribute): the next kernel of the
+    // stream may start its prologue now (it reads the gathered region only behind its own dependency wait, i.e.
+    // after this grid has completed), and this grid may have started while the kernel that produces the shard
+    // was still running: nothing of the shard is read before the wait.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     // epoch of this launch: every thread reads before the CTA barrier, one thread arrives behind it
     unsigned long long c;
     asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(c) : "l"(P.counter) : "memory");
@@ -111,8 +117,26 @@ int nq_allgather_push(const void* shard, size_t shard_bytes, void* const* rank_b
     size_t ctas = (P.n16 + (size_t)kPushThreads * 4 - 1) / ((size_t)kPushThreads * 4);   // four words per thread
     const size_t cap = (size_t)sm_count();
     ctas = ctas < 1 ? 1 : (ctas > cap ? cap : ctas);
-    allgather_push_kernel<<<(unsigned)ctas, kPushThreads, 0, as_stream(stream)>>>(P);
-    NQ_LAUNCH_CHECK();
+    // programmatic stream serialization: see the kernel; plain launches from then on if the driver refuses it once
+    static bool pdl_ok = true;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)ctas);
+    cfg.blockDim = dim3(kPushThreads);
+    cfg.stream = as_stream(stream);
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = pdl_ok ? 1 : 0;
+    void* args[] = {&P};
+    cudaError_t e = cudaLaunchKernelExC(&cfg, (const void*)allgather_push_kernel, args);
+    if (e != cudaSuccess && pdl_ok) {
+        (void)cudaGetLastError();
+        pdl_ok = false;
+        cfg.numAttrs = 0;
+        e = cudaLaunchKernelExC(&cfg, (const void*)allgather_push_kernel, args);
+    }
+    NQ_CUDA_TRY(e);
     return NQ_OK;
 }
 

@@ -37,7 +37,8 @@ def test_static_scratch_entry_point_matches_regular_one(dtype):
     from nanoquant_b200 import _lib
     from nanoquant_b200.kernel import utils as ku
     Lb = _lib.lib()
-    for (N, R, M, T) in ((1024, 288, 640, 3), (4096, 1600, 4096, 1)):
+    # 7 tokens: two launches on the shared array; rank 8192: the largest the array holds
+    for (N, R, M, T) in ((1024, 288, 640, 3), (4096, 1600, 4096, 1), (1024, 288, 640, 7), (512, 8192, 64, 2)):
         L = make_layer(N, R, M, T, dtype, seed=R + T)
         vt = ku.pack_tiles(half2_bits(L["V"]), (R, N), "half2")
         ut = ku.pack_tiles(half2_bits(L["U"]), (M, R), "half2")
@@ -48,12 +49,15 @@ def test_static_scratch_entry_point_matches_regular_one(dtype):
         assert parity_excess(exact_np(want), L["y64"], dtype) <= 0
         # same kernel, exact integer accumulation: the results are identical, well inside the bar
         assert torch.equal(first, want) and torch.equal(second, want)
+        # the array's status word is readable without its address: no wait gave up
+        assert Lb.nq_scratch_status(None, torch.cuda.current_stream().cuda_stream) == 0
 
 
 def test_static_scratch_entry_point_rejects_large_rank():
     from nanoquant_b200 import _lib
     Lb = _lib.lib()
-    big = int(Lb.nq_gemv_static_max_rank()) + 32
+    assert int(Lb.nq_gemv_static_max_rank()) == 8192
+    big = int(Lb.nq_gemv_static_max_rank()) + 1
     z = torch.zeros(16, dtype=torch.uint8, device="cuda")
     rc = Lb.nq_gemv_fwd_static(z.data_ptr(), z.data_ptr(), z.data_ptr(), None, z.data_ptr(), z.data_ptr(),
                                z.data_ptr(), 1, 64, big, 64, _lib.NQ_F16, torch.cuda.current_stream().cuda_stream)
