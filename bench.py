@@ -1313,6 +1313,8 @@ def main():
     ap.add_argument("--tokens", type=int, default=2048, help="tokens per GEMM in --mode prefill")
     ap.add_argument("--prefill-model", default="llama-2-7b", choices=sorted(PREFILL_SHAPES),
                     help="layer shapes of --mode prefill")
+    ap.add_argument("--precise-intermediate", action="store_true",
+                    help="bf16 GEMM path: keep the rank-R intermediate as scaled fp16 (nq_gemm_set_precise_intermediate)")
     ap.add_argument("--no-groups", action="store_true",
                     help="--mode prefill: one GEMM call per linear instead of launch groups for q/k/v and gate/up")
     ap.add_argument("--layers", type=int, default=LAYERS, help="decoder layers resident (fewer only for profiling)")
@@ -1325,6 +1327,9 @@ def main():
     set_workload(args.workload)
     if args.layers == WORKLOADS["qwen3-8b"][2]:   # the default of --layers means "all layers of the workload"
         args.layers = LAYERS
+    if args.precise_intermediate and args.impl != "reference":
+        from nanoquant_b200 import _lib
+        _lib.lib().nq_gemm_set_precise_intermediate(1)
     if args.impl == "reference":
         reference_arm(args)
     elif args.mode == "tp":

@@ -222,6 +222,15 @@ unsigned nq_gemv_set_wait_limit(unsigned polls);
  * a k split runs over the CTAs of a thread-block cluster and needs no scratch). */
 size_t nq_gemm_scratch_bytes(int T, int N, int R, int M);
 
+/* Precision of the rank-R intermediate of bf16 linears in the GEMM path (process-wide; returns the old setting).
+ * 0 (default): t is rounded to bf16 between the stages, as the reference's Marlin path keeps it in the I/O type;
+ * that rounding alone is up to 1.6e-3 of the output's maximum (inside the parity bar, by a narrow margin).
+ * 1: t is kept as fp16 times a per-token power of two found by one more small kernel per launch group (a bound
+ * on |t| from sum_k |s_in[k] x[k]| and max|s_mid|); the error beyond the output's own rounding drops to the fp16
+ * path's level (0.5e-3 of the maximum) at 12-21 % more time (least at 2048 tokens, most at 16).
+ * fp16 linears are not affected. */
+int nq_gemm_set_precise_intermediate(int on);
+
 /* y[T, M] = s_out * (U . (s_mid * (V . (s_in * x[T, N])))) as two tensor-core
  * GEMMs.  v_tiles / u_tiles are the same tile layout the GEMV reads.  The
  * intermediate is rounded to the I/O dtype between the stages, accumulation is

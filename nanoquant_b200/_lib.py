@@ -53,6 +53,7 @@ SIGNATURES = {
     "nq_gemv_fwd_static": (c_int, [c_void_p] * 7 + [c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "nq_gemv_static_max_rank": (c_size_t, []),
     "nq_gemm_scratch_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
+    "nq_gemm_set_precise_intermediate": (c_int, [c_int]),
     "nq_gemm_fwd": (c_int, [c_void_p] * 8 + [c_size_t, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "nq_gemm_group_scratch_bytes": (c_size_t, [ctypes.POINTER(LinearDesc), c_int, c_int]),
     "nq_gemm_group_fwd": (c_int, [ctypes.POINTER(LinearDesc), c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),

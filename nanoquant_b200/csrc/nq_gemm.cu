@@ -95,6 +95,7 @@ struct alignas(64) GemmJob {
     const void* pre;       // [K] input scales (I/O dtype) or nullptr (weights are +-1)
     const void* post;      // [Nout] output scales (I/O dtype) or nullptr
     void* out;             // [T, ld_out] I/O dtype
+    const int* row_exp;    // [T] per-token exponents of the intermediate or nullptr (see GemmParams::exp_sign)
     const void* bias;      // [Nout] (I/O dtype) or nullptr, added behind the output scale
     const void* resid;     // [T, ld_res] (I/O dtype) or nullptr, added behind the bias
     long long ld_out, ld_res;
@@ -115,8 +116,14 @@ struct GemmParams {
     int njobs;
     unsigned* status;      // device status word (0 = ok)
     int T, t_pad;          // tokens; slab row length (tokens, multiple of 4)
-    int is_bf16;
+    int is_bf16;           // type of the scales, bias and residual (the I/O type of the linear)
+    int a_bf16;            // type of the MMA operands: activations and expanded weights (bf16, else fp16)
+    int out_bf16;          // type of the output (bf16, else fp16)
     int saturate;          // apply the reference's output saturation bounds
+    // bf16 linears keep their rank-R intermediate as fp16 times a per-token power of two (11 significant bits
+    // instead of 8): stage 1 multiplies row t by 2^row_exp[t] (exp_sign = +1), stage 2 by 2^-row_exp[t] (-1).
+    // The exponents come from row_bound_kernel; 0: no row scaling.
+    int exp_sign;
     // Cluster split-K (more than 24 tokens, fewer output tiles than SMs): the `csplit` CTAs of a thread-block
     // cluster along grid.z share an output tile, each over `chunks_per` 256-column chunks of every job.  After the
     // main loops the accumulators are exchanged through distributed shared memory: 32-column blocks of the tile
@@ -364,7 +371,7 @@ __global__ void __launch_bounds__(GemmCfg<MH, NH>::kThreads) gemm_stage_kernel(c
         const int mw = warp == 1 ? 0 : 1;
         if (lane == 0 && mw < C::kIssuers) {
             const uint32_t acc_base = tmem_base + (uint32_t)(mw * MH * kBN);
-            const uint32_t fmt = P.is_bf16 ? 1u : 0u;
+            const uint32_t fmt = P.a_bf16 ? 1u : 0u;
             const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(kBN >> 3) << 17) |
                                    ((uint32_t)(kBM >> 4) << 24);
             bool ok = true;
@@ -396,7 +403,7 @@ __global__ void __launch_bounds__(GemmCfg<MH, NH>::kThreads) gemm_stage_kernel(c
         // group's rate; the small tiles run two groups of eight warps on alternate k blocks.
         const int tu = threadIdx.x - 32 * kFirstExpandWarp;
         const int grp = tu / kGroupThreads, tl = tu % kGroupThreads;
-        const uint32_t one2 = P.is_bf16 ? 0x3F803F80u : 0x3C003C00u;
+        const uint32_t one2 = P.a_bf16 ? 0x3F803F80u : 0x3C003C00u;
         bool ok = true;
         int c_seen = -1;
         for (int kb = grp; kb < nkb && ok; kb += kGroups) {
@@ -515,8 +522,16 @@ __global__ void __launch_bounds__(GemmCfg<MH, NH>::kThreads) gemm_stage_kernel(c
         // 32-column blocks of the MH accumulators, dealt round-robin to the warps that share a lane quarter
         if (ok) {
             tc_fence_after();
-            const float lim = P.saturate ? (P.is_bf16 ? 3.3895313892515355e+38f : 64504.0f) : 3.4e38f;
+            const float lim = P.saturate ? (P.out_bf16 ? 3.3895313892515355e+38f : 64504.0f) : 3.4e38f;
             const float4* post4 = reinterpret_cast<const float4*>(smem + kOffPost);
+            // per-token power of two of the intermediate (exact: the exponent is an integer), one load per
+            // token and thread ahead of the blocks (inside the loop its latency would repeat for every block)
+            float rs_mh[MH];
+#pragma unroll
+            for (int mh = 0; mh < MH; ++mh) {
+                const int row = m0 + kBM * mh + 32 * lq + lane;
+                rs_mh[mh] = (J.row_exp && row < P.T) ? exp2f((float)(P.exp_sign * J.row_exp[row])) : 1.f;
+            }
 #pragma unroll 1
             for (int blk = sub_w; blk < kBlocks; blk += kExpandThreads / 128) {
                 if (P.csplit > 1 && blk % P.csplit != crank) continue;   // another CTA of the cluster finishes this block
@@ -542,6 +557,7 @@ __global__ void __launch_bounds__(GemmCfg<MH, NH>::kThreads) gemm_stage_kernel(c
                 // The tensor-memory loads above are warp-collective: every lane takes part in every round, and a
                 // lane without a valid output only skips the stores.
                 const bool valid = row < P.T && n0 + c0 < J.Nout;
+                const float rs = MH == 1 ? rs_mh[0] : (mh == 0 ? rs_mh[0] : rs_mh[MH - 1]);
                 if (J.splits > 1) {   // partial sums of this k range: a warp writes 32 consecutive tokens per column
                     if (valid) {
                         float* slab = J.slabs + ((size_t)blockIdx.z * J.Nout + n0 + c0) * P.t_pad + row;
@@ -555,7 +571,8 @@ __global__ void __launch_bounds__(GemmCfg<MH, NH>::kThreads) gemm_stage_kernel(c
                 uint32_t packed[16];
 #pragma unroll
                 for (int e4 = 0; e4 < 8; ++e4) {
-                    const float4 sc = post4[(c0 >> 2) + e4];          // same address in every lane: broadcast
+                    float4 sc = post4[(c0 >> 2) + e4];                // same address in every lane: broadcast
+                    sc.x *= rs; sc.y *= rs; sc.z *= rs; sc.w *= rs;
                     float4 ad = bias4[(c0 >> 2) + e4];
                     if (res_row) {   // residual of these four outputs (element loads: the row may be unaligned or ragged)
                         const int cbase = n0 + c0 + 4 * e4;
@@ -571,7 +588,7 @@ __global__ void __launch_bounds__(GemmCfg<MH, NH>::kThreads) gemm_stage_kernel(c
                     const float v1 = fminf(fmaxf(__uint_as_float(r[4 * e4 + 1]) * sc.y + ad.y, -lim), lim);
                     const float v2 = fminf(fmaxf(__uint_as_float(r[4 * e4 + 2]) * sc.z + ad.z, -lim), lim);
                     const float v3 = fminf(fmaxf(__uint_as_float(r[4 * e4 + 3]) * sc.w + ad.w, -lim), lim);
-                    if (P.is_bf16) {
+                    if (P.out_bf16) {
                         const __nv_bfloat162 a2 = __floats2bfloat162_rn(v0, v1), b2 = __floats2bfloat162_rn(v2, v3);
                         packed[2 * e4] = *reinterpret_cast<const uint32_t*>(&a2);
                         packed[2 * e4 + 1] = *reinterpret_cast<const uint32_t*>(&b2);
@@ -619,7 +636,7 @@ __global__ void __launch_bounds__(GemmCfg<MH, NH>::kThreads) gemm_stage_kernel(c
             __threadfence();
             const int tp4 = P.t_pad >> 2;
             const int ncols = min(kBN, J.Nout - n0);
-            const float lim = P.saturate ? (P.is_bf16 ? 3.3895313892515355e+38f : 64504.0f) : 3.4e38f;
+            const float lim = P.saturate ? (P.out_bf16 ? 3.3895313892515355e+38f : 64504.0f) : 3.4e38f;
             const float* post_s = reinterpret_cast<const float*>(smem + kOffPost);
             const float* bias_s = reinterpret_cast<const float*>(smem + kOffBias);
             // Items: (column, group of four tokens).  Two items and eight splits per round keep 16 independent
@@ -670,9 +687,10 @@ __global__ void __launch_bounds__(GemmCfg<MH, NH>::kThreads) gemm_stage_kernel(c
                                 ex += P.is_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(J.resid)[ra])
                                                 : __half2float(static_cast<const __half*>(J.resid)[ra]);
                             }
-                            const float v1 = fminf(fmaxf(o[j] * sc + ex, -lim), lim);
+                            const float rs = J.row_exp ? exp2f((float)(P.exp_sign * J.row_exp[row])) : 1.f;
+                            const float v1 = fminf(fmaxf(o[j] * (sc * rs) + ex, -lim), lim);
                             const size_t at = (size_t)row * J.ld_out + n0 + col;
-                            if (P.is_bf16) static_cast<__nv_bfloat16*>(J.out)[at] = __float2bfloat16(v1);
+                            if (P.out_bf16) static_cast<__nv_bfloat16*>(J.out)[at] = __float2bfloat16(v1);
                             else static_cast<__half*>(J.out)[at] = __float2half(v1);
                         }
                     }
@@ -691,6 +709,89 @@ __global__ void __launch_bounds__(GemmCfg<MH, NH>::kThreads) gemm_stage_kernel(c
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)C::kTmemCols)
                      : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Per-token exponents of a bf16 linear's intermediate.  |t[tok, r]| <= max|s_mid| * sum_k |s_in[k] * x[tok, k]| =: B,
+// so t * 2^e with B * 2^e <= 2^14 fits fp16 for every r, whatever the signs in V are; typical elements sit
+// sqrt(K) below the bound, far above fp16's subnormal range.  One CTA per eight tokens, up to four linears (grid.y).
+// ---------------------------------------------------------------------------
+struct BoundJob {
+    const uint16_t* x;      // [T, ldx] bf16
+    long long ldx;
+    const uint16_t* s_in;   // [K] bf16
+    const uint16_t* s_mid;  // [R] bf16 or nullptr (ones)
+    int* row_exp;           // [T]
+    int K, R;
+};
+struct BoundParams {
+    BoundJob job[kMaxGemmJobs];
+    int T;
+};
+
+__global__ void __launch_bounds__(256) row_bound_kernel(const __grid_constant__ BoundParams P) {
+    const BoundJob& J = P.job[blockIdx.y];
+    __shared__ float s_red[8][9];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    auto bf = [](uint16_t h) { return __uint_as_float((uint32_t)h << 16); };
+    // the layer's constants first (they do not depend on the previous kernel)
+    float m = J.s_mid ? 0.f : 1.f;
+    if (J.s_mid)
+        for (int r = threadIdx.x; r < J.R; r += 256) m = fmaxf(m, fabsf(bf(J.s_mid[r])));
+    for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // the activations come from the previous kernel
+    // every thread takes 8-column pieces of all eight tokens of the CTA: the loads of a round are independent,
+    // so a row costs one memory round trip, not one per piece
+    const int tok0 = blockIdx.x * 8;
+    float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    const bool vec = (reinterpret_cast<uintptr_t>(J.x) & 15u) == 0 && (J.ldx % 8) == 0 &&
+                     (reinterpret_cast<uintptr_t>(J.s_in) & 15u) == 0;
+    const int kvec = vec ? (J.K & ~7) : 0;
+    for (int k = threadIdx.x * 8; k < kvec; k += 2048) {
+        const uint4 b = *reinterpret_cast<const uint4*>(J.s_in + k);
+        uint4 a[8];
+#pragma unroll
+        for (int t = 0; t < 8; ++t)
+            a[t] = tok0 + t < P.T ? *reinterpret_cast<const uint4*>(J.x + (size_t)(tok0 + t) * J.ldx + k) : make_uint4(0, 0, 0, 0);
+        const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {
+            const uint32_t aw[4] = {a[t].x, a[t].y, a[t].z, a[t].w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                sum[t] += fabsf(__uint_as_float(aw[i] << 16) * __uint_as_float(bw[i] << 16)) +
+                          fabsf(__uint_as_float(aw[i] & 0xFFFF0000u) * __uint_as_float(bw[i] & 0xFFFF0000u));
+        }
+    }
+    for (int k = kvec + threadIdx.x; k < J.K; k += 256) {
+        const float sk = bf(J.s_in[k]);
+#pragma unroll
+        for (int t = 0; t < 8; ++t)
+            if (tok0 + t < P.T) sum[t] += fabsf(bf(J.x[(size_t)(tok0 + t) * J.ldx + k]) * sk);
+    }
+#pragma unroll
+    for (int t = 0; t < 8; ++t)
+        for (int o = 16; o; o >>= 1) sum[t] += __shfl_xor_sync(0xffffffffu, sum[t], o);
+    if (lane == 0) {
+#pragma unroll
+        for (int t = 0; t < 8; ++t) s_red[warp][t] = sum[t];
+        s_red[warp][8] = m;
+    }
+    __syncthreads();
+    if (threadIdx.x < 8 && tok0 + (int)threadIdx.x < P.T) {
+        float total = 0.f, mm = 0.f;
+        for (int w = 0; w < 8; ++w) { total += s_red[w][threadIdx.x]; mm = fmaxf(mm, s_red[w][8]); }
+        const float bound = total * mm * 1.0001f;   // (rounding of the sum itself)
+        int e = 0;
+        if (bound > 0.f && bound < 3.0e38f) {
+            int q;
+            (void)frexpf(bound, &q);                // bound = f * 2^q, 0.5 <= f < 1
+            e = 14 - q;
+            e = e > 100 ? 100 : (e < -100 ? -100 : e);
+        }
+        J.row_exp[tok0 + threadIdx.x] = e;
     }
 }
 
@@ -727,6 +828,11 @@ struct StageJob {
     const void* bias;       // [Nout] or nullptr
     const void* resid;      // [T, ld_res] or nullptr
     long long ld_res;
+    const int* row_exp;     // [T] per-token exponents of the intermediate or nullptr
+};
+// Types of a stage: scales / bias / residual, MMA operands, output; sign of the row exponents (0: none).
+struct StageTypes {
+    int io_bf16, a_bf16, out_bf16, exp_sign;
 };
 
 // Tile shape of a launch and the k split of each of its jobs.
@@ -898,7 +1004,7 @@ static GroupPlan plan_group(int T, int n, const int* K, const int* Nout, bool al
 
 // One stage of up to four linears: out_j[T, Nout_j] = (a_j[T, K_j] . W_j^T) * post_j.  `counters` (zero
 // between launches) and `slabs` may be nullptr: no k split.
-static int launch_stage(const StageJob* jobs, int n, int T, int dtype, int saturate, unsigned* status,
+static int launch_stage(const StageJob* jobs, int n, int T, StageTypes ty, int saturate, unsigned* status,
                         unsigned* counters, float* slabs, cudaStream_t stream) {
     if (n < 1 || n > kMaxGemmJobs) return NQ_ERR_UNSUPPORTED;
     EncodeTiledFn enc = encode_tiled_fn();
@@ -920,7 +1026,10 @@ static int launch_stage(const StageJob* jobs, int n, int T, int dtype, int satur
     P.status = status;
     P.T = T;
     P.t_pad = pl.t_pad;
-    P.is_bf16 = dtype == NQ_BF16;
+    P.is_bf16 = ty.io_bf16;
+    P.a_bf16 = ty.a_bf16;
+    P.out_bf16 = ty.out_bf16;
+    P.exp_sign = ty.exp_sign;
     P.saturate = saturate;
     P.csplit = pl.csplit;
     for (int j = 0; j < n; ++j) {
@@ -930,7 +1039,7 @@ static int launch_stage(const StageJob* jobs, int n, int T, int dtype, int satur
         const cuuint64_t strides[1] = {(cuuint64_t)S.lda * 2};
         const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)(kBM * mh)};
         const cuuint32_t estr[2] = {1, 1};
-        const CUresult r = enc(&J.map_a, dtype == NQ_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+        const CUresult r = enc(&J.map_a, ty.a_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
                                2, const_cast<void*>(S.a), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -940,6 +1049,7 @@ static int launch_stage(const StageJob* jobs, int n, int T, int dtype, int satur
         J.post = S.post;
         J.out = S.out;
         J.ld_out = S.ld_out;
+        J.row_exp = ty.exp_sign ? S.row_exp : nullptr;
         J.bias = S.bias;
         J.resid = S.resid;
         J.ld_res = S.ld_res;
@@ -988,21 +1098,29 @@ static int launch_stage(const StageJob* jobs, int n, int T, int dtype, int satur
     return NQ_OK;
 }
 
+static int g_precise_intermediate = 0;   // see nq_gemm_set_precise_intermediate
+
 }  // namespace nq
 
 using namespace nq;
 
 extern "C" {
 
-// Scratch of a GEMM group: header (status word, tile counters), the intermediates t_j[T, R_j] (I/O dtype,
-// 256-byte aligned each), split-K slabs (shared by the two stages).
-static size_t gemm_group_layout(const nq_linear_desc* d, int n, int T, size_t* t_off, size_t* slab_off) {
+// Scratch of a GEMM group: header (status word, tile counters), the intermediates t_j[T, R_j] (16-bit,
+// 256-byte aligned each), the per-token exponents of each intermediate (T words each; used by bf16 linears),
+// split-K slabs (shared by the two stages).
+static size_t gemm_group_layout(const nq_linear_desc* d, int n, int T, size_t* t_off, size_t* slab_off,
+                                size_t* exp_off = nullptr) {
     size_t off = 256;
     int K1[kMaxGemmJobs], N1[kMaxGemmJobs], K2[kMaxGemmJobs], N2[kMaxGemmJobs];
     for (int j = 0; j < n; ++j) {
         if (t_off) t_off[j] = off;
         off += ((size_t)T * (size_t)d[j].R * 2 + 255) / 256 * 256;
         K1[j] = d[j].N; N1[j] = d[j].R; K2[j] = d[j].R; N2[j] = d[j].M;
+    }
+    for (int j = 0; j < n; ++j) {
+        if (exp_off) exp_off[j] = off;
+        off += ((size_t)T * sizeof(int) + 255) / 256 * 256;
     }
     if (slab_off) *slab_off = off;
     const size_t a = plan_group(T, n, K1, N1, true, false).slab_floats, b = plan_group(T, n, K2, N2, true, false).slab_floats;
@@ -1030,8 +1148,9 @@ int nq_onebit_gemm_fwd(const void* x, const void* tiles, const void* s_in, const
     if (T <= 0 || K <= 0 || Nout <= 0) return NQ_ERR_SHAPE;
     if (dtype != NQ_F16 && dtype != NQ_BF16) return NQ_ERR_DTYPE;
     if (!aligned16(tiles)) return NQ_ERR_ALIGN;
-    const StageJob job = {x, K, tiles, s_in, s_out, y, Nout, K, Nout, nullptr, nullptr, 0};
-    return launch_stage(&job, 1, T, dtype, 1, static_cast<unsigned*>(status_word) + 2, nullptr, nullptr,
+    const StageJob job = {x, K, tiles, s_in, s_out, y, Nout, K, Nout, nullptr, nullptr, 0, nullptr};
+    const int b16 = dtype == NQ_BF16;
+    return launch_stage(&job, 1, T, StageTypes{b16, b16, b16, 0}, 1, static_cast<unsigned*>(status_word) + 2, nullptr, nullptr,
                         as_stream(stream));
 }
 
@@ -1050,8 +1169,8 @@ int nq_gemm_group_fwd(const nq_linear_desc* d, int n_linears, int T, int dtype, 
         if (L.N % 8 || L.R % 8) return NQ_ERR_SHAPE;
         if (!aligned16(L.v_tiles) || !aligned16(L.u_tiles)) return NQ_ERR_ALIGN;
     }
-    size_t t_off[kMaxGemmJobs], slab_off = 0;
-    if (scratch_bytes < gemm_group_layout(d, n_linears, T, t_off, &slab_off)) return NQ_ERR_SCRATCH;
+    size_t t_off[kMaxGemmJobs], exp_off[kMaxGemmJobs], slab_off = 0;
+    if (scratch_bytes < gemm_group_layout(d, n_linears, T, t_off, &slab_off, exp_off)) return NQ_ERR_SCRATCH;
     unsigned* status = static_cast<unsigned*>(scratch) + 2;   // same word as the GEMV header's status
     // Both stages use the same counters and slab space: a stage touches them only after the kernel before it
     // has completed (its stores come behind the dependency wait).
@@ -1061,12 +1180,53 @@ int nq_gemm_group_fwd(const nq_linear_desc* d, int n_linears, int T, int dtype, 
     for (int j = 0; j < n_linears; ++j) {
         const nq_linear_desc& L = d[j];
         void* t = static_cast<char*>(scratch) + t_off[j];
-        s1[j] = {L.x, L.ldx, L.v_tiles, L.s_in, L.s_mid, t, L.R, L.N, L.R, nullptr, nullptr, 0};
-        s2[j] = {t, L.R, L.u_tiles, nullptr, L.s_out, L.y, L.ldy, L.R, L.M, L.bias, L.residual, L.ldr};
+        int* row_exp = reinterpret_cast<int*>(static_cast<char*>(scratch) + exp_off[j]);
+        s1[j] = {L.x, L.ldx, L.v_tiles, L.s_in, L.s_mid, t, L.R, L.N, L.R, nullptr, nullptr, 0, row_exp};
+        s2[j] = {t, L.R, L.u_tiles, nullptr, L.s_out, L.y, L.ldy, L.R, L.M, L.bias, L.residual, L.ldr, row_exp};
     }
-    const int st = launch_stage(s1, n_linears, T, dtype, 0, status, counters, slabs, as_stream(stream));
+    if (dtype == NQ_F16 || !g_precise_intermediate) {   // the intermediate in the I/O type, as it comes
+        const int b16 = dtype == NQ_BF16;
+        const StageTypes ty = {b16, b16, b16, 0};
+        const int st = launch_stage(s1, n_linears, T, ty, 0, status, counters, slabs, as_stream(stream));
+        if (st != NQ_OK) return st;
+        return launch_stage(s2, n_linears, T, ty, 1, status, counters, slabs, as_stream(stream));
+    }
+    // bf16 with the precise intermediate switched on: a bf16 intermediate carries 8 significant bits into stage 2
+    // (its rounding alone is up to 1.6e-3 of the output's maximum); here it is kept as fp16 times a per-token
+    // power of two instead.  row_bound_kernel finds the exponents from a bound on |t| that holds for any signs;
+    // stage 2 then runs as an fp16 MMA on +-1 weights.  One more small kernel per launch group.
+    {
+        BoundParams B;
+        memset(&B, 0, sizeof(B));
+        B.T = T;
+        for (int j = 0; j < n_linears; ++j) {
+            const nq_linear_desc& L = d[j];
+            B.job[j] = {static_cast<const uint16_t*>(L.x), L.ldx, static_cast<const uint16_t*>(L.s_in),
+                        static_cast<const uint16_t*>(L.s_mid), const_cast<int*>(s1[j].row_exp), L.N, L.R};
+        }
+        static bool pdl_ok = true;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)((T + 7) / 8), (unsigned)n_linears);
+        cfg.blockDim = dim3(256);
+        cfg.stream = as_stream(stream);
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr.val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = pdl_ok ? 1 : 0;
+        void* args[] = {&B};
+        cudaError_t e = cudaLaunchKernelExC(&cfg, (const void*)row_bound_kernel, args);
+        if (e != cudaSuccess && pdl_ok) {
+            (void)cudaGetLastError();
+            pdl_ok = false;
+            cfg.numAttrs = 0;
+            e = cudaLaunchKernelExC(&cfg, (const void*)row_bound_kernel, args);
+        }
+        NQ_CUDA_TRY(e);
+    }
+    const int st = launch_stage(s1, n_linears, T, StageTypes{1, 1, 0, +1}, 0, status, counters, slabs, as_stream(stream));
     if (st != NQ_OK) return st;
-    return launch_stage(s2, n_linears, T, dtype, 1, status, counters, slabs, as_stream(stream));
+    return launch_stage(s2, n_linears, T, StageTypes{1, 0, 1, -1}, 1, status, counters, slabs, as_stream(stream));
 }
 
 int nq_gemm_fwd(const void* x, const void* s_in, const void* v_tiles, const void* s_mid, const void* u_tiles,
@@ -1081,6 +1241,12 @@ int nq_gemm_fwd(const void* x, const void* s_in, const void* v_tiles, const void
     return nq_gemm_group_fwd(&d, 1, T, dtype, scratch, scratch_bytes, stream);
 }
 
+
+int nq_gemm_set_precise_intermediate(int on) {
+    const int old = g_precise_intermediate;
+    g_precise_intermediate = on ? 1 : 0;
+    return old;
+}
 
 // One decode launch handles four tokens; from five tokens on the split-K GEMM is faster than two launches.
 int nq_gemv_max_tokens(void) { return 4; }

@@ -72,6 +72,13 @@ def reserve_scratch(device: torch.device, nbytes: int) -> torch.Tensor:
     return buf
 
 
+def set_precise_intermediate(on: bool) -> bool:
+    """bf16 linears through the GEMM path (5 tokens and more): keep the rank-R intermediate as fp16 times a
+    per-token power of two instead of rounding it to bf16 between the stages (one more small kernel per launch
+    group; see ``nq_gemm_set_precise_intermediate``).  Process-wide; returns the previous setting."""
+    return bool(_lib.lib().nq_gemm_set_precise_intermediate(1 if on else 0))
+
+
 def group_scratch_bytes(shapes, T: int) -> int:
     """Scratch bytes one launch group of linears with ``shapes = [(N, R, M), ...]`` needs at `T` tokens."""
     L = _lib.lib()

@@ -220,6 +220,54 @@ def test_c_abi_gemm_group_matches_single_linears(T):
         col += m
 
 
+@pytest.fixture
+def precise_intermediate():
+    from nanoquant_b200 import ops
+    old = ops.set_precise_intermediate(True)
+    yield
+    ops.set_precise_intermediate(old)
+
+
+@pytest.mark.parametrize("T,N,R,M", [(7, 1032, 264, 1001), (16, 4096, 1600, 4096), (128, 4096, 1536, 4096), (300, 2048, 1000, 1536),
+                                     (2048, 2048, 1024, 2048)])
+def test_precise_intermediate_of_bf16_linears(precise_intermediate, T, N, R, M):
+    # The rank-R intermediate as fp16 times a per-token power of two (slab split, cluster split and plain tiles):
+    # inside the parity bar like the default, and the error BEYOND the output's own rounding is below 1e-3 of the
+    # maximum (with the bf16 intermediate it is up to 1.6e-3).  A token scaled by 2^20 and one by 2^-20 check that
+    # the exponents follow the tokens, and an all-zero token that nothing divides by zero.
+    from nanoquant_b200 import _lib
+    from tests.util import tiles_on_gpu, elementwise_bound
+    Lb = _lib.lib()
+    dtype = torch.bfloat16
+    L = make_layer(N, R, M, T, dtype, seed=40 + T)
+    x = L["x"].clone()
+    if T >= 7:
+        x[1] *= 2.0 ** 20
+        x[2] *= 2.0 ** -20
+        x[3] = 0
+    y64 = oc.forward_fp64(exact_np(x), L["V"], L["U"], exact_np(L["s_pre"]), exact_np(L["s_mid"]), exact_np(L["s_post"]))
+    vt, ut = tiles_on_gpu(L["V"]), tiles_on_gpu(L["U"])
+    y = torch.full((T, M), float("nan"), dtype=dtype, device="cuda")
+    nb = Lb.nq_gemm_scratch_bytes(T, N, R, M)
+    scratch = torch.zeros(nb, dtype=torch.uint8, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    for _ in range(2):
+        _lib.check(Lb.nq_gemm_fwd(x.data_ptr(), L["s_pre"].data_ptr(), vt.data_ptr(), L["s_mid"].data_ptr(), ut.data_ptr(),
+                                  L["s_post"].data_ptr(), y.data_ptr(), scratch.data_ptr(), nb, T, N, R, M, _lib.NQ_BF16, st), "gemm")
+    assert Lb.nq_scratch_status(scratch.data_ptr(), st) == 0
+    yn = exact_np(y)
+    for rows in ([1], [2], [3], [r for r in range(T) if r not in (1, 2, 3)] if T >= 7 else list(range(T))):
+        if T < 7 and rows != list(range(T)):
+            continue
+        a, b = yn[rows], y64[rows]
+        if not np.any(b):
+            assert not np.any(a)
+            continue
+        half_ulp = elementwise_bound(b, dtype, 0.0, a)
+        beyond = np.max(np.abs(a - b) - half_ulp) / np.max(np.abs(b))
+        assert beyond <= 1e-3, (rows[:3], beyond)
+
+
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("T", [25, 40, 100, 128, 200, 300])
 def test_c_abi_gemm_cluster_split(T, dtype):
