@@ -197,10 +197,11 @@ __global__ void __launch_bounds__(256) pack_marlin_staged_kernel(const int8_t* _
         for (int o8 = 0; o8 < 2; ++o8)
 #pragma unroll
             for (int r8 = 0; r8 < 2; ++r8) {
-                const int8_t* p = tile + (16 * o16 + 8 * o8 + o1) * kMarlinPitch + 16 * trl + 8 * r8 + 2 * r2;
+                // the two weights of a bit pair are neighbours: one 16-bit load, sign bits 7 and 15 -> pos and pos + 16
+                const uint32_t h = *reinterpret_cast<const uint16_t*>(tile + (16 * o16 + 8 * o8 + o1) * kMarlinPitch +
+                                                                      16 * trl + 8 * r8 + 2 * r2);
                 const int pos = 15 - 4 * o16 - 2 * o8 - r8;
-                bits |= (uint32_t)(p[0] < 0) << pos;
-                bits |= (uint32_t)(p[1] < 0) << (pos + 16);
+                bits |= (((h >> 7) & 1u) | ((h << 1) & 0x10000u)) << pos;
             }
     B[(k0 / 16 + trl) * (out_f / 2) + 32 * to + colw] = bits;
 }
