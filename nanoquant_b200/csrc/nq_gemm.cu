@@ -1,6 +1,6 @@
 // Prefill GEMM for the binary low-rank linear on the 5th-generation tensor cores.
 //
-//   stage 1:  t[T, R] = ((x * s_in) . V^T) * s_mid        (t kept in the I/O dtype)
+//   stage 1:  t[T, R] = ((x * s_in) . V^T) * s_mid        (t kept in the I/O dtype by default)
 //   stage 2:  y[T, M] = (t . U^T) * s_out
 //
 // Each stage is one launch of the same kernel: Out[T, Nout] = (A[T, K] . W[Nout, K]^T) * post,
@@ -22,6 +22,12 @@
 //               stage's "ready" barrier; afterwards the same warps run the epilogue.
 //   epilogue    tcgen05.ld of the accumulator(s) (lane = token, column = output row),
 //               * post[n], saturate, convert, 16-byte stores.
+//
+// Launches with fewer output tiles than SMs split K: over independent CTAs with fp32 slabs in global
+// memory and a last-CTA reduction (up to 24 tokens), or over the CTAs of a thread-block cluster that
+// exchange their partial sums through distributed shared memory (more tokens); see GemmParams::csplit
+// and plan_group.  bf16 linears may keep their intermediate as fp16 times a per-token power of two
+// (row_bound_kernel, nq_gemm_set_precise_intermediate).
 //
 // The packed operand is the same tile layout the decode GEMV streams (nq_rows_to_tiles),
 // so a layer keeps one copy of its weights for both kernels.  No TMA multicast is used.
