@@ -359,7 +359,9 @@ class StepCycle:
 def check_step(T, dtype, device):
     """The launch structure of the timed step on ONE decoder layer with real factors: seeded +-1 matrices packed on
     the GPU (nq_pack_rows, nq_rows_to_tiles), the same four group launches (q/k/v, o, gate/up, down), every output
-    against the fp64 oracle.  Outside the timed region; returns max |y - y64| / max |y64| over the 7 linears."""
+    against the fp64 oracle.  Outside the timed region; returns (max |y - y64| / max |y64|, the same with half a unit
+    in the last place of the output type taken off every element's error) over the 7 linears, and stops the
+    benchmark when the second exceeds the tests' bar of 2e-3."""
     import numpy as np
     import torch
     from nanoquant_b200 import _lib
@@ -393,13 +395,22 @@ def check_step(T, dtype, device):
                        scratch.data_ptr(), nb, st), "check launch")
         if L.nq_scratch_status(scratch.data_ptr(), st) != 0:
             raise SystemExit("bench.py --check: a device-side wait timed out")
-    worst = 0.0
+    worst, beyond = 0.0, 0.0
     f64 = lambda t_: t_.float().cpu().numpy().astype(np.float64)
+    bits = 8 if dtype == torch.bfloat16 else 11     # significant bits of the output type
     for t in keep:
         y64 = oc.forward_fp64(f64(t["x"]), t["V"].cpu().numpy(), t["U"].cpu().numpy(), f64(t["s_in"]), f64(t["s_mid"]),
                               f64(t["s_out"]))
-        worst = max(worst, oc.rel_err(f64(t["y"]), y64))
-    return worst
+        y = f64(t["y"])
+        worst = max(worst, oc.rel_err(y, y64))
+        # the parity bar of the tests: |y - y64| <= 2e-3 * max|y64| + half a unit in the last place at that element
+        mag = np.maximum(np.maximum(np.abs(y64), np.abs(y)), 2.0 ** -126)
+        half_ulp = 2.0 ** (np.floor(np.log2(mag)) - bits)
+        beyond = max(beyond, float(np.max(np.abs(y - y64) - half_ulp) / np.max(np.abs(y64))))
+    if beyond > 2e-3:
+        raise SystemExit(f"bench.py: output check failed: an element is {beyond:.3e} of the maximum off the oracle beyond "
+                         f"its own rounding (bar 2e-3)")
+    return worst, beyond
 
 
 VOCAB = {"qwen3-8b": 151936, "llama-3.2-1b": 128256}
@@ -513,8 +524,6 @@ def gpu_arm(args):
     dtype = torch.bfloat16
     # the launches that are about to be timed, on real factors, against the oracle (bf16 outputs: 2e-3 + half an ulp)
     check_err = check_step(T, dtype, device) if (rank == 0 and not args.no_check) else None
-    if check_err is not None and not check_err <= 2e-3 + 2.0 ** -8:
-        raise SystemExit(f"bench.py: output check failed, max|y-y64|/max|y64| = {check_err:.3e}")
     step = StepCycle(T, dtype, device, args.layers)
     step.capture()
 
@@ -611,7 +620,9 @@ def gpu_arm(args):
                 "h2d_bytes_per_step": sum(v.numel() * v.element_size() for v in hx.values()),
                 "d2h_bytes_per_step": hy.numel() * hy.element_size()},
         "gpu_launches": step.kernels_per_step * args.steps,
-        "checked": check_err is not None, "max_rel_err": check_err,
+        "checked": check_err is not None, "max_rel_err": check_err[0] if check_err else None,
+        "max_err_beyond_output_rounding": check_err[1] if check_err else None,
+        "parity_bar": "2e-3 * max|y64| + half ulp of the output type at the element",
         "clocks": clocks,
     }
     if out_note:
