@@ -590,15 +590,18 @@ __global__ void __launch_bounds__(GemmCfg<MH, NH>::kThreads) gemm_stage_kernel(c
                         }
                         ad.x += rr[0]; ad.y += rr[1]; ad.z += rr[2]; ad.w += rr[3];
                     }
-                    const float v0 = fminf(fmaxf(__uint_as_float(r[4 * e4 + 0]) * sc.x + ad.x, -lim), lim);
-                    const float v1 = fminf(fmaxf(__uint_as_float(r[4 * e4 + 1]) * sc.y + ad.y, -lim), lim);
-                    const float v2 = fminf(fmaxf(__uint_as_float(r[4 * e4 + 2]) * sc.z + ad.z, -lim), lim);
-                    const float v3 = fminf(fmaxf(__uint_as_float(r[4 * e4 + 3]) * sc.w + ad.w, -lim), lim);
+                    float v0 = __uint_as_float(r[4 * e4 + 0]) * sc.x + ad.x, v1 = __uint_as_float(r[4 * e4 + 1]) * sc.y + ad.y;
+                    float v2 = __uint_as_float(r[4 * e4 + 2]) * sc.z + ad.z, v3 = __uint_as_float(r[4 * e4 + 3]) * sc.w + ad.w;
                     if (P.out_bf16) {
-                        const __nv_bfloat162 a2 = __floats2bfloat162_rn(v0, v1), b2 = __floats2bfloat162_rn(v2, v3);
-                        packed[2 * e4] = *reinterpret_cast<const uint32_t*>(&a2);
-                        packed[2 * e4 + 1] = *reinterpret_cast<const uint32_t*>(&b2);
+                        // the reference's bound for bf16 is the largest finite bf16: the saturating conversion applies it
+                        // (this arithmetic, two clamps per output at half rate, was half of a large tile's epilogue)
+                        asm("cvt.rn.satfinite.bf16x2.f32 %0, %1, %2;" : "=r"(packed[2 * e4]) : "f"(v1), "f"(v0));
+                        asm("cvt.rn.satfinite.bf16x2.f32 %0, %1, %2;" : "=r"(packed[2 * e4 + 1]) : "f"(v3), "f"(v2));
                     } else {
+                        if (P.saturate) {
+                            v0 = fminf(fmaxf(v0, -lim), lim); v1 = fminf(fmaxf(v1, -lim), lim);
+                            v2 = fminf(fmaxf(v2, -lim), lim); v3 = fminf(fmaxf(v3, -lim), lim);
+                        }
                         const __half2 a2 = __floats2half2_rn(v0, v1), b2 = __floats2half2_rn(v2, v3);
                         packed[2 * e4] = *reinterpret_cast<const uint32_t*>(&a2);
                         packed[2 * e4 + 1] = *reinterpret_cast<const uint32_t*>(&b2);
