@@ -924,11 +924,11 @@ static int cluster_capacity(int mh, int nh, int s) {
         if (set_kernel_attributes() != NQ_OK || cudaOccupancyMaxActiveClusters(&clusters, ki.fn, &cfg) != cudaSuccess ||
             clusters <= 0) {
             (void)cudaGetLastError();
-            clusters = sm_count() * 7 / 8 / s;   // a guess on the safe side
+            clusters = 0;   // this cluster size cannot be launched here: the planner leaves it out
         }
-        c = clusters * s;
+        c = clusters > 0 ? clusters * s : -1;
     }
-    return c;
+    return c > 0 ? c : 0;
 }
 
 // Tile shape (128*mh tokens x 128*nh weight rows) by a small cost model: a CTA needs a measured number of
@@ -967,6 +967,7 @@ static GroupPlan plan_group(int T, int n, const int* K, const int* Nout, bool al
                 if ((long long)s * ((ki.blocks + s - 1) / s) * (128 * 32 * 4) > ki.pipe_bytes) continue;
             }
             const long long resident = s == 1 ? sms : cluster_capacity(c[0], c[1], s);
+            if (resident <= 0) continue;
             const long long waves = (tiles * s + resident - 1) / resident;
             const long long steps = 4LL * ((max_chunks + s - 1) / s);
             const long long cost = waves * (steps * per_step + fixed + (s > 1 ? 2500 + 300LL * s : 0));
