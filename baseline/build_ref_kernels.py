@@ -37,6 +37,8 @@ def build(reference_root: str) -> str:
     tlib = os.path.join(os.path.dirname(torch.__file__), "lib")
     subprocess.run(["g++", "-shared", "-o", LIB, obj_k, obj_b, f"-L{tlib}", "-L/usr/local/cuda/lib64", "-lc10", "-lc10_cuda",
                     "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-lcudart"], check=True)
+    for obj in (obj_k, obj_b):   # only the library travels
+        os.remove(obj)
     return LIB
 
 
