@@ -325,6 +325,22 @@ class Step:
         torch.cuda.current_stream(self.device).wait_stream(s)
         torch.cuda.synchronize(self.device)
 
+    def capture_e2e(self, hx, hy):
+        """The step with its host traffic as ONE graph: the activations copied in from the pinned host tensors `hx`,
+        the launches, the last output copied out to the pinned host tensor `hy` (what a serving loop replays per token)."""
+        torch = self.torch
+        s = torch.cuda.Stream(self.device)
+        s.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(s):
+            self.e2e_graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.e2e_graph, stream=s):
+                for k in hx:
+                    self.x[k].copy_(hx[k], non_blocking=True)
+                self.run()
+                hy.copy_(self.last_y, non_blocking=True)
+        torch.cuda.current_stream(self.device).wait_stream(s)
+        torch.cuda.synchronize(self.device)
+
     def status(self):
         return self.L.nq_scratch_status(self.scratch.data_ptr(), self.torch.cuda.current_stream(self.device).cuda_stream)
 
@@ -561,12 +577,12 @@ def gpu_arm(args):
     # end to end through host buffers
     hx = {k: v.cpu().pin_memory() for k, v in step.current().x.items()}
     hy = torch.empty_like(step.current().last_y, device="cpu").pin_memory()
-    def e2e_step():
-        for k in hx:
-            step.current().x[k].copy_(hx[k], non_blocking=True)
-        cur = step.current()
-        step.replay()
-        hy.copy_(cur.last_y, non_blocking=True)
+    for st_ in step.steps:
+        st_.capture_e2e(hx, hy)
+
+    def e2e_step():   # host -> device copies, the step, device -> host copy: one graph launch and one wait per token
+        step.current().e2e_graph.replay()
+        step.i += 1
         torch.cuda.current_stream(device).synchronize()
     for _ in range(3):
         e2e_step()
